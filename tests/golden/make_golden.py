@@ -1,0 +1,128 @@
+"""Generates tests/golden/hotpath_golden.npz from code the reference itself ships.
+
+Run in a container that has the reference checkout (default /root/reference) and
+oracle/_ref/libmetalref.so built (``make -C oracle``):
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+Two sources, both the reference's own code, neither needing MLX:
+
+* ``models/quantize_weights.py`` (numpy): symmetric group-wise quantiser, q4 packing and the fp32
+  ``(q - zero) * scale`` dequantisation.
+* the Metal kernel bodies under ``kernels/`` compiled as C++ (oracle/metal_shim.cpp): dequant,
+  serial matvec, paged q4/q8 GQA decode attention (ragged lengths, permuted block table with -1
+  entries), fused SwiGLU, block-table lookup.
+
+Inputs come from numpy's seeded generator and are stored next to the outputs, so the fixtures
+are self-contained.
+"""
+from __future__ import annotations
+
+import importlib.util
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+from oracle import metal_ref  # noqa: E402
+
+
+def _load_reference_quantizer(ref_root: Path):
+    spec = importlib.util.spec_from_file_location("ref_quantize_weights", ref_root / "models" / "quantize_weights.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main():
+    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    qw = _load_reference_quantizer(ref_root)
+    rng = np.random.default_rng(20240607)
+    out = {}
+
+    # --- numpy quantiser / packer / dequantiser of the reference -----------------------------
+    for bits in (4, 8):
+        for tag, (N, K, G) in {"a": (6, 96, 32), "b": (5, 80, 16)}.items():
+            w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+            cfg = qw.QuantizationConfig(bits=bits, group_size=G, symmetric=True, dtype="float16")
+            qt = qw.quantize_weight_groupwise(w, cfg)
+            zeros = (rng.standard_normal(qt.scales.shape) * 4 + 8).astype(np.float32)
+            key = f"np_q{bits}{tag}"
+            out[f"{key}_w"] = w
+            out[f"{key}_codes"] = np.asarray(qt.packed_weight)
+            out[f"{key}_scales"] = np.asarray(qt.scales)
+            out[f"{key}_G"] = np.int32(G)
+            out[f"{key}_deq_sym"] = qw.dequantize_quantized_weight(qt.packed_weight, qt.scales, None, bits=bits, group_size=G)
+            out[f"{key}_zeros"] = zeros
+            out[f"{key}_deq_zero"] = qw.dequantize_quantized_weight(qt.packed_weight, qt.scales, zeros, bits=bits, group_size=G)
+    codes = rng.integers(0, 16, size=(4, 63), dtype=np.uint8)
+    out["np_pack_codes"] = codes
+    out["np_pack_packed"] = qw._pack_q4_numpy(codes)
+
+    # --- Metal kernel bodies run on the CPU ---------------------------------------------------
+    for bits in (4, 8):
+        M, K, G = 8, 128, 32
+        cols = K // 2 if bits == 4 else K
+        codes = rng.integers(0, 256, size=(M, cols), dtype=np.uint8)
+        scales = rng.standard_normal((M, K // G)).astype(np.float16)
+        zeros = (rng.standard_normal((M, K // G)) * 3 + (8 if bits == 4 else 128)).astype(np.float16)
+        x = rng.standard_normal((2, K)).astype(np.float16)
+        key = f"mtl_q{bits}"
+        out[f"{key}_codes"], out[f"{key}_scales"], out[f"{key}_zeros"], out[f"{key}_x"] = codes, scales, zeros, x
+        out[f"{key}_deq_zero"] = metal_ref.dequant(bits, codes, scales, zeros, G)
+        out[f"{key}_deq_nozero"] = metal_ref.dequant(bits, codes, scales, None, G)
+        out[f"{key}_matvec_zero"] = metal_ref.matvec(bits, x, codes, scales * np.float16(0.01), zeros, G)
+        out[f"{key}_matvec_nozero"] = metal_ref.matvec(bits, x, codes, scales * np.float16(0.01), None, G)
+
+    # paged attention: ragged lengths, shuffled pages, -1 beyond the length, G=32
+    for bits in (4, 8):
+        for tag, (B, Hq, Hkv, D, P, max_blocks, lengths) in {
+            "gqa": (3, 8, 2, 64, 4, 6, [24, 7, 0]),
+            "mqa": (2, 4, 1, 128, 16, 3, [33, 48]),
+            "d16": (1, 4, 4, 16, 4, 4, [13]),
+        }.items():
+            num_pages = B * max_blocks + 3
+            G = 32
+            groups = (D + G - 1) // G
+            cols = (D + 1) // 2 if bits == 4 else D
+            kq = rng.integers(0, 256, size=(num_pages, P, Hkv, cols), dtype=np.uint8)
+            vq = rng.integers(0, 256, size=(num_pages, P, Hkv, cols), dtype=np.uint8)
+            smax = 7 if bits == 4 else 127
+            ks = (np.abs(rng.standard_normal((num_pages, P, Hkv, groups))) * 2.5 / smax + 1e-3).astype(np.float16)
+            vs = (np.abs(rng.standard_normal((num_pages, P, Hkv, groups))) * 2.5 / smax + 1e-3).astype(np.float16)
+            perm = rng.permutation(num_pages).astype(np.int32)
+            bt = np.full((B, max_blocks), -1, dtype=np.int32)
+            cur = 0
+            for b, L in enumerate(lengths):
+                n = (L + P - 1) // P
+                bt[b, :n] = perm[cur:cur + n]
+                cur += n
+            q = rng.standard_normal((B, 1, Hq, D)).astype(np.float16)
+            scale = np.float32(1.0 / np.sqrt(D))
+            o = metal_ref.paged_attention(bits, q, kq, vq, ks, vs, bt, np.asarray(lengths, np.int32),
+                                          (num_pages, P, Hkv, D), G, float(scale))
+            key = f"mtl_attn_q{bits}_{tag}"
+            for name, val in dict(q=q, kq=kq, vq=vq, ks=ks, vs=vs, bt=bt, lengths=np.asarray(lengths, np.int32),
+                                  shape=np.asarray((num_pages, P, Hkv, D), np.int32), out=o).items():
+                out[f"{key}_{name}"] = val
+
+    gate = (rng.standard_normal((3, 50)) * 3).astype(np.float16)
+    up = rng.standard_normal((3, 50)).astype(np.float16)
+    out["mtl_swiglu_gate"], out["mtl_swiglu_up"] = gate, up
+    out["mtl_swiglu_out"] = metal_ref.fused_swiglu(gate, up)
+
+    bt = rng.permutation(64).astype(np.int32).reshape(4, 16)
+    pos = np.asarray([0, 17, 63, 126], dtype=np.int32)
+    out["mtl_btl_table"], out["mtl_btl_pos"] = bt, pos
+    out["mtl_btl_pages"], out["mtl_btl_offsets"] = metal_ref.block_table_lookup(bt, pos, 8)
+
+    dest = Path(__file__).resolve().parent / "hotpath_golden.npz"
+    np.savez_compressed(dest, **out)
+    print(f"wrote {dest} ({dest.stat().st_size} bytes, {len(out)} arrays)")
+
+
+if __name__ == "__main__":
+    main()

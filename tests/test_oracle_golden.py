@@ -1,0 +1,105 @@
+"""Pins the CPU oracle against outputs of code the reference itself ships.
+
+Sources of the fixtures (tests/golden/make_golden.py): the reference's numpy quantiser /
+dequantiser (models/quantize_weights.py) and its Metal kernel bodies compiled as C++.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import elementwise_ops, paged_kv_ops, paged_quantized_kv_ops as pq, quant_ops as oq
+
+
+def t(a):
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_dequant_matches_reference_numpy_dequantizer(golden, bits, tag):
+    key = f"np_q{bits}{tag}"
+    G = int(golden[f"{key}_G"])
+    codes, scales, zeros = t(golden[f"{key}_codes"]), t(golden[f"{key}_scales"]), t(golden[f"{key}_zeros"])
+    fn = oq.reference_dequant_q4 if bits == 4 else oq.reference_dequant_q8
+    sym_zero = torch.full(scales.shape, 8.0 if bits == 4 else 128.0)
+    for z, want in ((sym_zero, golden[f"{key}_deq_sym"]), (zeros, golden[f"{key}_deq_zero"])):
+        for dt in (torch.float16, torch.bfloat16):
+            got = fn(codes, scales, z, group_size=G, out_dtype=dt)
+            # the numpy reference stops at fp32; the MLX path adds one round-to-nearest cast
+            assert torch.equal(got, t(want).to(dt))
+
+
+def test_pack_matches_reference_numpy_packer(golden):
+    codes = t(golden["np_pack_codes"])
+    packed = oq.pack_q4(codes)
+    assert torch.equal(packed, t(golden["np_pack_packed"]))
+    assert torch.equal(oq.unpack_q4_reference(packed, K=codes.shape[1]), codes)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_symmetric_weight_quantizer_fixture_roundtrip(golden, bits):
+    # codes produced by the reference quantiser dequantise to within half a step of the weights
+    key = f"np_q{bits}a"
+    w = golden[f"{key}_w"]
+    deq = golden[f"{key}_deq_sym"]
+    G = int(golden[f"{key}_G"])
+    step = np.repeat(golden[f"{key}_scales"].astype(np.float32), G, axis=1)[:, : w.shape[1]]
+    # half a quantisation step, plus the fp16 rounding of the stored scale times the largest code
+    assert np.all(np.abs(deq - w) <= 0.5 * step + 128 * step * 2.0 ** -11 + 1e-7)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_dequant_matches_metal_kernel_body(golden, bits):
+    key = f"mtl_q{bits}"
+    codes, scales, zeros = t(golden[f"{key}_codes"]), t(golden[f"{key}_scales"]), t(golden[f"{key}_zeros"])
+    fn = oq.reference_dequant_q4 if bits == 4 else oq.reference_dequant_q8
+    assert torch.equal(fn(codes, scales, zeros, group_size=32), t(golden[f"{key}_deq_zero"]))
+    assert torch.equal(fn(codes, scales, None, group_size=32), t(golden[f"{key}_deq_nozero"]))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_matvec_matches_metal_kernel_body(golden, bits):
+    # The Metal kernel keeps W in fp32 and sums serially; the MLX path rounds W to fp16 first.
+    # They agree to fp16 weight-rounding error, which is what this bound states.
+    key = f"mtl_q{bits}"
+    codes, zeros, x = t(golden[f"{key}_codes"]), t(golden[f"{key}_zeros"]), t(golden[f"{key}_x"])
+    scales = t(golden[f"{key}_scales"]) * 0.01
+    fn = oq.reference_q4_matvec_decode if bits == 4 else oq.reference_q8_matvec_decode
+    for z, want in ((zeros, golden[f"{key}_matvec_zero"]), (None, golden[f"{key}_matvec_nozero"])):
+        got = fn(x, codes, scales, z, group_size=32).float()
+        want = t(want).float()
+        assert float((got - want).norm() / want.norm()) < 1.5e-3
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("tag", ["gqa", "mqa", "d16"])
+def test_paged_attention_matches_metal_kernel_body(golden, bits, tag):
+    key = f"mtl_attn_q{bits}_{tag}"
+    g = {n: golden[f"{key}_{n}"] for n in ("q", "kq", "vq", "ks", "vs", "bt", "lengths", "shape", "out")}
+    cache = pq.OraclePagedKV(
+        k_pages_q=t(g["kq"]), v_pages_q=t(g["vq"]), k_scales=t(g["ks"]), v_scales=t(g["vs"]),
+        block_table=t(g["bt"]), lengths=t(g["lengths"]), bits=bits, page_size=int(g["shape"][1]),
+        group_size=32, original_page_shape=tuple(int(v) for v in g["shape"]),
+    )
+    got = pq.reference_paged_quantized_kv_gqa_decode_attention(t(g["q"]), cache)
+    # Metal keeps dequantised K/V in fp32 and uses a streaming softmax; the MLX path rounds K/V to fp16.
+    # Bound: 2e-3 absolute, widened by one fp16 ulp where the fixture's outputs exceed 1 in magnitude.
+    want = t(g["out"]).float()
+    assert bool(((got.float() - want).abs() <= 2e-3 + want.abs() * 2.0 ** -10).all())
+    # a sequence of length 0 produces zeros
+    zero_rows = np.nonzero(g["lengths"] == 0)[0]
+    for b in zero_rows:
+        assert float(got[b].abs().max()) == 0.0
+
+
+def test_swiglu_matches_metal_kernel_body(golden):
+    got = elementwise_ops.reference_swiglu(t(golden["mtl_swiglu_gate"]), t(golden["mtl_swiglu_up"]))
+    want = t(golden["mtl_swiglu_out"])
+    # expf implementations differ in the last bit; allow one fp16 ulp
+    assert float((got.float() - want.float()).abs().max()) <= float(want.float().abs().max()) * 2 ** -10
+
+
+def test_block_table_lookup_matches_metal_kernel_body(golden):
+    pages, offsets = paged_kv_ops.reference_block_table_lookup(t(golden["mtl_btl_table"]), t(golden["mtl_btl_pos"]), 8)
+    assert torch.equal(pages, t(golden["mtl_btl_pages"]))
+    assert torch.equal(offsets, t(golden["mtl_btl_offsets"]))
