@@ -1,0 +1,135 @@
+/*
+ * b200q.h -- C ABI of libb200q.so: hand-written sm_100a CUDA kernels for the quantized
+ * single-token decode path (q4/q8 group-wise matvec family, fused gate/up + SwiGLU MLP,
+ * q4/q8 paged-KV GQA decode attention, block-table gather).
+ *
+ * Every entry point is what the matching operator of manishklach/mlx-metal-kernels hands to
+ * `mx.fast.metal_kernel(...)(inputs=..., output_shapes=..., grid=..., threadgroup=...)`: raw
+ * device buffers plus the integers the reference packs into its `meta` array.  The reference
+ * site each one replaces is cited as path:line within that project.
+ *
+ * Conventions
+ *   - all pointers are DEVICE pointers on the current CUDA device; the library never
+ *     allocates, frees or keeps them.  Outputs and workspaces are caller-allocated.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  Calls are
+ *     asynchronous and stream-ordered.
+ *   - dtype codes: B200Q_F16, B200Q_BF16, B200Q_F32.
+ *   - return value: B200Q_OK (0) or a negative B200Q_ERR_* code; nothing aborts or traps.
+ *     Execution errors of an already-launched kernel surface at the caller's next sync.
+ *   - weights: q4 = two codes per byte, low nibble = even k, rows of ceil(K/2) bytes;
+ *     q8 = one byte per code; scales/zeros [rows, ceil(K/group)] row-major.  Dequantisation
+ *     is (code - zero) * scale, or code * scale when zeros is NULL
+ *     (ops/quant_ops.py:205-212).
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { B200Q_F16 = 0, B200Q_BF16 = 1, B200Q_F32 = 2 };
+
+enum {
+    B200Q_OK = 0,
+    B200Q_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, unknown dtype/bits */
+    B200Q_ERR_UNSUPPORTED = -2,  /* shape outside what the kernels implement (e.g. head_dim > 128) */
+    B200Q_ERR_LAUNCH = -3,       /* cudaGetLastError() after the launch was not cudaSuccess */
+    B200Q_ERR_WORKSPACE = -4,    /* workspace pointer NULL or smaller than *_workspace_bytes() */
+    B200Q_ERR_DEVICE_WAIT = -5   /* reported by b200q_device_status(): a bounded device wait gave up */
+};
+
+int b200q_version(void);
+const char* b200q_strerror(int code);
+
+/* Reads (and, if reset != 0, clears) the device-side status word that kernels set when one of
+ * their bounded waits on an mbarrier runs out.  Synchronises `stream`.  0 = no event. */
+int b200q_device_status(int reset, void* stream);
+
+/* Runtime tuning knob (benchmark sweeps; defaults are chosen per shape when unset/0).
+ * Known keys: "gemv.stage_k", "gemv.stages", "gemv.ctas_per_sm", "attn.stages", "attn.ctas_per_sm",
+ * "attn.force_simple" (1 = always use the one-warp-per-head kernel), "no_pdl" (1 = launch without
+ * programmatic dependent launch). */
+int b200q_set_tuning(const char* key, int value);
+
+/* Group-wise dequantisation, bit-exact: out = cast(fp32(code - zero) * scale) with two
+ * separately rounded fp32 operations.  Replaces kernels/dequant_q4.metal, dequant_q8.metal as
+ * launched by dequant_q4 / dequant_q8 (ops/quant_ops.py:215-253, 279-316).
+ * codes [M, ceil(K/2)] (bits=4) or [M, K] (bits=8); zeros may be NULL; out [M, K]. */
+int b200q_dequant(int bits, const uint8_t* codes, const void* scales, const void* zeros, void* out,
+                  int64_t M, int64_t K, int group_size, int scale_dtype, int out_dtype, void* stream);
+
+/* y[b, n] = sum_k x[b, k] * (code[n, k] - zero[n, k/G]) * scale[n, k/G], fp32 accumulation,
+ * saturated to the finite range of act_dtype.  One implementation serves the reference's
+ * `metal`, `metal_parallel` and `metal_tiled` launches of q4/q8_matvec_decode
+ * (ops/quant_ops.py:407-506, 529-631; kernels/q{4,8}_matvec_decode{,_parallel,_tiled}.metal).
+ * If `residual` is not NULL the result is cast(residual + cast(y)), the residual_add that
+ * follows the down projection in quantized_mlp_block (ops/mlp_block_ops.py:360-361;
+ * kernels/residual_add.metal).  x [B, K], y and residual [B, N] in act_dtype. */
+int b200q_qmatvec(int bits, const void* x, const uint8_t* codes, const void* scales, const void* zeros,
+                  const void* residual, void* y, int B, int64_t N, int64_t K, int group_size,
+                  int act_dtype, int scale_dtype, void* stream);
+
+/* Gate and up projections of the same rows in one launch, with the SwiGLU that follows them:
+ * gate = Wg x, up = Wu x (each rounded to act_dtype), act = cast(silu(gate) * up),
+ * silu(g) = g / (1 + exp(-g)).  Any of gate_out / up_out / act_out may be NULL.  Replaces
+ * q4/q8_gate_up_matvec_tiled (ops/quant_ops.py:634-738; kernels/q{4,8}_gate_up_matvec_tiled.metal)
+ * plus fused_swiglu (ops/activation_ops.py:118-153; kernels/fused_swiglu.metal).
+ *
+ * Optional fused prologue (norm_weight != NULL): the rows fed to the projections are
+ * rmsnorm(x + residual_in) as in quantized_mlp_block (ops/mlp_block_ops.py:339-340;
+ * kernels/residual_add.metal, kernels/rms_norm.metal); z_out = cast(x + residual_in) and
+ * normed_out = cast(z * rsqrt(mean(z^2) + eps) * norm_weight) are written when not NULL.
+ * residual_in may be NULL (z = x); norm_weight [K] is read in norm_w_dtype. */
+int b200q_gate_up_swiglu(int bits, const void* x, const uint8_t* gate_codes, const uint8_t* up_codes,
+                         const void* gate_scales, const void* up_scales, const void* gate_zeros,
+                         const void* up_zeros, void* gate_out, void* up_out, void* act_out,
+                         const void* residual_in, const void* norm_weight, int norm_w_dtype, float eps,
+                         void* z_out, void* normed_out, int rows, int64_t N, int64_t K, int group_size,
+                         int act_dtype, int scale_dtype, void* stream);
+
+/* out = cast(silu(gate) * up) on [rows, dim].  Replaces kernels/swiglu.metal and
+ * kernels/fused_swiglu.metal (ops/activation_ops.py:91-153). */
+int b200q_swiglu(const void* gate, const void* up, void* out, int64_t rows, int64_t dim, int dtype, void* stream);
+
+/* out = cast(float(x) + float(residual)).  Replaces kernels/residual_add.metal
+ * (ops/fused_ops.py:155-180). */
+int b200q_residual_add(const void* x, const void* residual, void* out, int64_t n, int dtype, void* stream);
+
+/* z = cast(x + residual) (residual may be NULL: z = x), y = cast(z * rsqrt(mean(z^2) + eps) * w).
+ * z_out may be NULL.  Replaces kernels/rms_norm.metal and kernels/rmsnorm_residual.metal
+ * (ops/norm_ops.py:55-85, ops/fused_ops.py:212-241).  x [rows, D]; weight [D] in w_dtype. */
+int b200q_rmsnorm_residual(const void* x, const void* residual, const void* weight, void* y, void* z_out,
+                           int64_t rows, int64_t D, float eps, int dtype, int w_dtype, void* stream);
+
+/* page_ids[b] = block_table[b, positions[b] / page_size]; offsets[b] = positions[b] % page_size.
+ * Replaces kernels/block_table_lookup.metal (ops/paged_kv_ops.py:155-182). */
+int b200q_block_table_lookup(const int32_t* block_table, const int32_t* positions, int32_t* page_ids,
+                             int32_t* offsets, int B, int max_blocks, int page_size, void* stream);
+
+/* Paged quantized-KV GQA decode attention.  For every (b, hq): hkv = hq / (Hq/Hkv); over the
+ * valid tokens j < min(lengths[b], max_blocks*page_size) whose block-table entry is >= 0,
+ * out = softmax(scale * q . Khat_j) . Vhat_j with Khat = fp16((code - 128|8) * k_scale).
+ * A sequence with no valid token writes zeros.  Replaces
+ * kernels/q{4,8}_paged_gqa_decode_attention.metal as launched by
+ * _metal_q{8,4}_paged_gqa_decode_attention (ops/paged_quantized_kv_ops.py:549-629).
+ *   q, out      [B, Hq, D] in q_dtype (the reference's [B,1,Hq,D])
+ *   k/v codes   [num_pages, page_size, Hkv, D] (bits=8) or [.., ceil(D/2)] (bits=4)
+ *   k/v scales  [num_pages, page_size, Hkv, ceil(D/group)] in scale_dtype
+ *   block_table [B, max_blocks] int32, lengths [B] int32
+ *   workspace   b200q_paged_gqa_workspace_bytes(B, Hq, D) bytes of scratch (split-KV partials)
+ */
+size_t b200q_paged_gqa_workspace_bytes(int B, int Hq, int D);
+int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                           const void* k_scales, const void* v_scales, const int32_t* block_table,
+                           const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
+                           int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages, int max_blocks,
+                           int group_size, float scale, int q_dtype, int scale_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,640 @@
+// Paged quantized-KV GQA decode attention (q4 / q8 symmetric, fp16 scales) for sm_100a.
+//
+//   out[b, hq] = softmax_j( scale * q[b, hq] . Khat[j, hkv] ) . Vhat[j, hkv],  hkv = hq / (Hq/Hkv)
+//   Khat = fp16((code - 8|128) * |k_scale|)   over the valid tokens j of sequence b.
+//
+// Fast kernel (head_dim 128, q in fp16, group size a multiple of 32, <= 16 query heads per kv
+// head):
+//   * the (sequence, page) pairs of the whole batch form one flattened list that is cut into
+//     equal contiguous ranges, one per CTA ("stream-K" over ragged lengths: every CTA streams the
+//     same number of pages whatever the length distribution).  A CTA writes one partial
+//     (max, sum, accumulator) per sequence it touches; a second small kernel merges them.
+//   * a producer warp walks the block table and stages whole pages - every token row of K and V
+//     for ALL kv heads plus their scales - into a ring of shared-memory slots with 1-D bulk
+//     copies (TMA engine) completing on mbarriers.  Row strides in shared memory are padded
+//     (K: = 64 mod 128 bytes, V: = 16 mod 64 bytes) so both read patterns are conflict-free.
+//   * consumer warp w owns kv head w: scores S^T[head, token] = Q K^T on mma.sync.m16n8k16 with
+//     the query heads of the group as the 16 rows and in-register dequantised K as the B operand
+//     (a thread dequantises exactly the 16 bytes it loaded); online softmax in fp32; the
+//     probabilities are already in B-operand layout for O^T[d, head] += V^T P, where V^T is the
+//     A operand built from 8-byte pieces of four token rows with one byte-permute per word pair.
+//     KV bytes are read once per kv head, not once per query head.
+//
+// Everything else (other head dims, bf16 queries, odd group sizes) runs the simple kernel: one
+// warp per (sequence, query head), the reference's streaming-softmax loop.
+#include "common.cuh"
+
+#include <algorithm>
+#include <cmath>
+
+namespace b200q {
+
+B200Q_DEFINE_STATUS_WORD(attn_read_status)
+
+namespace {
+
+constexpr int kAttnConsumerWarps = 8;
+constexpr int kAttnThreads = (kAttnConsumerWarps + 1) * 32;
+constexpr int kAttnMaxStages = 16;
+constexpr int kMaxGrid = 512;             // upper bound on CTAs of the fast kernel (sizes the workspace)
+constexpr int kMaxBatchFast = 2048;       // prefix sums of page counts live in shared memory
+constexpr uint32_t kAttnWaitLimit = 1u << 21;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+    const __half* q;            // [B, Hq, D]
+    const uint8_t* k_codes;
+    const uint8_t* v_codes;
+    const __half* k_scales;
+    const __half* v_scales;
+    const int32_t* block_table; // [B, max_blocks]
+    const int32_t* lengths;     // [B]
+    float* partial;             // [(grid + B)][Hq][D + 2]  (acc[D], max, sum)
+    void* out;                  // [B, Hq, D]
+    int B, Hq, Hkv, D, P, max_blocks, G, Gd, group;
+    int64_t num_pages;
+    float scale;
+    int q_dtype;
+    int bits;
+    int stages;
+    int row_bytes;              // bytes of one token row of codes, all kv heads
+    int k_stride, v_stride;     // padded shared-memory strides of a token row
+    int scale_row_bytes;        // bytes of one token row of scales, all kv heads
+    uint32_t off_meta, off_prefix, off_ring, slot_bytes, off_k, off_v, off_ks, off_vs;
+    int grid;
+};
+
+__device__ __forceinline__ int clamp_len(int len, int cap) { return max(0, min(len, cap)); }
+
+// Prefix sums of per-sequence page counts into shared memory; returns the total.
+__device__ int build_prefix(const AttnParams& p, int* prefix) {
+    // executed by every thread of the CTA up to the final __syncthreads
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int running = 0;
+        for (int b0 = 0; b0 < p.B; b0 += 32) {
+            const int b = b0 + lane;
+            int n = 0;
+            if (b < p.B) n = (clamp_len(p.lengths[b], p.max_blocks * p.P) + p.P - 1) / p.P;
+            int incl = n;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (b < p.B) prefix[b] = running + incl - n;
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) prefix[p.B] = running;
+    }
+    __syncthreads();
+    return prefix[p.B];
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(kAttnThreads, 1) paged_attn_kernel(const __grid_constant__ AttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int D = 128;
+    constexpr int DP = BITS == 4 ? 64 : 128;       // code bytes per head and token
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + kAttnMaxStages;
+    int* meta = reinterpret_cast<int*>(smem + p.off_meta);       // [stages][4]: page id, b, page index in sequence
+    int* prefix = reinterpret_cast<int*>(smem + p.off_prefix);   // [B + 1]
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], (uint32_t)min(p.Hkv, kAttnConsumerWarps));   // one arrival per working warp
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();   // lengths / block table / q may be produced by the previous kernel
+
+    const int total = build_prefix(p, prefix);
+    const int ppc = (total + p.grid - 1) / p.grid;               // pages per CTA
+    const int lo = min(total, (int)blockIdx.x * ppc);
+    const int hi = min(total, lo + ppc);
+    if (lo >= hi) return;
+
+    uint8_t* ring = smem + p.off_ring;
+
+    if (warp == kAttnConsumerWarps) {
+        // ------------------------------- producer ------------------------------------------------
+        int b = 0;
+        bool ok = true;
+        const uint32_t tx_bytes = 2u * p.P * p.row_bytes + 2u * p.P * p.scale_row_bytes;
+        for (int f = lo, it = 0; f < hi; ++f, ++it) {
+            while (f >= prefix[b + 1]) ++b;
+            const int pg = f - prefix[b];
+            const int slot = it % p.stages;
+            if (it >= p.stages) {
+                ok = mbar_wait_bounded(&empty[slot], ((it / p.stages) - 1) & 1, &g_device_status, EV_ATTN_EMPTY_WAIT,
+                                       ok ? kAttnWaitLimit : 64u) && ok;
+            }
+            int page = p.block_table[(int64_t)b * p.max_blocks + pg];
+            if (page < 0 || page >= p.num_pages) page = -1;
+            uint8_t* slotp = ring + (size_t)slot * p.slot_bytes;
+            if (lane == 0) {
+                meta[slot * 4 + 0] = page;
+                meta[slot * 4 + 1] = b;
+                meta[slot * 4 + 2] = pg;
+                meta[slot * 4 + 3] = min(p.P, clamp_len(p.lengths[b], p.max_blocks * p.P) - pg * p.P);
+                if (page >= 0) mbar_arrive_expect_tx(&full[slot], tx_bytes);
+                else mbar_arrive(&full[slot]);
+            }
+            __syncwarp();
+            if (page >= 0) {
+                const uint8_t* ksrc = p.k_codes + (size_t)page * p.P * p.row_bytes;
+                const uint8_t* vsrc = p.v_codes + (size_t)page * p.P * p.row_bytes;
+                for (int i = lane; i < 2 * p.P; i += 32) {
+                    const int r = i < p.P ? i : i - p.P;
+                    if (i < p.P) bulk_g2s(slotp + p.off_k + (size_t)r * p.k_stride, ksrc + (size_t)r * p.row_bytes, p.row_bytes, &full[slot]);
+                    else bulk_g2s(slotp + p.off_v + (size_t)r * p.v_stride, vsrc + (size_t)r * p.row_bytes, p.row_bytes, &full[slot]);
+                }
+                if (lane == 0) {
+                    const uint32_t sb = p.P * p.scale_row_bytes;
+                    bulk_g2s(slotp + p.off_ks, reinterpret_cast<const uint8_t*>(p.k_scales) + (size_t)page * sb, sb, &full[slot]);
+                    bulk_g2s(slotp + p.off_vs, reinterpret_cast<const uint8_t*>(p.v_scales) + (size_t)page * sb, sb, &full[slot]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ----------------------------------- consumers ------------------------------------------------
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int group = p.group;
+    const float sm_scale = p.scale;
+    bool ok = true;
+
+    for (int h = warp; h < p.Hkv; h += kAttnConsumerWarps) {
+        // The ring is walked once per kv head handled by this warp; with Hkv <= 8 that is once.
+        // (Hkv > 8 is routed to the simple kernel by the host, see fast_ok().)
+        uint32_t qa[8][4];          // Q as A operand: [mma][a0a1 (row g), a2a3 (row g+8), a4a5, a6a7]
+        float o[8][4];              // O^T tiles: rows d, cols heads
+        float m_run = -INFINITY;    // running max / sum of query head g of the group
+        float l_run = 0.0f;
+        int cur_b = -1;
+
+        auto flush = [&](int b) {
+            // partial slot: (cta + b), see merge kernel
+            float* dst = p.partial + ((size_t)(blockIdx.x + b) * p.Hq) * (D + 2);
+            // reduce l over the quad
+            float l0 = l_run;
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+            // O^T[d][head]: thread (g,t) holds d = 16g + 2i (+1), heads 2t, 2t+1
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int head = 2 * t + (e & 1);
+                    const int d = 16 * g + 2 * i + (e >> 1);
+                    if (head < group) dst[(size_t)(h * group + head) * (D + 2) + d] = o[i][e];
+                }
+            }
+            if (t == 0 && g < group) {
+                dst[(size_t)(h * group + g) * (D + 2) + D] = m_run;
+                dst[(size_t)(h * group + g) * (D + 2) + D + 1] = l0;
+            }
+        };
+
+        for (int f = lo, it = 0; f < hi; ++f, ++it) {
+            const int slot = it % p.stages;
+            ok = mbar_wait_bounded(&full[slot], (it / p.stages) & 1, &g_device_status, EV_ATTN_FULL_WAIT,
+                                   ok ? kAttnWaitLimit : 64u) && ok;
+            const int page = meta[slot * 4 + 0];
+            const int b = meta[slot * 4 + 1];
+            const int valid = meta[slot * 4 + 3];    // tokens of this page that exist
+            if (b != cur_b) {
+                if (cur_b >= 0) flush(cur_b);
+                cur_b = b;
+                m_run = -INFINITY;
+                l_run = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
+                // Q fragments for (b, kv head h): row r of the tile is query head h*group + r
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int r = g + 8 * half;
+                        uint4 u = make_uint4(0, 0, 0, 0);
+                        int d0;
+                        if (BITS == 4) d0 = 32 * t + 8 * c;
+                        else d0 = (c < 2 ? 16 * t + 8 * c : 64 + 16 * t + 8 * (c - 2));
+                        if (r < group)   // group <= 8: rows 8..15 of the tile stay zero
+                            u = *reinterpret_cast<const uint4*>(p.q + ((size_t)b * p.Hq + h * group + r) * D + d0);
+                        const uint32_t w[4] = {u.x, u.y, u.z, u.w};   // halves d0..d0+7
+                        if (BITS == 4) {
+                            // mma 2c: pairs (0,4) (1,5); mma 2c+1: pairs (2,6) (3,7)
+                            const uint32_t p04 = prmt(w[0], w[2], 0x5410), p15 = prmt(w[0], w[2], 0x7632);
+                            const uint32_t p26 = prmt(w[1], w[3], 0x5410), p37 = prmt(w[1], w[3], 0x7632);
+                            qa[2 * c][half] = p04;     qa[2 * c][2 + half] = p15;
+                            qa[2 * c + 1][half] = p26; qa[2 * c + 1][2 + half] = p37;
+                        } else {
+                            // mma 2c: codes 0..3 -> pairs (0,1) (2,3); mma 2c+1: codes 4..7
+                            qa[2 * c][half] = w[0];     qa[2 * c][2 + half] = w[1];
+                            qa[2 * c + 1][half] = w[2]; qa[2 * c + 1][2 + half] = w[3];
+                        }
+                    }
+                }
+            }
+            if (page >= 0) {
+                const uint8_t* slotp = ring + (size_t)slot * p.slot_bytes;
+
+                // ---------------- S^T = Q K^T : two n-tiles (tokens g and g + 8) ------------------
+                float s[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+                    const int tok = g + 8 * nt;
+                    const uint8_t* krow = slotp + p.off_k + (size_t)tok * p.k_stride + h * DP;
+                    const __half* ksc = reinterpret_cast<const __half*>(slotp + p.off_ks + (size_t)tok * p.scale_row_bytes) + h * p.Gd;
+                    if (BITS == 4) {
+                        const uint4 u = *reinterpret_cast<const uint4*>(krow + 16 * t);
+                        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                        const uint32_t s2 = half_dup(__habs(ksc[(32 * t) / p.G]));
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint32_t w2 = w[c] >> 8;
+                            // exact (code - 8), then one rounding in the multiply: fp16((code-8)*s)
+                            const uint32_t v0 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                            const uint32_t v1 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                            const uint32_t v2 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                            const uint32_t v3 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                            mma_m16n8k16(s[nt], qa[2 * c][0], qa[2 * c][1], qa[2 * c][2], qa[2 * c][3], v0, v1);
+                            mma_m16n8k16(s[nt], qa[2 * c + 1][0], qa[2 * c + 1][1], qa[2 * c + 1][2], qa[2 * c + 1][3], v2, v3);
+                        }
+                    } else {
+#pragma unroll
+                        for (int hb = 0; hb < 2; ++hb) {
+                            const uint4 u = *reinterpret_cast<const uint4*>(krow + 64 * hb + 16 * t);
+                            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                            const uint32_t s2 = half_dup(__habs(ksc[(64 * hb + 16 * t) / p.G]));
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const uint32_t v0 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4140u), 0x64806480u), s2);
+                                const uint32_t v1 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4342u), 0x64806480u), s2);
+                                const int mi = 4 * hb + c;
+                                mma_m16n8k16(s[nt], qa[mi][0], qa[mi][1], qa[mi][2], qa[mi][3], v0, v1);
+                            }
+                        }
+                    }
+                }
+                // ---------------- online softmax (row g = query head g of the group; rows 8..15 are padding) ----
+                float pr[2][2];
+                float alpha;
+                {
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int tok = 8 * nt + 2 * t + e;
+                            float v = s[nt][e] * sm_scale;
+                            if (tok >= valid) v = -INFINITY;
+                            s[nt][e] = v;
+                            mx = fmaxf(mx, v);
+                        }
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float m_new = fmaxf(m_run, mx);          // finite: every staged page has a valid token
+                    alpha = exp2f((m_run - m_new) * kLog2e);       // exp(-inf) = 0 on the first page
+                    float lsum = 0.0f;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float pv = exp2f((s[nt][e] - m_new) * kLog2e);
+                            pr[nt][e] = pv;
+                            lsum += pv;
+                        }
+                    l_run = l_run * alpha + lsum;
+                    m_run = m_new;
+                }
+                // ---------------- rescale O^T columns (heads 2t, 2t+1); alpha of head r lives in lanes g == r ----
+                {
+                    const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * t);
+                    const float a1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
+                    if (__any_sync(0xffffffffu, (a0 != 1.0f) || (a1 != 1.0f))) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            o[i][0] *= a0; o[i][1] *= a1; o[i][2] *= a0; o[i][3] *= a1;
+                        }
+                    }
+                }
+                // ---------------- O^T += V^T P ---------------------------------------------------------
+                // B operand: P[token][head]: b0b1 = tokens 2t,2t+1 ; b2b3 = tokens 2t+8,2t+9 ; column = head g
+                uint32_t pb0, pb1;
+                {
+                    const __half2 x0 = __floats2half2_rn(pr[0][0], pr[0][1]);   // tokens 2t, 2t+1
+                    const __half2 x1 = __floats2half2_rn(pr[1][0], pr[1][1]);   // tokens 2t+8, 2t+9
+                    pb0 = *reinterpret_cast<const uint32_t*>(&x0);
+                    pb1 = *reinterpret_cast<const uint32_t*>(&x1);
+                }
+                const __half* vsc = reinterpret_cast<const __half*>(slotp + p.off_vs) + h * p.Gd + (16 * g) / p.G;
+                const int srow = p.scale_row_bytes / 2;   // halves per token row of scales
+                uint32_t vreg[2][16];   // [token pair][j]: (Vhat[tokA][16g + j], Vhat[tokB][16g + j])
+#pragma unroll
+                for (int tp = 0; tp < 2; ++tp) {
+                    const int tokA = 2 * t + 8 * tp, tokB = tokA + 1;
+                    const uint8_t* ra = slotp + p.off_v + (size_t)tokA * p.v_stride + h * DP;
+                    const uint8_t* rbp = ra + p.v_stride;
+                    // slots past the end of the sequence may hold anything: their weight is 0, make the value 0 too
+                    const __half sA = tokA < valid ? __habs(vsc[(size_t)tokA * srow]) : __ushort_as_half(0);
+                    const __half sB = tokB < valid ? __habs(vsc[(size_t)tokB * srow]) : __ushort_as_half(0);
+                    const uint32_t s2 = (uint32_t)__half_as_ushort(sA) | ((uint32_t)__half_as_ushort(sB) << 16);
+                    if (BITS == 4) {
+                        const uint2 ua = *reinterpret_cast<const uint2*>(ra + 8 * g);
+                        const uint2 ub = *reinterpret_cast<const uint2*>(rbp + 8 * g);
+                        const uint32_t wa[2] = {ua.x, ua.y}, wb[2] = {ub.x, ub.y};
+#pragma unroll
+                        for (int w = 0; w < 2; ++w) {
+                            const uint32_t r0 = prmt(wa[w], wb[w], 0x5410);   // nibbles 0..3 of A | of B
+                            const uint32_t r1 = prmt(wa[w], wb[w], 0x7632);   // nibbles 4..7
+                            const uint32_t r0s = r0 >> 8, r1s = r1 >> 8;
+                            vreg[tp][8 * w + 0] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                            vreg[tp][8 * w + 1] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                            vreg[tp][8 * w + 2] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                            vreg[tp][8 * w + 3] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                            vreg[tp][8 * w + 4] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                            vreg[tp][8 * w + 5] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                            vreg[tp][8 * w + 6] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                            vreg[tp][8 * w + 7] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                        }
+                    } else {
+                        const uint4 ua = *reinterpret_cast<const uint4*>(ra + 16 * g);
+                        const uint4 ub = *reinterpret_cast<const uint4*>(rbp + 16 * g);
+                        const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            const uint32_t e = prmt(wa[w], wb[w], 0x5140);   // A.b0 B.b0 A.b1 B.b1
+                            const uint32_t f2 = prmt(wa[w], wb[w], 0x7362);  // A.b2 B.b2 A.b3 B.b3
+                            vreg[tp][4 * w + 0] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4140u), 0x64806480u), s2);
+                            vreg[tp][4 * w + 1] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4342u), 0x64806480u), s2);
+                            vreg[tp][4 * w + 2] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4140u), 0x64806480u), s2);
+                            vreg[tp][4 * w + 3] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4342u), 0x64806480u), s2);
+                        }
+                    }
+                }
+                // tile i: row g <-> d = 16g + 2i, row g+8 <-> d = 16g + 2i + 1
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    mma_m16n8k16(o[i], vreg[0][2 * i], vreg[0][2 * i + 1], vreg[1][2 * i], vreg[1][2 * i + 1], pb0, pb1);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+        if (cur_b >= 0) flush(cur_b);
+    }
+}
+
+// Merges the partials of every (sequence, query head): one warp each, lanes over d.
+__global__ void __launch_bounds__(128) paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    int* prefix = reinterpret_cast<int*>(smem);
+    pdl_wait();
+    const int total = build_prefix(p, prefix);
+    const int D = p.D;
+    const int ppc = (total + p.grid - 1) / p.grid;
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= p.B * p.Hq) return;
+    const int b = item / p.Hq;
+    const int hq = item - b * p.Hq;
+    const int s_lo = prefix[b], s_hi = prefix[b + 1];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float l_tot = 0.0f;
+    if (s_hi > s_lo) {
+        const int c_first = s_lo / ppc, c_last = (s_hi - 1) / ppc;
+        float m_tot = -INFINITY;
+        for (int c = c_first; c <= c_last; ++c)
+            m_tot = fmaxf(m_tot, p.partial[((size_t)(c + b) * p.Hq + hq) * (D + 2) + D]);
+        for (int c = c_first; c <= c_last; ++c) {
+            const float* src = p.partial + ((size_t)(c + b) * p.Hq + hq) * (D + 2);
+            const float m = src[D];
+            const float w = (m == -INFINITY) ? 0.0f : exp2f((m - m_tot) * kLog2e);
+            l_tot += w * src[D + 1];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int d = lane + 32 * j;
+                if (d < D) acc[j] = fmaf(w, src[d], acc[j]);
+            }
+        }
+    }
+    const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) {
+            const size_t o = ((size_t)b * p.Hq + hq) * D + d;
+            if (p.q_dtype == B200Q_F16) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(acc[j] * inv);
+            else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(acc[j] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Simple kernel: one warp per (b, hq); any D <= 128, any group size, fp16/bf16 q, any scale dtype.
+// ------------------------------------------------------------------------------------------------
+struct SimpleParams {
+    const void* q; const uint8_t* k_codes; const uint8_t* v_codes; const void* k_scales; const void* v_scales;
+    const int32_t* block_table; const int32_t* lengths; void* out;
+    int B, Hq, Hkv, D, P, max_blocks, G, Gd, bits, q_dtype, scale_dtype;
+    int64_t num_pages;
+    float scale;
+};
+
+__global__ void __launch_bounds__(128) paged_attn_simple_kernel(const __grid_constant__ SimpleParams p) {
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= p.B * p.Hq) return;
+    const int b = item / p.Hq;
+    const int hq = item - b * p.Hq;
+    const int hkv = hq / (p.Hq / p.Hkv);
+    const int DPk = p.bits == 4 ? (p.D + 1) / 2 : p.D;
+    const int L = clamp_len(p.lengths[b], p.max_blocks * p.P);
+    float qv[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int d = lane + 32 * j;
+        qv[j] = d < p.D ? load_as_f32(p.q, p.q_dtype, ((int64_t)b * p.Hq + hq) * p.D + d) : 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    const float off = p.bits == 4 ? 8.0f : 128.0f;
+    for (int j = 0; j < L; ++j) {
+        const int page = p.block_table[(int64_t)b * p.max_blocks + j / p.P];
+        if (page < 0 || page >= p.num_pages) continue;
+        const int64_t tok = ((int64_t)page * p.P + (j % p.P)) * p.Hkv + hkv;
+        float kd[4], vd[4], dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int d = lane + 32 * i;
+            kd[i] = vd[i] = 0.0f;
+            if (d < p.D) {
+                uint32_t kc, vc;
+                if (p.bits == 4) {
+                    const uint8_t kb = p.k_codes[tok * DPk + (d >> 1)], vb = p.v_codes[tok * DPk + (d >> 1)];
+                    kc = (d & 1) ? (kb >> 4) : (kb & 0xF);
+                    vc = (d & 1) ? (vb >> 4) : (vb & 0xF);
+                } else {
+                    kc = p.k_codes[tok * DPk + d];
+                    vc = p.v_codes[tok * DPk + d];
+                }
+                const float ks = fabsf(load_as_f32(p.k_scales, p.scale_dtype, tok * p.Gd + d / p.G));
+                const float vs = fabsf(load_as_f32(p.v_scales, p.scale_dtype, tok * p.Gd + d / p.G));
+                kd[i] = __half2float(__float2half_rn(__fmul_rn((float)kc - off, ks)));
+                vd[i] = __half2float(__float2half_rn(__fmul_rn((float)vc - off, vs)));
+                dot = fmaf(qv[i], kd[i], dot);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float sc = dot * p.scale;
+        const float m_new = fmaxf(m, sc);
+        const float alpha = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+        const float beta = expf(sc - m_new);
+        l = l * alpha + beta;
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = acc[i] * alpha + beta * vd[i];
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int d = lane + 32 * i;
+        if (d < p.D) {
+            const int64_t o = ((int64_t)b * p.Hq + hq) * p.D + d;
+            if (p.q_dtype == B200Q_F16) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(acc[i] * inv);
+            else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(acc[i] * inv);
+        }
+    }
+}
+
+inline uint32_t align_up_u32(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+inline int pad_stride(int bytes, int mod, int rem) {
+    // smallest stride >= bytes with stride % mod == rem and stride % 16 == 0
+    int s = (bytes + 15) / 16 * 16;
+    while (s % mod != rem) s += 16;
+    return s;
+}
+
+}  // namespace
+
+size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int D) {
+    if (B <= 0 || Hq <= 0 || D <= 0) return 0;
+    return (size_t)(kMaxGrid + B) * Hq * (D + 2) * sizeof(float);
+}
+
+int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes, const void* k_scales,
+                          const void* v_scales, const int32_t* block_table, const int32_t* lengths, void* out,
+                          void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size,
+                          int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                          int scale_dtype, cudaStream_t stream) {
+    if ((bits != 4 && bits != 8) || q == nullptr || k_codes == nullptr || v_codes == nullptr || k_scales == nullptr ||
+        v_scales == nullptr || block_table == nullptr || lengths == nullptr || out == nullptr)
+        return B200Q_ERR_BAD_ARG;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
+        group_size <= 0 || Hq % Hkv != 0 || !is_act_dtype(q_dtype) || !is_scale_dtype(scale_dtype))
+        return B200Q_ERR_BAD_ARG;
+    if (D > 128) return B200Q_ERR_UNSUPPORTED;
+    const int Gd = (D + group_size - 1) / group_size;
+    const int group = Hq / Hkv;
+    const int dp = bits == 4 ? D / 2 : D;
+
+    const bool fast_ok = tuning_get("attn.force_simple") == 0 && D == 128 && q_dtype == B200Q_F16 &&
+                         scale_dtype == B200Q_F16 && group_size % 32 == 0 && D % group_size == 0 && group <= 8 &&
+                         Hkv <= kAttnConsumerWarps && page_size == 16 && B <= kMaxBatchFast &&
+                         ((uintptr_t)q % 16 == 0) && ((uintptr_t)k_codes % 16 == 0) && ((uintptr_t)v_codes % 16 == 0) &&
+                         ((uintptr_t)k_scales % 16 == 0) && ((uintptr_t)v_scales % 16 == 0) &&
+                         ((Hkv * dp) % 16 == 0) && ((page_size * Hkv * Gd * 2) % 16 == 0);
+    if (!fast_ok) {
+        SimpleParams sp = {q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out,
+                           B, Hq, Hkv, D, page_size, max_blocks, group_size, Gd, bits, q_dtype, scale_dtype,
+                           num_pages, scale};
+        const int warps = 4;
+        paged_attn_simple_kernel<<<(B * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(sp);
+        return finish_launch();
+    }
+    if (workspace == nullptr || workspace_bytes < paged_gqa_workspace_bytes_impl(B, Hq, D)) return B200Q_ERR_WORKSPACE;
+
+    AttnParams p = {};
+    p.q = (const __half*)q; p.k_codes = k_codes; p.v_codes = v_codes;
+    p.k_scales = (const __half*)k_scales; p.v_scales = (const __half*)v_scales;
+    p.block_table = block_table; p.lengths = lengths; p.partial = (float*)workspace; p.out = out;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.P = page_size; p.max_blocks = max_blocks; p.G = group_size; p.Gd = Gd;
+    p.group = group; p.num_pages = num_pages; p.scale = scale; p.q_dtype = q_dtype; p.bits = bits;
+    p.row_bytes = Hkv * dp;
+    p.k_stride = pad_stride(p.row_bytes, 128, 64);
+    p.v_stride = pad_stride(p.row_bytes, 64, 16);
+    p.scale_row_bytes = Hkv * Gd * 2;
+
+    uint32_t off = 2 * kAttnMaxStages * sizeof(uint64_t);
+    p.off_meta = off; off += kAttnMaxStages * 4 * sizeof(int);
+    p.off_prefix = off; off += align_up_u32((B + 1) * sizeof(int), 16);
+    off = align_up_u32(off, 128);
+    p.off_ring = off;
+    uint32_t so = 0;
+    p.off_k = so; so += align_up_u32(page_size * p.k_stride, 128);
+    p.off_v = so; so += align_up_u32(page_size * p.v_stride, 128);
+    p.off_ks = so; so += align_up_u32(page_size * p.scale_row_bytes, 128);
+    p.off_vs = so; so += align_up_u32(page_size * p.scale_row_bytes, 128);
+    p.slot_bytes = so;
+    int stages = tuning_get("attn.stages");
+    if (stages <= 0) stages = 8;
+    stages = std::min(stages, kAttnMaxStages);
+    const uint32_t cap = (uint32_t)max_smem_optin();
+    while (stages > 2 && off + (uint64_t)stages * p.slot_bytes > cap) --stages;
+    if (off + (uint64_t)stages * p.slot_bytes > cap) return B200Q_ERR_UNSUPPORTED;
+    p.stages = stages;
+    const uint32_t total_smem = off + stages * p.slot_bytes;
+
+    int ctas_per_sm = tuning_get("attn.ctas_per_sm");
+    if (ctas_per_sm <= 0) ctas_per_sm = 1;
+    p.grid = std::min(kMaxGrid, sm_count() * ctas_per_sm);
+
+    auto kernel = bits == 4 ? paged_attn_kernel<4> : paged_attn_kernel<8>;
+    static bool configured[2][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[bits == 4][dev & 63]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap) != cudaSuccess)
+            return B200Q_ERR_LAUNCH;
+        configured[bits == 4][dev & 63] = true;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(p.grid);
+        cfg.blockDim = dim3(kAttnThreads);
+        cfg.dynamicSmemBytes = total_smem;
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = tuning_get("no_pdl") ? 0 : 1;
+        if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200Q_ERR_LAUNCH;
+    }
+    {
+        const int warps = 4;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((B * Hq + warps - 1) / warps);
+        cfg.blockDim = dim3(warps * 32);
+        cfg.dynamicSmemBytes = align_up_u32((B + 1) * sizeof(int), 16);
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = tuning_get("no_pdl") ? 0 : 1;
+        if (cudaLaunchKernelEx(&cfg, paged_attn_merge_kernel, p) != cudaSuccess) return B200Q_ERR_LAUNCH;
+    }
+    return finish_launch();
+}
+
+}  // namespace b200q

@@ -1,0 +1,162 @@
+"""GPU parity: gate/up fused launch, quantized_linear, SwiGLU / RMSNorm / residual kernels and the
+full quantized MLP block against the CPU oracle (rel-L2 <= 1e-3, fp16, fp32 accumulation)."""
+import pytest
+import torch
+
+from helpers import act_ops, cabi, fused_ops, mlp_ops, norm_ops, quant_ops, random_quant_case, rel_l2, synth, to_dev
+from oracle import elementwise_ops as oe, mlp_block_ops as om, quant_ops as oq
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+TOL_BF16_TC = 6e-3
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("shape,N,G,zeros,dtype", [
+    ((1, 1, 64), 128, 32, None, torch.float16),        # tests/test_gate_up_matvec_tiled.py shapes
+    ((2, 4, 64), 128, 32, "float", torch.float16),
+    ((1, 3, 96), 50, 32, "float", torch.float16),
+    ((2, 4, 64), 50, 32, None, torch.bfloat16),
+    ((3, 256), 130, 64, "float", torch.float16),       # tensor-core path, N not a multiple of 16
+    ((2, 5, 512), 300, 128, "float", torch.float16),   # 10 rows -> two batch tiles
+])
+def test_gate_up_matvec_parity(cuda, bits, shape, N, G, zeros, dtype):
+    K = shape[-1]
+    gw, gs, gz = random_quant_case(bits, N, K, G, 21, zeros=zeros, scale_kind="uniform")
+    uw, us, uz = random_quant_case(bits, N, K, G, 22, zeros=zeros, scale_kind="uniform")
+    x = torch.randn(shape, generator=torch.Generator().manual_seed(23)).to(dtype)
+    wg, wu = oq.reference_gate_up_matvec(x, gw, uw, gs, us, gz, uz, bits=bits, group_size=G)
+    fn = quant_ops.q4_gate_up_matvec_tiled if bits == 4 else quant_ops.q8_gate_up_matvec_tiled
+    gg, gu = fn(*to_dev(cuda, x, gw, uw, gs, us, gz, uz), group_size=G)
+    assert gg.shape == wg.shape and gu.shape == wu.shape
+    fast = K % (128 if bits == 4 else 64) == 0
+    tol = TOL if dtype == torch.float16 or not fast else TOL_BF16_TC
+    assert rel_l2(gg, wg) <= tol and rel_l2(gu, wu) <= tol
+    # the projection wrapper takes weights and scales interleaved per projection
+    dz = lambda t: None if t is None else t.to(cuda)
+    pg, pu = mlp_ops.quantized_gate_up_projection(*to_dev(cuda, x, gw, gs, uw, us), gate_zeros=dz(gz), up_zeros=dz(uz),
+                                                  bits=bits, group_size=G, backend="metal_gate_up_tiled")
+    assert torch.equal(pg, gg) and torch.equal(pu, gu)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_quantized_linear_shapes(cuda, bits):
+    w, s, z = random_quant_case(bits, 48, 128, 32, 31, scale_kind="uniform")
+    x = torch.randn(2, 3, 128).to(torch.float16)
+    want = om.reference_quantized_linear(x, w, s, z, bits=bits, group_size=32)
+    got = mlp_ops.quantized_linear(*to_dev(cuda, x, w, s, z), bits=bits, group_size=32, backend="metal_tiled")
+    assert got.shape == (2, 3, 48) and rel_l2(got, want) <= TOL
+    got2 = mlp_ops.quantized_linear(*to_dev(cuda, x[0], w, s, z), bits=bits, group_size=32)
+    assert got2.shape == (3, 48)
+
+
+def test_elementwise_kernels(cuda, golden):
+    import numpy as np
+    g = torch.randn(2, 3, 130).to(torch.float16) * 3
+    u = torch.randn(2, 3, 130).to(torch.float16)
+    want = oe.reference_swiglu(g, u)
+    for got in (act_ops.swiglu(g.to(cuda), u.to(cuda)), act_ops.fused_swiglu(g.to(cuda), u.to(cuda)),
+                act_ops.fused_swiglu(g.reshape(6, 130).to(cuda), u.reshape(6, 130).to(cuda)).reshape(2, 3, 130)):
+        assert float((got.cpu().float() - want.float()).abs().max()) <= float(want.float().abs().max()) * 2 ** -10
+    fix = act_ops.fused_swiglu(torch.from_numpy(np.ascontiguousarray(golden["mtl_swiglu_gate"])).to(cuda),
+                               torch.from_numpy(np.ascontiguousarray(golden["mtl_swiglu_up"])).to(cuda))
+    ref = torch.from_numpy(np.ascontiguousarray(golden["mtl_swiglu_out"])).float()
+    assert float((fix.cpu().float() - ref).abs().max()) <= float(ref.abs().max()) * 2 ** -10
+
+    x = torch.randn(2, 2, 96).to(torch.float16)
+    r = torch.randn(2, 2, 96).to(torch.float16)
+    w = torch.rand(96) + 0.5
+    assert torch.equal(fused_ops.residual_add(x.to(cuda), r.to(cuda)).cpu(), oe.reference_residual_add(x, r))
+    for wt in (w, w.to(torch.float16)):
+        got = norm_ops.rms_norm(x.to(cuda), wt.to(cuda), eps=1e-5)
+        assert rel_l2(got, oe.reference_rms_norm(x, wt, eps=1e-5)) <= 5e-4
+        y, z = fused_ops.rmsnorm_residual(x.to(cuda), r.to(cuda), wt.to(cuda), return_residual=True)
+        wy, wz = oe.reference_rmsnorm_residual(x, r, wt, return_residual=True)
+        assert torch.equal(z.cpu(), wz) and rel_l2(y, wy) <= 5e-4
+
+
+def _mlp_case(bits, B, S, hidden, inter, G, seed, dtype=torch.float16, zeros=None):
+    g = torch.Generator().manual_seed(seed)
+    lo, hi = (0.01, 0.1) if bits == 4 else (0.001, 0.005)      # scale ranges of tests/test_quantized_mlp_block.py
+    def qw(n, k, s):
+        cols = k // 2 if bits == 4 else k
+        codes = torch.randint(0, 256, (n, cols), generator=g, dtype=torch.int32).to(torch.uint8)
+        scales = torch.rand((n, (k + G - 1) // G), generator=g) * (hi - lo) + lo
+        z = None
+        if zeros:
+            z = torch.randn((n, (k + G - 1) // G), generator=g) + (8.0 if bits == 4 else 128.0)
+        return codes, scales, z
+    x = torch.randn((B, S, hidden), generator=g).to(dtype)
+    res = torch.randn((B, S, hidden), generator=g).to(dtype)
+    nw = (torch.rand(hidden, generator=g) + 0.5)
+    return x, res, nw, qw(inter, hidden, 1), qw(inter, hidden, 2), qw(hidden, inter, 3)
+
+
+@pytest.mark.parametrize("bits,B,S,hidden,inter,G,zeros", [
+    (4, 1, 1, 64, 128, 32, False),      # tests/test_quantized_mlp_block.py / _fused_backend.py
+    (8, 1, 1, 64, 128, 32, False),
+    (4, 2, 4, 64, 128, 32, False),
+    (4, 1, 1, 64, 130, 32, False),
+    (4, 2, 2, 256, 512, 64, True),      # tensor-core path
+    (8, 3, 1, 256, 448, 64, True),
+])
+@pytest.mark.parametrize("preset", ["metal", "parallel", "tiled", "fused_experimental", "cuda"])
+def test_mlp_block_presets(cuda, bits, B, S, hidden, inter, G, zeros, preset):
+    x, res, nw, (gw, gs, gz), (uw, us, uz), (dw, ds, dz) = _mlp_case(bits, B, S, hidden, inter, G, 41, zeros=zeros)
+    # zero points centre the symmetric codes so the activations stay O(1)
+    if not zeros:
+        c = 8.0 if bits == 4 else 128.0
+        gz, uz, dz = torch.full_like(gs, c), torch.full_like(us, c), torch.full_like(ds, c)
+    want, wi = om.reference_quantized_mlp_block(x, res, nw, gw, gs, uw, us, dw, ds, gate_zeros=gz, up_zeros=uz,
+                                                down_zeros=dz, bits=bits, group_size=G, return_intermediates=True)
+    d = lambda t: None if t is None else t.to(cuda)
+    got, gi = mlp_ops.quantized_mlp_block(d(x), d(res), d(nw), d(gw), d(gs), d(uw), d(us), d(dw), d(ds),
+                                          gate_zeros=d(gz), up_zeros=d(uz), down_zeros=d(dz), bits=bits, group_size=G,
+                                          backend_preset=preset, return_intermediates=True)
+    assert set(gi) == {"z", "normed", "gate", "up", "mlp", "down"}
+    assert torch.equal(gi["z"].cpu(), wi["z"])
+    for key in ("normed", "gate", "up", "mlp", "down"):
+        assert gi[key].shape == wi[key].shape
+        assert rel_l2(gi[key], wi[key]) <= 2e-3, key      # stage-wise; rounding of the previous stage feeds in
+    assert rel_l2(got, want) <= TOL
+    plain = mlp_ops.quantized_mlp_block(d(x), d(res), d(nw), d(gw), d(gs), d(uw), d(us), d(dw), d(ds),
+                                        gate_zeros=d(gz), up_zeros=d(uz), down_zeros=d(dz), bits=bits, group_size=G,
+                                        backend_preset=preset)
+    assert torch.equal(plain, got)
+
+
+def test_mlp_decode_step_uses_x_as_residual(cuda):
+    x, _, nw, (gw, gs, _), (uw, us, _), (dw, ds, _) = _mlp_case(4, 1, 1, 256, 512, 64, 43)
+    z8 = lambda s: torch.full_like(s, 8.0)
+    want = om.reference_quantized_mlp_block(x, x, nw, gw, gs, uw, us, dw, ds, gate_zeros=z8(gs), up_zeros=z8(us),
+                                            down_zeros=z8(ds), bits=4, group_size=64)
+    d = lambda t: t.to(cuda)
+    got = mlp_ops.quantized_mlp_decode_step(d(x), d(nw), d(gw), d(gs), d(uw), d(us), d(dw), d(ds), gate_zeros=d(z8(gs)),
+                                            up_zeros=d(z8(us)), down_zeros=d(z8(ds)), bits=4, group_size=64,
+                                            backend_preset="parallel")
+    assert rel_l2(got, want) <= TOL
+
+
+@pytest.mark.parametrize("B", [1, 8, 32])
+def test_mlp_block_llama3_8b_shapes(cuda, B):
+    """C3: hidden 4096, intermediate 14336, q4 group 64, affine weights ~N(0,0.02) (seed 1003)."""
+    hidden, inter, G = 4096, 14336, 64
+    gw, gs, gz = synth.quantized_weight(inter, hidden, 4, G, seed=1003)
+    uw, us, uz = synth.quantized_weight(inter, hidden, 4, G, seed=1004)
+    dw, ds, dz = synth.quantized_weight(hidden, inter, 4, G, seed=1005)
+    x = synth.activations((B, 1, hidden), 1006)
+    res = torch.zeros_like(x)
+    nw = torch.ones(hidden, dtype=torch.float16)
+    want, wi = om.reference_quantized_mlp_block(x, res, nw, gw, gs, uw, us, dw, ds, gate_zeros=gz, up_zeros=uz,
+                                                down_zeros=dz, bits=4, group_size=G, return_intermediates=True)
+    d = lambda t: t.to(cuda)
+    args = [d(t) for t in (x, res, nw, gw, gs, uw, us, dw, ds)]
+    kw = dict(gate_zeros=d(gz), up_zeros=d(uz), down_zeros=d(dz), bits=4, group_size=G, backend_preset="fused_experimental")
+    got, gi = mlp_ops.quantized_mlp_block(*args, **kw, return_intermediates=True)
+    assert rel_l2(gi["gate"], wi["gate"]) <= TOL and rel_l2(gi["up"], wi["up"]) <= TOL
+    assert rel_l2(gi["mlp"], wi["mlp"]) <= 2e-3
+    assert rel_l2(gi["down"], wi["down"]) <= 2e-3
+    assert rel_l2(got, want) <= TOL
+    again = mlp_ops.quantized_mlp_block(*args, **kw)
+    assert torch.equal(again, got)
+    assert cabi.device_status() == 0
