@@ -12,8 +12,10 @@
 //     the <= 8 activation rows as the B operand, accumulating in fp32.  The k order inside an
 //     instruction is permuted so that every thread consumes the 16 bytes it loaded; the
 //     activations are staged once per CTA in the matching order.
-//   * the zero-point term  - sum_g scale*zero * (sum_{k in g} x[b,k])  is added in fp32 in the
-//     epilogue, so no precision is lost to offsets inside the tensor-core sum.
+//   * zero points: the integer part rint(zero) is folded into the dequant constant, so the fp16
+//     weight fed to the tensor core is (code - rint(zero)) * scale rounded once; the fractional
+//     part and the rounding error of the constant are added back in fp32 in the epilogue through
+//     per-group sums of the activations.
 //   * warps split K; partial tiles are reduced through shared memory in a fixed order
 //     (bitwise reproducible), then clamp / round / optional residual add or SwiGLU.
 //   * optional prologue: x := rmsnorm(x + residual) recomputed by every CTA from L2.
@@ -214,69 +216,103 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int B = p.B;
 
     uint8_t* xperm = smem + p.off_xperm;
-    float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);        // [Gn][B]
+    float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);        // [2][Gn][B]: even-k / odd-k sums per group
     float* xscale = reinterpret_cast<float*>(smem + p.off_xscale);    // [B]: 2^e ; [B..2B): inv_rms
-    __half* sS = reinterpret_cast<__half*>(smem + p.off_scales);      // [MATS][kRowBlock][Gn]
-    float* corr = reinterpret_cast<float*>(smem + p.off_corr);        // [MATS][kRowBlock][B]
+    uint2* slots = reinterpret_cast<uint2*>(smem + p.off_scales);     // [MATS][kRowBlock][Gn] dequant constants
+    __half* zr16 = reinterpret_cast<__half*>(smem + p.off_corr);      // [MATS][kRowBlock][Gn] integer part of zero
     float* red = reinterpret_cast<float*>(smem + p.off_red);          // [W][MATS][kRowBlock][B]
     const bool has_zero = (p.z[0] != nullptr) || (MATS == 2 && p.z[1] != nullptr);
+    float* xsum_e = xsum;
+    float* xsum_o = xsum + p.Gn * B;
+
+    // Dequant constants of one (row, group): the kernel computes fp16((off + q) * s + c) with
+    // c = fp16(-(off + zr) * s), zr = rint(zero), off = 1024 (even k / q8) or 64 (odd k, q4): the
+    // fused multiply-add rounds (q - zr) * s + e once, where e = c + (off + zr) * s is the (exactly
+    // known) rounding error of c.  e and the fractional part of the zero point go into the fp32
+    // correction term of the epilogue.
+    auto build_slot = [&](int m, int r, int gi, int row) {
+        const float sf = __half2float(__float2half_rn(load_as_f32(p.s[m], p.scale_dtype, (int64_t)row * p.Gn + gi)));
+        float zr = 0.0f, dz = 0.0f;
+        if (p.z[m] != nullptr) {
+            const float z = load_as_f32(p.z[m], p.scale_dtype, (int64_t)row * p.Gn + gi);
+            zr = fminf(fmaxf(rintf(z), -512.0f), 512.0f);
+            dz = z - zr;
+        }
+        const __half s16 = __float2half_rn(sf);
+        const __half c1024 = __float2half_rn(-(1024.0f + zr) * sf);
+        const __half c64 = __float2half_rn(-(64.0f + zr) * sf);
+        uint2 v;
+        v.x = (uint32_t)__half_as_ushort(s16) | ((uint32_t)__half_as_ushort(c1024) << 16);
+        v.y = (uint32_t)__half_as_ushort(c64) | ((uint32_t)__half_as_ushort(__float2half_rn(dz)) << 16);
+        slots[(m * kRowBlock + r) * p.Gn + gi] = v;
+        zr16[(m * kRowBlock + r) * p.Gn + gi] = __float2half_rn(zr);
+    };
+    auto stage_slots = [&](int row0, int rows) {
+        for (int m = 0; m < MATS; ++m)
+            for (int i = ctid; i < rows * p.Gn; i += kConsumerThreads) {
+                const int r = i / p.Gn;
+                build_slot(m, r, i - r * p.Gn, row0 + r);
+            }
+    };
+
+    // Scales and zero points do not depend on the previous kernel either: convert the first row
+    // block's constants before waiting on it.
+    {
+        const int rows0 = min(rb_rows, r_cnt);
+        stage_slots(r_lo, rows0);
+    }
 
     pdl_wait();   // activations (and the output buffers) belong to the previous kernel until here
 
     // per batch row: inv_rms (norm prologue) and the power-of-two that maps bf16 rows into fp16 range
-    for (int b = cw; b < B; b += kConsumerWarps) {
-        float inv = 1.0f;
-        if (p.norm_w != nullptr) {
-            float ss = 0.0f;
-            for (int k = lane * 8; k < p.K; k += 256) {
-                float zv[8];
-                load8_z(p, b, k, zv);
+    const bool need_row_pass = (p.norm_w != nullptr) || (p.act_dtype == B200Q_BF16);
+    if (need_row_pass) {
+        for (int b = cw; b < B; b += kConsumerWarps) {
+            float inv = 1.0f;
+            if (p.norm_w != nullptr) {
+                float ss = 0.0f;
+                for (int k = lane * 8; k < p.K; k += 256) {
+                    float zv[8];
+                    load8_z(p, b, k, zv);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
+                    for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
+                }
+                ss = warp_sum(ss);
+                inv = rsqrtf(ss / (float)p.K + p.eps);
             }
-            ss = warp_sum(ss);
-            inv = rsqrtf(ss / (float)p.K + p.eps);
-        }
-        float sc = 1.0f;
-        if (p.act_dtype == B200Q_BF16) {
-            float mx = 0.0f;
-            for (int k = lane * 8; k < p.K; k += 256) {
-                float v[8];
-                load8_act(p, b, k, inv, false, v);
+            float sc = 1.0f;
+            if (p.act_dtype == B200Q_BF16) {
+                float mx = 0.0f;
+                for (int k = lane * 8; k < p.K; k += 256) {
+                    float v[8];
+                    load8_act(p, b, k, inv, false, v);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
+                    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
+                }
+                mx = warp_max(mx);
+                int ex = 0;
+                if (mx > 0.0f && mx < INFINITY) frexpf(mx, &ex);
+                ex = max(-100, min(114, ex - 14));
+                sc = exp2f((float)ex);
             }
-            mx = warp_max(mx);
-            int ex = 0;
-            if (mx > 0.0f && mx < INFINITY) frexpf(mx, &ex);
-            ex = max(-100, min(114, ex - 14));
-            sc = exp2f((float)ex);
+            if (lane == 0) {
+                xscale[b] = sc;
+                xscale[B + b] = inv;
+            }
         }
-        if (lane == 0) {
-            xscale[b] = sc;
-            xscale[B + b] = inv;
-        }
+        named_bar_sync(1, kConsumerThreads);
     }
-    named_bar_sync(1, kConsumerThreads);
 
     uint32_t it = 0;
     bool ok = true;
     const int n_xc = (p.K + p.xk - 1) / p.xk;
     const int st_per_xc = p.xk / p.kc;
+    const float fmax_act = p.act_dtype == B200Q_F16 ? 65504.0f : 3.3895313892515355e38f;
 
     for (int rb = 0; rb < n_rb; ++rb) {
         const int row0 = r_lo + rb * rb_rows;
         const int rows = min(rb_rows, r_hi - row0);
-
-        // ---- scales of this row block -> shared memory (fp16) ----
-        for (int m = 0; m < MATS; ++m) {
-            for (int i = ctid; i < rows * p.Gn; i += kConsumerThreads) {
-                const int r = i / p.Gn;
-                const int gi = i - r * p.Gn;
-                sS[(m * kRowBlock + r) * p.Gn + gi] =
-                    __float2half_rn(load_as_f32(p.s[m], p.scale_dtype, (int64_t)(row0 + r) * p.Gn + gi));
-            }
-        }
+        if (rb > 0) stage_slots(row0, rows);     // (row block 0 was converted before the wait)
 
         float acc[MATS][kRowTiles][NT][4];
 #pragma unroll
@@ -299,8 +335,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                     const int b = i / chunks;
                     const int kk = (i - b * chunks) * 8;
                     float v[8];
-                    load8_act(p, b, xk0 + kk, xscale[B + b], cta == 0 && rb == 0, v);
-                    const float down = 1.0f / xscale[b];
+                    const float inv = need_row_pass ? xscale[B + b] : 1.0f;
+                    const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
+                    load8_act(p, b, xk0 + kk, inv, cta == 0 && rb == 0, v);
                     __half h[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j] * down);
@@ -325,13 +362,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                 }
                 named_bar_sync(1, kConsumerThreads);
                 if (has_zero && rb == 0) {
-                    // per-group sums of the staged (fp16) activations for the zero-point term
+                    // per-group sums of the staged (fp16) activations for the zero-point term; read again
+                    // only after the reduction barrier at the end of the row block
                     const int g0 = xk0 / p.G;
                     const int gn = xkn / p.G;
                     for (int i = ctid; i < gn * B; i += kConsumerThreads) {
                         const int gi = i / B;
                         const int b = i - gi * B;
-                        float sum = 0.0f;
+                        float se = 0.0f, so = 0.0f;
                         for (int kk = gi * p.G; kk < (gi + 1) * p.G; kk += 8) {
                             const int ksx = kk / KS;
                             const int rem = kk - ksx * KS;
@@ -339,18 +377,25 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                             const int c = (rem - tt * KT) / 8;
                             const uint4 u = *reinterpret_cast<const uint4*>(
                                 xperm + ((size_t)((ksx * CH + c) * B + b) * 4 + tt) * 16);
-                            const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const __half2 h2 = *reinterpret_cast<const __half2*>(&w4[j]);
-                                sum += __low2float(h2) + __high2float(h2);
+                            const __half2 h0 = *reinterpret_cast<const __half2*>(&u.x);
+                            const __half2 h1 = *reinterpret_cast<const __half2*>(&u.y);
+                            const __half2 h2 = *reinterpret_cast<const __half2*>(&u.z);
+                            const __half2 h3 = *reinterpret_cast<const __half2*>(&u.w);
+                            const float a0 = __low2float(h0) + __high2float(h0), a1 = __low2float(h1) + __high2float(h1);
+                            const float a2 = __low2float(h2) + __high2float(h2), a3 = __low2float(h3) + __high2float(h3);
+                            if (BITS == 4) {            // registers 0 and 2 hold even k, 1 and 3 odd k
+                                se += a0 + a2;
+                                so += a1 + a3;
+                            } else {
+                                se += (a0 + a1) + (a2 + a3);
                             }
                         }
-                        xsum[(g0 + gi) * B + b] = sum;
+                        xsum_e[(g0 + gi) * B + b] = se;
+                        xsum_o[(g0 + gi) * B + b] = so;
                     }
                 }
             } else if (xc == 0) {
-                named_bar_sync(1, kConsumerThreads);   // scales of this row block are visible
+                named_bar_sync(1, kConsumerThreads);   // constants of this row block are visible
             }
 
             const int st_begin = xc * st_per_xc;
@@ -386,8 +431,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                                 const uint8_t* pa = stage + (size_t)rowA * p.row_stride + ksl * 64 + t * 16;
                                 const uint4 ua = *reinterpret_cast<const uint4*>(pa);
                                 const uint4 ub = *reinterpret_cast<const uint4*>(pa + 8 * p.row_stride);
-                                const ScaleRegs sa = make_scale_regs(sS[rowA * p.Gn + gi]);
-                                const ScaleRegs sb = make_scale_regs(sS[(rowA + 8) * p.Gn + gi]);
+                                const uint2 ka = slots[rowA * p.Gn + gi];
+                                const uint2 kb = slots[(rowA + 8) * p.Gn + gi];
+                                ScaleRegs sa, sb;
+                                sa.s2 = prmt(ka.x, ka.x, 0x1010); sa.c1024 = prmt(ka.x, ka.x, 0x3232); sa.c64 = prmt(ka.y, ka.y, 0x1010);
+                                sb.s2 = prmt(kb.x, kb.x, 0x1010); sb.c1024 = prmt(kb.x, kb.x, 0x3232); sb.c64 = prmt(kb.y, kb.y, 0x1010);
                                 const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w};
                                 const uint32_t wb[4] = {ub.x, ub.y, ub.z, ub.w};
 #pragma unroll
@@ -448,69 +496,72 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         const int b = nt * 8 + 2 * t + (i & 1);
                         if (b < B) red[((cw * MATS + m) * kRowBlock + r) * B + b] = acc[m][rt][nt][i];
                     }
-        // ---- zero-point term: corr[m][r][b] = sum_g scale*zero * xsum[g][b] (warp per row) ----
-        if (has_zero) {
-            for (int i = cw; i < rows * MATS; i += kConsumerWarps) {
-                const int m = i / rows;
-                const int r = i - m * rows;
-                float part[NT * 8];
-#pragma unroll
-                for (int b = 0; b < NT * 8; ++b) part[b] = 0.0f;
-                if (p.z[m] != nullptr) {
-                    for (int gi = lane; gi < p.Gn; gi += 32) {
-                        const float sz = __half2float(sS[(m * kRowBlock + r) * p.Gn + gi]) *
-                                         load_as_f32(p.z[m], p.scale_dtype, (int64_t)(row0 + r) * p.Gn + gi);
-#pragma unroll
-                        for (int b = 0; b < NT * 8; ++b)
-                            if (b < B) part[b] = fmaf(sz, xsum[gi * B + b], part[b]);
-                    }
-                }
-#pragma unroll
-                for (int b = 0; b < NT * 8; ++b) {
-                    if (b < B) {
-                        const float s = warp_sum(part[b]);
-                        if (lane == 0) corr[(m * kRowBlock + r) * B + b] = s;
-                    }
-                }
-            }
-        }
         named_bar_sync(1, kConsumerThreads);
 
-        // ---- epilogue ----
-        const float fmax_act = p.act_dtype == B200Q_F16 ? 65504.0f : 3.3895313892515355e38f;
-        for (int i = ctid; i < rows * B; i += kConsumerThreads) {
-            const int b = i / rows;
-            const int r = i - b * rows;
+        // ---- epilogue: one warp per output row.  Lanes first split the groups of the row for the
+        //      zero-point term, then lane b finishes batch row b. ----
+        for (int r = cw; r < rows; r += kConsumerWarps) {
             float val[MATS];
 #pragma unroll
             for (int m = 0; m < MATS; ++m) {
-                float s = 0.0f;
+                float mine = 0.0f;       // correction for batch row == lane
+                if (has_zero && p.z[m] != nullptr) {
+                    float part[NT * 8];
 #pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w) s += red[((w * MATS + m) * kRowBlock + r) * B + b];
-                if (has_zero) s -= corr[(m * kRowBlock + r) * B + b];
-                s *= xscale[b];
+                    for (int b = 0; b < NT * 8; ++b) part[b] = 0.0f;
+                    for (int gi = lane; gi < p.Gn; gi += 32) {
+                        const uint2 k = slots[(m * kRowBlock + r) * p.Gn + gi];
+                        const float sf = __half2float(__ushort_as_half((unsigned short)(k.x & 0xFFFF)));
+                        const float c1024 = __half2float(__ushort_as_half((unsigned short)(k.x >> 16)));
+                        const float c64 = __half2float(__ushort_as_half((unsigned short)(k.y & 0xFFFF)));
+                        const float dz = __half2float(__ushort_as_half((unsigned short)(k.y >> 16)));
+                        const float zr = __half2float(zr16[(m * kRowBlock + r) * p.Gn + gi]);
+                        const float base = dz * sf;
+                        const float ke = base + fmaf(1024.0f + zr, sf, c1024);
+                        const float ko = base + fmaf(64.0f + zr, sf, c64);
+#pragma unroll
+                        for (int b = 0; b < NT * 8; ++b)
+                            if (b < B) part[b] = fmaf(ke, xsum_e[gi * B + b], fmaf(ko, xsum_o[gi * B + b], part[b]));
+                    }
+#pragma unroll
+                    for (int b = 0; b < NT * 8; ++b) {
+                        if (b < B) {
+                            const float s = warp_sum(part[b]);
+                            if (lane == b) mine = s;
+                        }
+                    }
+                }
+                float s = 0.0f;
+                if (lane < B) {
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; ++w) s += red[((w * MATS + m) * kRowBlock + r) * B + lane];
+                    s -= mine;
+                    if (need_row_pass) s *= xscale[lane];
+                }
                 val[m] = round_act(fminf(fmaxf(s, -fmax_act), fmax_act), p.act_dtype);
             }
-            const int64_t o = (int64_t)b * p.N + row0 + r;
-            auto store = [&](void* base, float v) {
-                if (p.act_dtype == B200Q_F16) reinterpret_cast<__half*>(base)[o] = __float2half_rn(v);
-                else reinterpret_cast<__nv_bfloat16*>(base)[o] = __float2bfloat16_rn(v);
-            };
-            if (GATE_UP) {
-                if (p.gate_out != nullptr) store(p.gate_out, val[0]);
-                if (p.up_out != nullptr) store(p.up_out, val[MATS - 1]);
-                if (p.act_out != nullptr) {
-                    const float gte = val[0];
-                    const float silu = gte / (1.0f + expf(-gte));
-                    store(p.act_out, silu * val[MATS - 1]);
+            if (lane < B) {
+                const int64_t o = (int64_t)lane * p.N + row0 + r;
+                auto store = [&](void* base, float v) {
+                    if (p.act_dtype == B200Q_F16) reinterpret_cast<__half*>(base)[o] = __float2half_rn(v);
+                    else reinterpret_cast<__nv_bfloat16*>(base)[o] = __float2bfloat16_rn(v);
+                };
+                if (GATE_UP) {
+                    if (p.gate_out != nullptr) store(p.gate_out, val[0]);
+                    if (p.up_out != nullptr) store(p.up_out, val[MATS - 1]);
+                    if (p.act_out != nullptr) {
+                        const float gte = val[0];
+                        const float silu = gte / (1.0f + expf(-gte));
+                        store(p.act_out, silu * val[MATS - 1]);
+                    }
+                } else {
+                    float v = val[0];
+                    if (p.residual != nullptr) v = load_as_f32(p.residual, p.act_dtype, o) + v;
+                    store(p.y, v);
                 }
-            } else {
-                float v = val[0];
-                if (p.residual != nullptr) v = load_as_f32(p.residual, p.act_dtype, o) + v;
-                store(p.y, v);
             }
         }
-        named_bar_sync(1, kConsumerThreads);   // red / corr / scales are reused by the next row block
+        named_bar_sync(1, kConsumerThreads);   // red / constants are reused by the next row block
     }
 }
 
@@ -620,10 +671,10 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     uint32_t off = 2 * kMaxStages * sizeof(uint64_t);
     off = align_up(off, 128);
     p.off_xperm = off;  off += align_up((uint32_t)xk * p.B * 2, 128);
-    p.off_xsum = off;   off += align_up((uint32_t)p.Gn * p.B * 4, 128);
+    p.off_xsum = off;   off += align_up((uint32_t)2 * p.Gn * p.B * 4, 128);
     p.off_xscale = off; off += align_up((uint32_t)p.B * 2 * 4, 128);
-    p.off_scales = off; off += align_up((uint32_t)MATS * kRowBlock * p.Gn * 2, 128);
-    p.off_corr = off;   off += align_up((uint32_t)MATS * kRowBlock * p.B * 4, 128);
+    p.off_scales = off; off += align_up((uint32_t)MATS * kRowBlock * p.Gn * 8, 128);   // dequant constants
+    p.off_corr = off;   off += align_up((uint32_t)MATS * kRowBlock * p.Gn * 2, 128);   // integer zero points
     p.off_red = off;    off += align_up((uint32_t)kConsumerWarps * MATS * kRowBlock * p.B * 4, 128);
     p.off_ring = off;
     const uint32_t smem_cap = (uint32_t)max_smem_optin();
@@ -670,7 +721,7 @@ bool fast_path_ok(const GemvParams& p, int bits) {
     const int kt = ks / 4;
     if (p.K % ks != 0 || p.G % kt != 0 || p.K % p.G != 0 || (ks * kConsumerWarps) % p.G != 0) return false;
     if (p.B > 16) return false;
-    if ((size_t)p.Gn * kRowBlock * 2 * 2 > 48 * 1024) return false;
+    if ((size_t)p.Gn * kRowBlock * 2 * 10 > 96 * 1024) return false;
     if (!aligned16(p.x) || !aligned16(p.w[0]) || (p.w[1] != nullptr && !aligned16(p.w[1]))) return false;
     if (p.res_in != nullptr && !aligned16(p.res_in)) return false;
     if (p.z_out != nullptr && !aligned16(p.z_out)) return false;
