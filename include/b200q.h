@@ -73,6 +73,15 @@ int b200q_qmatvec(int bits, const void* x, const uint8_t* codes, const void* sca
                   const void* residual, void* y, int B, int64_t N, int64_t K, int group_size,
                   int act_dtype, int scale_dtype, void* stream);
 
+/* The same matvec with the RMSNorm (and residual add) that precedes it fused in: the rows fed to the
+ * projection are rmsnorm(x + residual_in) (residual_in may be NULL).  Replaces rms_norm followed by the
+ * QKV matvec of llama_layer_decode_step (ops/llama_layer_ops.py:255-259,
+ * ops/quantized_decode_block_ops.py:113-131).  z_out / normed_out are written when not NULL. */
+int b200q_norm_qmatvec(int bits, const void* x, const void* residual_in, const void* norm_weight, int norm_w_dtype,
+                       float eps, void* z_out, void* normed_out, const uint8_t* codes, const void* scales,
+                       const void* zeros, const void* residual, void* y, int B, int64_t N, int64_t K,
+                       int group_size, int act_dtype, int scale_dtype, void* stream);
+
 /* Gate and up projections of the same rows in one launch, with the SwiGLU that follows them:
  * gate = Wg x, up = Wu x (each rounded to act_dtype), act = cast(silu(gate) * up),
  * silu(g) = g / (1 + exp(-g)).  Any of gate_out / up_out / act_out may be NULL.  Replaces
@@ -120,14 +129,27 @@ int b200q_block_table_lookup(const int32_t* block_table, const int32_t* position
  *   k/v codes   [num_pages, page_size, Hkv, D] (bits=8) or [.., ceil(D/2)] (bits=4)
  *   k/v scales  [num_pages, page_size, Hkv, ceil(D/group)] in scale_dtype
  *   block_table [B, max_blocks] int32, lengths [B] int32
- *   workspace   b200q_paged_gqa_workspace_bytes(B, Hq, D) bytes of scratch (split-KV partials)
+ *   workspace   b200q_paged_gqa_workspace_bytes(B, Hq, Hkv, D) bytes of scratch (split-KV partials)
  */
-size_t b200q_paged_gqa_workspace_bytes(int B, int Hq, int D);
+size_t b200q_paged_gqa_workspace_bytes(int B, int Hq, int Hkv, int D);
 int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
                            const void* k_scales, const void* v_scales, const int32_t* block_table,
                            const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
                            int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages, int max_blocks,
                            int group_size, float scale, int q_dtype, int scale_dtype, void* stream);
+
+/* Decode-layer glue: split a fused QKV row [B, (Hq + 2 Hkv) * D] (fp16), apply the interleaved-pair
+ * rotary embedding at positions[b] to q and k (tables cos/sin [table_len, D/2] fp32, as
+ * reference_apply_rope, ops/rope_ops.py:61-75, after reference_gqa_qkv_split_rope,
+ * ops/gqa_ops.py:148-160), write q_out [B, Hq, D], and append k / v - quantised with the cache rule
+ * of ops/paged_quantized_kv_ops.py:146-175 - to page block_table[b, pos / page_size], slot
+ * pos % page_size.  The reference has no quantised append (its update kernels copy the whole cache,
+ * kernels/paged_kv_cache_update.metal); this is the in-place form the decode stack needs. */
+int b200q_rope_kv_append(const void* qkv, const float* cos_table, const float* sin_table,
+                         const int32_t* positions, const int32_t* block_table, void* q_out, uint8_t* k_codes,
+                         uint8_t* v_codes, void* k_scales, void* v_scales, int bits, int B, int Hq, int Hkv,
+                         int D, int page_size, int64_t num_pages, int max_blocks, int group_size, int table_len,
+                         void* stream);
 
 #ifdef __cplusplus
 }

@@ -49,13 +49,18 @@ int gemv_read_status(int reset, cudaStream_t stream);
 int attn_read_status(int reset, cudaStream_t stream);
 int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scales, const void* zeros,
                  const void* residual, void* y, int B, int64_t N, int64_t K, int group_size, int act_dtype,
-                 int scale_dtype, cudaStream_t stream);
+                 int scale_dtype, const void* residual_in, const void* norm_weight, int norm_w_dtype, float eps,
+                 void* z_out, void* normed_out, cudaStream_t stream);
+int rope_kv_append_impl(const void* qkv, const float* cos_table, const float* sin_table, const int32_t* positions,
+                        const int32_t* block_table, void* q_out, uint8_t* k_codes, uint8_t* v_codes, void* k_scales,
+                        void* v_scales, int bits, int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages,
+                        int max_blocks, int group_size, int table_len, cudaStream_t stream);
 int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8_t* up_codes, const void* gate_scales,
                  const void* up_scales, const void* gate_zeros, const void* up_zeros, void* gate_out, void* up_out,
                  void* act_out, const void* residual_in, const void* norm_weight, float eps, void* z_out,
                  void* normed_out, int rows, int64_t N, int64_t K, int group_size, int act_dtype, int scale_dtype,
                  int norm_w_dtype, cudaStream_t stream);
-size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int D);
+size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int Hkv, int D);
 int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes, const void* k_scales,
                           const void* v_scales, const int32_t* block_table, const int32_t* lengths, void* out,
                           void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size,
@@ -263,7 +268,25 @@ int b200q_qmatvec(int bits, const void* x, const uint8_t* codes, const void* sca
                   const void* residual, void* y, int B, int64_t N, int64_t K, int group_size, int act_dtype,
                   int scale_dtype, void* stream) {
     return qmatvec_impl(bits, x, codes, scales, zeros, residual, y, B, N, K, group_size, act_dtype, scale_dtype,
-                        (cudaStream_t)stream);
+                        nullptr, nullptr, B200Q_F16, 0.0f, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+int b200q_norm_qmatvec(int bits, const void* x, const void* residual_in, const void* norm_weight, int norm_w_dtype,
+                       float eps, void* z_out, void* normed_out, const uint8_t* codes, const void* scales,
+                       const void* zeros, const void* residual, void* y, int B, int64_t N, int64_t K, int group_size,
+                       int act_dtype, int scale_dtype, void* stream) {
+    if (norm_weight == nullptr) return B200Q_ERR_BAD_ARG;
+    return qmatvec_impl(bits, x, codes, scales, zeros, residual, y, B, N, K, group_size, act_dtype, scale_dtype,
+                        residual_in, norm_weight, norm_w_dtype, eps, z_out, normed_out, (cudaStream_t)stream);
+}
+
+int b200q_rope_kv_append(const void* qkv, const float* cos_table, const float* sin_table, const int32_t* positions,
+                         const int32_t* block_table, void* q_out, uint8_t* k_codes, uint8_t* v_codes, void* k_scales,
+                         void* v_scales, int bits, int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages,
+                         int max_blocks, int group_size, int table_len, void* stream) {
+    return rope_kv_append_impl(qkv, cos_table, sin_table, positions, block_table, q_out, k_codes, v_codes, k_scales,
+                               v_scales, bits, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, table_len,
+                               (cudaStream_t)stream);
 }
 
 int b200q_gate_up_swiglu(int bits, const void* x, const uint8_t* gate_codes, const uint8_t* up_codes,
@@ -319,7 +342,7 @@ int b200q_block_table_lookup(const int32_t* block_table, const int32_t* position
     return finish_launch();
 }
 
-size_t b200q_paged_gqa_workspace_bytes(int B, int Hq, int D) { return paged_gqa_workspace_bytes_impl(B, Hq, D); }
+size_t b200q_paged_gqa_workspace_bytes(int B, int Hq, int Hkv, int D) { return paged_gqa_workspace_bytes_impl(B, Hq, Hkv, D); }
 
 int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
                            const void* k_scales, const void* v_scales, const int32_t* block_table,

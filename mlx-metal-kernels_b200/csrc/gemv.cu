@@ -2,21 +2,25 @@
 //
 //   y[b, n] = sum_k x[b, k] * (code[n, k] - zero[n, k/G]) * scale[n, k/G]          b < B <= 16
 //
-// Design (one CTA per SM slot, 8 consumer warps + 1 producer warp):
-//   * output rows are dealt out evenly to the CTAs; a CTA walks its rows in blocks of 32.
-//   * the producer warp streams the block's weight rows through a ring of shared-memory stages
-//     with 1-D bulk copies (TMA engine, one copy per row and k-chunk) signalled on mbarriers.  It
-//     starts before griddepcontrol.wait: weights do not depend on the previous kernel.
-//   * consumers dequantise in registers, fp16(code*scale) via lop3/prmt + one HFMA2 per two
-//     codes, and feed mma.sync.m16n8k16 with the WEIGHTS as the A operand (16 output rows) and
-//     the <= 8 activation rows as the B operand, accumulating in fp32.  The k order inside an
-//     instruction is permuted so that every thread consumes the 16 bytes it loaded; the
-//     activations are staged once per CTA in the matching order.
+// Design (one CTA per SM, 16 consumer warps + 1 producer warp):
+//   * output rows are dealt out evenly to the CTAs; a CTA walks its rows in tiles of 16 (one
+//     tensor-core M tile).
+//   * the producer warp streams each tile through a ring of shared-memory stages with 1-D bulk
+//     copies (TMA engine) signalled on mbarriers: one copy per weight row and k-chunk, sized
+//     about 2 KB because the copy engine needs >= 2 KB per copy to saturate HBM (measured: 512 B
+//     copies top out near 2.2 TB/s, 2 KB copies reach 7.2 TB/s), plus one copy each for the
+//     tile's scales and zero points, which are contiguous over rows.  The producer starts before
+//     griddepcontrol.wait: weights do not depend on the previous kernel.
+//   * consumers dequantise in registers, fp16 via lop3/prmt + one HFMA2 per two codes, and feed
+//     mma.sync.m16n8k16 with the WEIGHTS as the A operand (16 output rows) and the <= 8
+//     activation rows as the B operand, accumulating in fp32.  The k order inside an instruction
+//     is permuted so that every thread consumes the 16 bytes it loaded; the activations are
+//     staged once per CTA in the matching order.
 //   * zero points: the integer part rint(zero) is folded into the dequant constant, so the fp16
 //     weight fed to the tensor core is (code - rint(zero)) * scale rounded once; the fractional
 //     part and the rounding error of the constant are added back in fp32 in the epilogue through
 //     per-group sums of the activations.
-//   * warps split K; partial tiles are reduced through shared memory in a fixed order
+//   * 16 warps split K; partial tiles are reduced through shared memory in a fixed order
 //     (bitwise reproducible), then clamp / round / optional residual add or SwiGLU.
 //   * optional prologue: x := rmsnorm(x + residual) recomputed by every CTA from L2.
 //
@@ -34,14 +38,14 @@ B200Q_DEFINE_STATUS_WORD(gemv_read_status)
 
 namespace {
 
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 16;           // the reduction below assumes 16
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kRowTiles = 2;                  // 16-row MMA tiles per row block
-constexpr int kRowBlock = kRowTiles * 16;
+constexpr int kTileRows = 16;
+constexpr int kMaxBlockTiles = 2;             // tiles whose accumulators stay live across activation chunks
 constexpr int kRowPad = 64;                   // stage row stride = chunk bytes + 64: conflict-free 16-byte reads
 constexpr uint32_t kWaitLimit = 1u << 21;
-constexpr int kMaxStages = 12;
+constexpr int kMaxStages = 8;
 
 struct GemvParams {
     // activations
@@ -65,11 +69,15 @@ struct GemvParams {
     int act_dtype, scale_dtype, norm_w_dtype;
     int row_bytes;          // bytes of one weight row
     int kc;                 // k per ring stage
+    int n_kc;               // stages per (matrix, tile)
     int stages;
     int xk;                 // k per staged activation chunk (multiple of kc)
+    int block_tiles;        // tiles per row block (1 unless the activations need several chunks)
+    int logG;               // group size is a power of two on the fast path
+    int meta_by_tma;        // scales / zeros are fp16 and 16-byte aligned per tile: bulk-copied with the tile
     int rows_lo, rem;       // CTA c owns rows_lo (+1 if c < rem) rows
-    uint32_t off_xperm, off_xsum, off_xscale, off_scales, off_corr, off_red, off_ring;
-    uint32_t stage_bytes, row_stride;
+    uint32_t off_xperm, off_xsum, off_xscale, off_slots, off_red, off_ring;
+    uint32_t stage_bytes, row_stride, stage_meta_off, slots_buf_elems, red_buf_elems;
 };
 
 // ---- activation source: 8 consecutive values of batch row b at k, as the reference would hold them --------
@@ -161,9 +169,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int r_lo = cta * p.rows_lo + min(cta, p.rem);
     const int r_cnt = p.rows_lo + (cta < p.rem ? 1 : 0);
     const int r_hi = r_lo + r_cnt;
-    const int n_rb = (r_cnt + kRowBlock - 1) / kRowBlock;
-    const int rb_rows = n_rb > 0 ? (r_cnt + n_rb - 1) / n_rb : 0;   // balanced row blocks
-    const int n_st = (p.K + p.kc - 1) / p.kc;
+    const int n_tiles = (r_cnt + kTileRows - 1) / kTileRows;
+    const int TB = p.block_tiles;
+    const int n_rb = (n_tiles + TB - 1) / TB;
+    const int n_xc = (p.K + p.xk - 1) / p.xk;
+    const int kc_per_xc = p.xk / p.kc;           // ring stages per (matrix, tile, activation chunk)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -177,31 +187,55 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
     uint8_t* ring = smem + p.off_ring;
 
+    // Both sides walk the stages in the same order: row block, activation chunk, tile, matrix, k-chunk.
     if (warp == kConsumerWarps) {
         // ------------------------------ producer warp ------------------------------------------
-        uint32_t it = 0;
         bool ok = true;
+        int p_slot = 0;
+        uint32_t p_phase = 1;            // first pass over the ring does not wait
+        bool first_pass = true;
         for (int rb = 0; rb < n_rb; ++rb) {
-            const int row0 = r_lo + rb * rb_rows;
-            const int rows = min(rb_rows, r_hi - row0);
-            for (int st = 0; st < n_st; ++st, ++it) {
-                const int slot = it % p.stages;
-                if (it >= (uint32_t)p.stages) {
-                    const uint32_t parity = ((it / p.stages) - 1) & 1;
-                    ok = mbar_wait_bounded(&empty[slot], parity, &g_device_status, EV_GEMV_EMPTY_WAIT,
-                                           ok ? kWaitLimit : 64u) && ok;
-                }
-                const int k0 = st * p.kc;
-                const int kcur = min(p.kc, p.K - k0);
-                const uint32_t bytes_row = (uint32_t)(kcur * BITS / 8);
-                if (lane == 0) mbar_arrive_expect_tx(&full[slot], bytes_row * rows * MATS);
-                __syncwarp();
-                uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-                for (int i = lane; i < rows * MATS; i += 32) {
-                    const int m = i / rows;
-                    const int r = i - m * rows;
-                    const uint8_t* src = p.w[m] + (size_t)(row0 + r) * p.row_bytes + (size_t)k0 * BITS / 8;
-                    bulk_g2s(stage + (size_t)(m * kRowBlock + r) * p.row_stride, src, bytes_row, &full[slot]);
+            for (int xc = 0; xc < n_xc; ++xc) {
+                const int c_begin = xc * kc_per_xc;
+                const int c_end = min(p.n_kc, c_begin + kc_per_xc);
+                for (int tl = rb * TB; tl < min(n_tiles, (rb + 1) * TB); ++tl) {
+                    const int row0 = r_lo + tl * kTileRows;
+                    const int rows = min(kTileRows, r_hi - row0);
+                    for (int m = 0; m < MATS; ++m) {
+                        for (int c = c_begin; c < c_end; ++c) {
+                            const int slot = p_slot;
+                            if (!first_pass)
+                                ok = mbar_wait_bounded(&empty[slot], p_phase, &g_device_status, EV_GEMV_EMPTY_WAIT,
+                                                       ok ? kWaitLimit : 64u) && ok;
+                            if (++p_slot == p.stages) { p_slot = 0; p_phase ^= 1; first_pass = false; }
+                            const int k0 = c * p.kc;
+                            const int kcur = min(p.kc, p.K - k0);
+                            const uint32_t bytes_row = (uint32_t)(kcur * BITS / 8);
+                            const bool with_meta = (c == 0) && p.meta_by_tma;
+                            const uint32_t meta_bytes = (uint32_t)rows * p.Gn * 2;
+                            uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
+                            if (lane == 0) {
+                                uint32_t tx = bytes_row * rows;
+                                if (with_meta) tx += meta_bytes * (p.z[m] != nullptr ? 2 : 1);
+                                mbar_arrive_expect_tx(&full[slot], tx);
+                            }
+                            __syncwarp();
+                            if (lane < rows) {
+                                const uint8_t* src = p.w[m] + (size_t)(row0 + lane) * p.row_bytes + (size_t)k0 * BITS / 8;
+                                bulk_g2s(stage + (size_t)lane * p.row_stride, src, bytes_row, &full[slot]);
+                            }
+                            if (with_meta) {
+                                if (lane == 16)
+                                    bulk_g2s(stage + p.stage_meta_off,
+                                             reinterpret_cast<const uint8_t*>(p.s[m]) + (size_t)row0 * p.Gn * 2, meta_bytes,
+                                             &full[slot]);
+                                if (lane == 17 && p.z[m] != nullptr)
+                                    bulk_g2s(stage + p.stage_meta_off + kTileRows * p.Gn * 2,
+                                             reinterpret_cast<const uint8_t*>(p.z[m]) + (size_t)row0 * p.Gn * 2, meta_bytes,
+                                             &full[slot]);
+                            }
+                        }
+                    }
                 }
             }
         }
@@ -214,53 +248,39 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int g = lane >> 2;
     const int t = lane & 3;
     const int B = p.B;
+    const int Gn = p.Gn;
 
     uint8_t* xperm = smem + p.off_xperm;
-    float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);        // [2][Gn][B]: even-k / odd-k sums per group
+    float* xsum_e = reinterpret_cast<float*>(smem + p.off_xsum);      // [Gn][B] sums over even k (all k for q8)
+    float* xsum_o = xsum_e + Gn * B;                                  // [Gn][B] sums over odd k
     float* xscale = reinterpret_cast<float*>(smem + p.off_xscale);    // [B]: 2^e ; [B..2B): inv_rms
-    uint2* slots = reinterpret_cast<uint2*>(smem + p.off_scales);     // [MATS][kRowBlock][Gn] dequant constants
-    __half* zr16 = reinterpret_cast<__half*>(smem + p.off_corr);      // [MATS][kRowBlock][Gn] integer part of zero
-    float* red = reinterpret_cast<float*>(smem + p.off_red);          // [W][MATS][kRowBlock][B]
+    uint2* slots_base = reinterpret_cast<uint2*>(smem + p.off_slots); // [2][MATS][TB][16][Gn] dequant constants
+    float* red_base = reinterpret_cast<float*>(smem + p.off_red);     // [2]{ red [MATS][TB][16][B][W] ; corr [MATS][TB][16][B] }
     const bool has_zero = (p.z[0] != nullptr) || (MATS == 2 && p.z[1] != nullptr);
-    float* xsum_e = xsum;
-    float* xsum_o = xsum + p.Gn * B;
 
     // Dequant constants of one (row, group): the kernel computes fp16((off + q) * s + c) with
     // c = fp16(-(off + zr) * s), zr = rint(zero), off = 1024 (even k / q8) or 64 (odd k, q4): the
     // fused multiply-add rounds (q - zr) * s + e once, where e = c + (off + zr) * s is the (exactly
     // known) rounding error of c.  e and the fractional part of the zero point go into the fp32
-    // correction term of the epilogue.
-    auto build_slot = [&](int m, int r, int gi, int row) {
-        const float sf = __half2float(__float2half_rn(load_as_f32(p.s[m], p.scale_dtype, (int64_t)row * p.Gn + gi)));
-        float zr = 0.0f, dz = 0.0f;
-        if (p.z[m] != nullptr) {
-            const float z = load_as_f32(p.z[m], p.scale_dtype, (int64_t)row * p.Gn + gi);
-            zr = fminf(fmaxf(rintf(z), -512.0f), 512.0f);
-            dz = z - zr;
-        }
-        const __half s16 = __float2half_rn(sf);
-        const __half c1024 = __float2half_rn(-(1024.0f + zr) * sf);
-        const __half c64 = __float2half_rn(-(64.0f + zr) * sf);
+    // correction term of the epilogue.  Slot = {s, c1024, c64, zero} as four halves; built with
+    // fp16 arithmetic only (off + zr is an exact integer, the product is rounded once).
+    // The correction coefficients (ke, ko) = (z - zr) * s + e are also formed here, in fp16: e is the
+    // rounding error of an fp16 product and therefore exact in fp16; (z - zr) is exact; only the small
+    // product (z - zr) * s is rounded (relative 2^-11 of at most half a quantisation step).
+    auto make_slot = [&](__half s16, __half z16, uint32_t& kk) -> uint2 {
+        const __half2 z2 = __half2half2(z16);
+        const __half2 s2 = __half2half2(s16);
+        const __half2 zr2 = __hmax2(__hmin2(h2rint(z2), __float2half2_rn(512.0f)), __float2half2_rn(-512.0f));
+        const __half2 a2 = __hadd2(zr2, __halves2half2(__float2half_rn(1024.0f), __float2half_rn(64.0f)));
+        const __half2 c2 = __hneg2(__hmul2(a2, s2));                                    // (c1024, c64)
+        const __half2 e2 = __hfma2(a2, s2, c2);                                         // exact rounding errors
+        const __half2 k2 = __hfma2(__hsub2(z2, zr2), s2, e2);                           // (ke, ko)
+        kk = *reinterpret_cast<const uint32_t*>(&k2);
         uint2 v;
-        v.x = (uint32_t)__half_as_ushort(s16) | ((uint32_t)__half_as_ushort(c1024) << 16);
-        v.y = (uint32_t)__half_as_ushort(c64) | ((uint32_t)__half_as_ushort(__float2half_rn(dz)) << 16);
-        slots[(m * kRowBlock + r) * p.Gn + gi] = v;
-        zr16[(m * kRowBlock + r) * p.Gn + gi] = __float2half_rn(zr);
+        v.x = (uint32_t)__half_as_ushort(s16) | ((uint32_t)__half_as_ushort(__low2half(c2)) << 16);
+        v.y = (uint32_t)__half_as_ushort(__high2half(c2));
+        return v;
     };
-    auto stage_slots = [&](int row0, int rows) {
-        for (int m = 0; m < MATS; ++m)
-            for (int i = ctid; i < rows * p.Gn; i += kConsumerThreads) {
-                const int r = i / p.Gn;
-                build_slot(m, r, i - r * p.Gn, row0 + r);
-            }
-    };
-
-    // Scales and zero points do not depend on the previous kernel either: convert the first row
-    // block's constants before waiting on it.
-    {
-        const int rows0 = min(rb_rows, r_cnt);
-        stage_slots(r_lo, rows0);
-    }
 
     pdl_wait();   // activations (and the output buffers) belong to the previous kernel until here
 
@@ -303,27 +323,43 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         named_bar_sync(1, kConsumerThreads);
     }
 
-    uint32_t it = 0;
     bool ok = true;
-    const int n_xc = (p.K + p.xk - 1) / p.xk;
-    const int st_per_xc = p.xk / p.kc;
+    int buf = 0;
     const float fmax_act = p.act_dtype == B200Q_F16 ? 65504.0f : 3.3895313892515355e38f;
+    // per-thread constants of the inner loop
+    const uint32_t w_off = (uint32_t)g * p.row_stride + t * 16;       // this thread's 16 bytes inside a stage row
+    const uint32_t w_off8 = 8 * p.row_stride;
+    const uint32_t x_step = (uint32_t)B * 64;                         // bytes between consecutive activation chunks
+    const uint32_t x_lane = (uint32_t)t * 16;
+    uint32_t x_nt[NT];                                                // byte offset of this lane's batch row per n-tile
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) x_nt[nt] = (uint32_t)min(nt * 8 + g, B - 1) * 64;
+    const int logG = p.logG;
+    const int n_stages = p.stages;
+    const uint32_t stage_bytes = p.stage_bytes;
+    int c_slot = 0;                  // ring slot and phase parity of the stage the consumer is at
+    uint32_t c_phase = 0;
 
-    for (int rb = 0; rb < n_rb; ++rb) {
-        const int row0 = r_lo + rb * rb_rows;
-        const int rows = min(rb_rows, r_hi - row0);
-        if (rb > 0) stage_slots(row0, rows);     // (row block 0 was converted before the wait)
+    for (int rb = 0; rb < n_rb; ++rb, buf ^= 1) {
+        const int tile_begin = rb * TB;
+        const int tile_end = min(n_tiles, tile_begin + TB);
+        uint2* slots = slots_base + (size_t)buf * p.slots_buf_elems;      // [MATS][TB][16][Gn] {s, c1024, c64, -}
+        uint32_t* kks = reinterpret_cast<uint32_t*>(slots_base + 2 * (size_t)p.slots_buf_elems) +
+                        (size_t)buf * p.slots_buf_elems;                  // [MATS][TB][16][Gn] (ke, ko) halves
+        float* red = red_base + (size_t)buf * p.red_buf_elems;            // [MATS][TB][16][B][W] then corr [MATS][TB][16][B]
+        float* corr = red + (size_t)MATS * TB * kTileRows * B * kConsumerWarps;
 
-        float acc[MATS][kRowTiles][NT][4];
+        float acc[MATS][kMaxBlockTiles][NT][4];
 #pragma unroll
         for (int m = 0; m < MATS; ++m)
 #pragma unroll
-            for (int rt = 0; rt < kRowTiles; ++rt)
+            for (int tb = 0; tb < kMaxBlockTiles; ++tb)
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[m][rt][nt][i] = 0.0f;
+                    for (int i = 0; i < 4; ++i) acc[m][tb][nt][i] = 0.0f;
 
+#pragma unroll 1
         for (int xc = 0; xc < n_xc; ++xc) {
             const int xk0 = xc * p.xk;
             const int xkn = min(p.xk, p.K - xk0);
@@ -362,15 +398,15 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                 }
                 named_bar_sync(1, kConsumerThreads);
                 if (has_zero && rb == 0) {
-                    // per-group sums of the staged (fp16) activations for the zero-point term; read again
-                    // only after the reduction barrier at the end of the row block
-                    const int g0 = xk0 / p.G;
-                    const int gn = xkn / p.G;
+                    // per-group sums of the staged (fp16) activations for the zero-point term; they are read
+                    // only after a later barrier (the one that publishes the dequant constants)
+                    const int g0 = xk0 >> logG;
+                    const int gn = xkn >> logG;
                     for (int i = ctid; i < gn * B; i += kConsumerThreads) {
                         const int gi = i / B;
                         const int b = i - gi * B;
                         float se = 0.0f, so = 0.0f;
-                        for (int kk = gi * p.G; kk < (gi + 1) * p.G; kk += 8) {
+                        for (int kk = gi << logG; kk < ((gi + 1) << logG); kk += 8) {
                             const int ksx = kk / KS;
                             const int rem = kk - ksx * KS;
                             const int tt = rem / KT;
@@ -394,157 +430,181 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         xsum_o[(g0 + gi) * B + b] = so;
                     }
                 }
-            } else if (xc == 0) {
-                named_bar_sync(1, kConsumerThreads);   // constants of this row block are visible
             }
 
-            const int st_begin = xc * st_per_xc;
-            const int st_end = min(n_st, st_begin + st_per_xc);
-            for (int st = st_begin; st < st_end; ++st, ++it) {
-                const int slot = it % p.stages;
-                ok = mbar_wait_bounded(&full[slot], (it / p.stages) & 1, &g_device_status, EV_GEMV_FULL_WAIT,
-                                       ok ? kWaitLimit : 64u) && ok;
-                const int k0 = st * p.kc;
-                const int kcur = min(p.kc, p.K - k0);
-                const int nks = kcur / KS;
-                const uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-                for (int ksl = cw; ksl < nks; ksl += kConsumerWarps) {
-                    const int kg = k0 + ksl * KS;
-                    const int ksx = (kg - xk0) / KS;
-                    const int gi = (kg + t * KT) / p.G;
-                    uint32_t bf[NT == 1 ? CH : 1][4];
-                    if (NT == 1) {
+            const int c_begin = xc * kc_per_xc;
+            const int c_end = min(p.n_kc, c_begin + kc_per_xc);
 #pragma unroll
-                        for (int c = 0; c < CH; ++c) {
-                            uint4 u = make_uint4(0, 0, 0, 0);
-                            if (g < B)
-                                u = *reinterpret_cast<const uint4*>(xperm + ((size_t)((ksx * CH + c) * B + g) * 4 + t) * 16);
-                            bf[c][0] = u.x; bf[c][1] = u.y; bf[c][2] = u.z; bf[c][3] = u.w;
+            for (int tb = 0; tb < kMaxBlockTiles; ++tb) {
+                const int tl = tile_begin + tb;
+                if (tl < tile_end) {
+                    const int row0 = r_lo + tl * kTileRows;
+                    const int rows = min(kTileRows, r_hi - row0);
+#pragma unroll
+                    for (int m = 0; m < MATS; ++m) {
+                        uint2* tslots = slots + (size_t)(m * TB + tb) * kTileRows * Gn;
+                        uint32_t* tkk = kks + (size_t)(m * TB + tb) * kTileRows * Gn;
+                        if (xc == 0) {
+                            // ---- dequant constants of this (matrix, tile): from the scales / zeros that were
+                            //      bulk-copied with its first stage, or straight from global memory ----
+                            if (p.meta_by_tma) {
+                                ok = mbar_wait_bounded(&full[c_slot], c_phase, &g_device_status,
+                                                       EV_GEMV_FULL_WAIT, ok ? kWaitLimit : 64u) && ok;
+                                const __half* rs = reinterpret_cast<const __half*>(ring + (size_t)c_slot * stage_bytes + p.stage_meta_off);
+                                const __half* rz = rs + kTileRows * Gn;
+                                const bool hz = p.z[m] != nullptr;
+                                for (int i = ctid; i < rows * Gn; i += kConsumerThreads)
+                                    tslots[i] = make_slot(rs[i], hz ? rz[i] : __ushort_as_half(0), tkk[i]);
+                            } else {
+                                for (int i = ctid; i < rows * Gn; i += kConsumerThreads) {
+                                    const int64_t gidx = (int64_t)row0 * Gn + i;
+                                    tslots[i] = make_slot(__float2half_rn(load_as_f32(p.s[m], p.scale_dtype, gidx)),
+                                                          p.z[m] != nullptr ? __float2half_rn(load_as_f32(p.z[m], p.scale_dtype, gidx))
+                                                                            : __ushort_as_half(0), tkk[i]);
+                                }
+                            }
+                            named_bar_sync(1, kConsumerThreads);     // constants visible to every warp
                         }
-                    }
-#pragma unroll
-                    for (int rt = 0; rt < kRowTiles; ++rt) {
-                        if (rt * 16 < rows) {
-#pragma unroll
-                            for (int m = 0; m < MATS; ++m) {
-                                const int rowA = m * kRowBlock + rt * 16 + g;
-                                const uint8_t* pa = stage + (size_t)rowA * p.row_stride + ksl * 64 + t * 16;
+                        const uint2* slotsA = tslots + g * Gn;
+                        const uint2* slotsB = slotsA + 8 * Gn;
+#pragma unroll 1
+                        for (int c = c_begin; c < c_end; ++c) {
+                            const int slot = c_slot;
+                            ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT,
+                                                   ok ? kWaitLimit : 64u) && ok;
+                            if (++c_slot == n_stages) { c_slot = 0; c_phase ^= 1; }
+                            const int k0 = c * p.kc;
+                            const int kcur = min(p.kc, p.K - k0);
+                            const int nks = kcur / KS;
+                            const uint8_t* stage_w = ring + (size_t)slot * stage_bytes + w_off;
+                            const uint8_t* xbase = xperm + (size_t)((k0 - xk0) / KS) * CH * x_step + x_lane;
+#pragma unroll 1
+                            for (int ksl = cw; ksl < nks; ksl += kConsumerWarps) {
+                                const int gi = (k0 + ksl * KS + t * KT) >> logG;
+                                const uint8_t* pa = stage_w + ksl * 64;
                                 const uint4 ua = *reinterpret_cast<const uint4*>(pa);
-                                const uint4 ub = *reinterpret_cast<const uint4*>(pa + 8 * p.row_stride);
-                                const uint2 ka = slots[rowA * p.Gn + gi];
-                                const uint2 kb = slots[(rowA + 8) * p.Gn + gi];
+                                const uint4 ub = *reinterpret_cast<const uint4*>(pa + w_off8);
+                                const uint2 ka = slotsA[gi];
+                                const uint2 kb = slotsB[gi];
                                 ScaleRegs sa, sb;
                                 sa.s2 = prmt(ka.x, ka.x, 0x1010); sa.c1024 = prmt(ka.x, ka.x, 0x3232); sa.c64 = prmt(ka.y, ka.y, 0x1010);
                                 sb.s2 = prmt(kb.x, kb.x, 0x1010); sb.c1024 = prmt(kb.x, kb.x, 0x3232); sb.c64 = prmt(kb.y, kb.y, 0x1010);
                                 const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w};
                                 const uint32_t wb[4] = {ub.x, ub.y, ub.z, ub.w};
+                                const uint8_t* xk = xbase + (size_t)ksl * CH * x_step;
 #pragma unroll
-                                for (int c = 0; c < CH; ++c) {
-                                    // A fragments of MMA 2c and 2c+1
+                                for (int ch = 0; ch < CH; ++ch) {
+                                    // A fragments of MMA 2ch and 2ch+1
                                     uint32_t a[2][4];
                                     if (BITS == 4) {
                                         uint32_t va[4], vb[4];
-                                        dequant_q4_word(wa[c], sa, va);
-                                        dequant_q4_word(wb[c], sb, vb);
+                                        dequant_q4_word(wa[ch], sa, va);
+                                        dequant_q4_word(wb[ch], sb, vb);
                                         a[0][0] = va[0]; a[0][1] = vb[0]; a[0][2] = va[1]; a[0][3] = vb[1];
                                         a[1][0] = va[2]; a[1][1] = vb[2]; a[1][2] = va[3]; a[1][3] = vb[3];
                                     } else {
                                         uint32_t va[2], vb[2];
-                                        dequant_q8_word(wa[2 * c], sa, va);
-                                        dequant_q8_word(wb[2 * c], sb, vb);
+                                        dequant_q8_word(wa[2 * ch], sa, va);
+                                        dequant_q8_word(wb[2 * ch], sb, vb);
                                         a[0][0] = va[0]; a[0][1] = vb[0]; a[0][2] = va[1]; a[0][3] = vb[1];
-                                        dequant_q8_word(wa[2 * c + 1], sa, va);
-                                        dequant_q8_word(wb[2 * c + 1], sb, vb);
+                                        dequant_q8_word(wa[2 * ch + 1], sa, va);
+                                        dequant_q8_word(wb[2 * ch + 1], sb, vb);
                                         a[1][0] = va[0]; a[1][1] = vb[0]; a[1][2] = va[1]; a[1][3] = vb[1];
                                     }
 #pragma unroll
                                     for (int nt = 0; nt < NT; ++nt) {
-                                        uint32_t b0, b1, b2, b3;
-                                        if (NT == 1) {
-                                            b0 = bf[c][0]; b1 = bf[c][1]; b2 = bf[c][2]; b3 = bf[c][3];
-                                        } else {
-                                            uint4 u = make_uint4(0, 0, 0, 0);
-                                            const int bb = nt * 8 + g;
-                                            if (bb < B)
-                                                u = *reinterpret_cast<const uint4*>(
-                                                    xperm + ((size_t)((ksx * CH + c) * B + bb) * 4 + t) * 16);
-                                            b0 = u.x; b1 = u.y; b2 = u.z; b3 = u.w;
-                                        }
-                                        mma_m16n8k16(acc[m][rt][nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
-                                        mma_m16n8k16(acc[m][rt][nt], a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
+                                        // columns >= B read a clamped (valid) batch row; their results are never stored
+                                        const uint4 u = *reinterpret_cast<const uint4*>(xk + ch * x_step + x_nt[nt]);
+                                        mma_m16n8k16(acc[m][tb][nt], a[0][0], a[0][1], a[0][2], a[0][3], u.x, u.y);
+                                        mma_m16n8k16(acc[m][tb][nt], a[1][0], a[1][1], a[1][2], a[1][3], u.z, u.w);
                                     }
                                 }
                             }
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&empty[slot]);
                         }
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
             }
         }
 
-        // ---- cross-warp reduction (fixed order) ----
+        // ---- partial tiles -> shared memory, layout [m][tb][row][b][warp] ----
 #pragma unroll
         for (int m = 0; m < MATS; ++m)
 #pragma unroll
-            for (int rt = 0; rt < kRowTiles; ++rt)
+            for (int tb = 0; tb < kMaxBlockTiles; ++tb)
+                if (tile_begin + tb < tile_end) {
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
+                    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = rt * 16 + g + (i >> 1) * 8;
-                        const int b = nt * 8 + 2 * t + (i & 1);
-                        if (b < B) red[((cw * MATS + m) * kRowBlock + r) * B + b] = acc[m][rt][nt][i];
-                    }
-        named_bar_sync(1, kConsumerThreads);
-
-        // ---- epilogue: one warp per output row.  Lanes first split the groups of the row for the
-        //      zero-point term, then lane b finishes batch row b. ----
-        for (int r = cw; r < rows; r += kConsumerWarps) {
-            float val[MATS];
+                        for (int i = 0; i < 4; ++i) {
+                            const int r = g + (i >> 1) * 8;
+                            const int b = nt * 8 + 2 * t + (i & 1);
+                            if (b < B) red[((((m * TB + tb) * kTileRows + r) * B + b) << 4) + cw] = acc[m][tb][nt][i];
+                        }
+                }
+        // ---- zero-point term: warp per output row, lanes over the groups of the row ----
+        const int block_rows = min(r_hi, r_lo + tile_end * kTileRows) - (r_lo + tile_begin * kTileRows);
+        if (has_zero) {
+            for (int rr = cw; rr < block_rows; rr += kConsumerWarps) {
+                const int tb = rr / kTileRows;
+                const int r = rr - tb * kTileRows;
 #pragma unroll
-            for (int m = 0; m < MATS; ++m) {
-                float mine = 0.0f;       // correction for batch row == lane
-                if (has_zero && p.z[m] != nullptr) {
+                for (int m = 0; m < MATS; ++m) {
                     float part[NT * 8];
 #pragma unroll
                     for (int b = 0; b < NT * 8; ++b) part[b] = 0.0f;
-                    for (int gi = lane; gi < p.Gn; gi += 32) {
-                        const uint2 k = slots[(m * kRowBlock + r) * p.Gn + gi];
-                        const float sf = __half2float(__ushort_as_half((unsigned short)(k.x & 0xFFFF)));
-                        const float c1024 = __half2float(__ushort_as_half((unsigned short)(k.x >> 16)));
-                        const float c64 = __half2float(__ushort_as_half((unsigned short)(k.y & 0xFFFF)));
-                        const float dz = __half2float(__ushort_as_half((unsigned short)(k.y >> 16)));
-                        const float zr = __half2float(zr16[(m * kRowBlock + r) * p.Gn + gi]);
-                        const float base = dz * sf;
-                        const float ke = base + fmaf(1024.0f + zr, sf, c1024);
-                        const float ko = base + fmaf(64.0f + zr, sf, c64);
+                    if (p.z[m] != nullptr) {
+                        const uint32_t* rkk = kks + ((size_t)(m * TB + tb) * kTileRows + r) * Gn;
+                        for (int gi = lane; gi < Gn; gi += 32) {
+                            const uint32_t kk = rkk[gi];
+                            const __half2 k2 = *reinterpret_cast<const __half2*>(&kk);
+                            const float ke = __low2float(k2), ko = __high2float(k2);
 #pragma unroll
-                        for (int b = 0; b < NT * 8; ++b)
-                            if (b < B) part[b] = fmaf(ke, xsum_e[gi * B + b], fmaf(ko, xsum_o[gi * B + b], part[b]));
+                            for (int b = 0; b < NT * 8; ++b)
+                                if (b < B) part[b] = fmaf(ke, xsum_e[gi * B + b], fmaf(ko, xsum_o[gi * B + b], part[b]));
+                        }
                     }
 #pragma unroll
                     for (int b = 0; b < NT * 8; ++b) {
                         if (b < B) {
                             const float s = warp_sum(part[b]);
-                            if (lane == b) mine = s;
+                            if (lane == 0) corr[((m * TB + tb) * kTileRows + r) * B + b] = s;
                         }
                     }
                 }
-                float s = 0.0f;
-                if (lane < B) {
+            }
+        }
+        named_bar_sync(1, kConsumerThreads);
+
+        // ---- reduction over the warps (fixed order: xor tree inside 16 lanes) + epilogue.  red / corr /
+        //      slots are double-buffered, so the next row block may start while slower warps are here. ----
+        const int items = block_rows * B;            // (row, batch row) pairs of this block
+        for (int base = 0; base < items; base += kConsumerThreads / 16) {
+            const int item = base + (ctid >> 4);
+            const int w = ctid & 15;
+            const bool live = item < items;
+            const int rr = live ? item / B : 0;
+            const int b = live ? item - rr * B : 0;
+            const int tb = rr / kTileRows;
+            const int r = rr - tb * kTileRows;
+            float val[MATS];
 #pragma unroll
-                    for (int w = 0; w < kConsumerWarps; ++w) s += red[((w * MATS + m) * kRowBlock + r) * B + lane];
-                    s -= mine;
-                    if (need_row_pass) s *= xscale[lane];
-                }
+            for (int m = 0; m < MATS; ++m) {
+                float s = live ? red[((((m * TB + tb) * kTileRows + r) * B + b) << 4) + w] : 0.0f;
+                s += __shfl_xor_sync(0xffffffffu, s, 8);
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                if (has_zero && live) s -= corr[((m * TB + tb) * kTileRows + r) * B + b];
+                if (need_row_pass) s *= xscale[b];
                 val[m] = round_act(fminf(fmaxf(s, -fmax_act), fmax_act), p.act_dtype);
             }
-            if (lane < B) {
-                const int64_t o = (int64_t)lane * p.N + row0 + r;
-                auto store = [&](void* base, float v) {
-                    if (p.act_dtype == B200Q_F16) reinterpret_cast<__half*>(base)[o] = __float2half_rn(v);
-                    else reinterpret_cast<__nv_bfloat16*>(base)[o] = __float2bfloat16_rn(v);
+            if (live && w == 0) {
+                const int64_t o = (int64_t)b * p.N + r_lo + tile_begin * kTileRows + rr;
+                auto store = [&](void* basep, float v) {
+                    if (p.act_dtype == B200Q_F16) reinterpret_cast<__half*>(basep)[o] = __float2half_rn(v);
+                    else reinterpret_cast<__nv_bfloat16*>(basep)[o] = __float2bfloat16_rn(v);
                 };
                 if (GATE_UP) {
                     if (p.gate_out != nullptr) store(p.gate_out, val[0]);
@@ -561,7 +621,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                 }
             }
         }
-        named_bar_sync(1, kConsumerThreads);   // red / constants are reused by the next row block
     }
 }
 
@@ -636,52 +695,76 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     constexpr int MATS = GATE_UP ? 2 : 1;
     constexpr int KS = BITS == 4 ? 128 : 64;
     const int sms = sm_count();
-    int ctas_per_sm = tuning_get("gemv.ctas_per_sm");
-    if (ctas_per_sm <= 0) ctas_per_sm = 1;
-    // k per stage: default 8 k-steps (one per consumer warp)
+    const uint32_t smem_cap = (uint32_t)max_smem_optin();
+
+    // k per stage: per-row copies of about 2 KB, whole k-steps and whole groups
+    const int unit = std::max(KS, p.G);
+    p.logG = 0;
+    while ((1 << p.logG) < p.G) ++p.logG;
     int kc = tuning_get("gemv.stage_k");
-    if (kc <= 0) kc = KS * kConsumerWarps;
-    {
-        const int unit = std::max(KS, p.G);   // a stage holds whole k-steps and whole groups
-        kc = std::max(unit, kc / unit * unit);
+    if (kc <= 0) {
+        const int target_bytes = 2048;
+        const int n = std::max(1, (p.row_bytes + target_bytes / 2) / target_bytes);
+        kc = (p.K + n - 1) / n;
     }
-    kc = std::min(kc, p.K);
-    int stages = tuning_get("gemv.stages");
-    if (stages <= 0) stages = 4;
-    stages = std::min(stages, kMaxStages);
-
-    // activation chunk: whole K when it fits the budget, else a multiple of kc
-    const uint32_t x_budget = 64 * 1024;
-    int xk = p.K;
-    if ((size_t)p.K * p.B * 2 > x_budget) {
-        xk = (int)(x_budget / (p.B * 2)) / kc * kc;
-        if (xk < kc) xk = kc;
-    }
+    kc = std::min(p.K, std::max(unit, (kc + unit - 1) / unit * unit));
     p.kc = kc;
-    p.xk = xk;
-    p.stages = stages;
+    p.n_kc = (p.K + kc - 1) / kc;
 
-    int grid = std::min<int64_t>((int64_t)sms * ctas_per_sm, (p.N + 15) / 16);
+    int grid = (int)std::min<int64_t>(sms, (p.N + kTileRows - 1) / kTileRows);
+    const int ctas_per_sm = tuning_get("gemv.ctas_per_sm");
+    if (ctas_per_sm > 1) grid = (int)std::min<int64_t>((int64_t)sms * ctas_per_sm, (p.N + kTileRows - 1) / kTileRows);
     grid = std::max(grid, 1);
     p.rows_lo = p.N / grid;
     p.rem = p.N % grid;
+    const int max_tiles = (p.rows_lo + (p.rem ? 1 : 0) + kTileRows - 1) / kTileRows;
 
+    // scales / zeros ride along with the first stage of every tile when they are fp16 and every tile
+    // starts on a 16-byte boundary
+    p.meta_by_tma = p.scale_dtype == B200Q_F16 && (p.Gn % 8 == 0) && aligned16(p.s[0]) &&
+                    (p.z[0] == nullptr || aligned16(p.z[0])) &&
+                    (MATS == 1 || (aligned16(p.s[1]) && (p.z[1] == nullptr || aligned16(p.z[1]))));
     p.row_stride = (uint32_t)(kc * BITS / 8) + kRowPad;
-    p.stage_bytes = MATS * kRowBlock * p.row_stride;
-    uint32_t off = 2 * kMaxStages * sizeof(uint64_t);
-    off = align_up(off, 128);
-    p.off_xperm = off;  off += align_up((uint32_t)xk * p.B * 2, 128);
-    p.off_xsum = off;   off += align_up((uint32_t)2 * p.Gn * p.B * 4, 128);
-    p.off_xscale = off; off += align_up((uint32_t)p.B * 2 * 4, 128);
-    p.off_scales = off; off += align_up((uint32_t)MATS * kRowBlock * p.Gn * 8, 128);   // dequant constants
-    p.off_corr = off;   off += align_up((uint32_t)MATS * kRowBlock * p.Gn * 2, 128);   // integer zero points
-    p.off_red = off;    off += align_up((uint32_t)kConsumerWarps * MATS * kRowBlock * p.B * 4, 128);
-    p.off_ring = off;
-    const uint32_t smem_cap = (uint32_t)max_smem_optin();
+    p.stage_meta_off = align_up(kTileRows * p.row_stride, 128);
+    p.stage_bytes = p.stage_meta_off + align_up((uint32_t)2 * kTileRows * p.Gn * 2, 128);
+
+    // Activation chunk (whole K when it fits the budget, else a multiple of kc) and the number of tiles whose
+    // accumulators stay live across chunks: first choice that leaves room for a two-stage ring.
+    uint32_t off = 0;
+    bool fits = false;
+    const uint32_t budgets[3] = {64 * 1024, 32 * 1024, 16 * 1024};
+    for (int tb_try = kMaxBlockTiles; tb_try >= 1 && !fits; --tb_try) {
+        for (int bi = 0; bi < 3 && !fits; ++bi) {
+            int xk = p.n_kc * kc;
+            if ((size_t)p.K * p.B * 2 > budgets[bi]) xk = std::max(1, (int)(budgets[bi] / ((size_t)p.B * 2 * kc))) * kc;
+            const int n_xc = (p.K + xk - 1) / xk;
+            const int block_tiles = n_xc > 1 ? std::min(max_tiles, tb_try) : 1;
+            if (n_xc == 1 && (tb_try != kMaxBlockTiles || bi != 0)) continue;   // nothing new to try
+            p.xk = xk;
+            p.block_tiles = block_tiles;
+            p.slots_buf_elems = (uint32_t)MATS * block_tiles * kTileRows * p.Gn;
+            p.red_buf_elems = (uint32_t)(kConsumerWarps + 1) * MATS * block_tiles * kTileRows * p.B;
+            off = align_up(2 * kMaxStages * sizeof(uint64_t), 128);
+            p.off_xperm = off;  off += align_up((uint32_t)xk * p.B * 2, 128);
+            p.off_xsum = off;   off += align_up((uint32_t)2 * p.Gn * p.B * 4, 128);
+            p.off_xscale = off; off += align_up((uint32_t)p.B * 2 * 4, 128);
+            p.off_slots = off;  off += align_up(2 * p.slots_buf_elems * 12, 128);
+            p.off_red = off;    off += align_up(2 * p.red_buf_elems * 4, 128);
+            p.off_ring = off;
+            fits = off + 2ull * p.stage_bytes <= smem_cap;
+        }
+    }
+    if (!fits) return B200Q_ERR_UNSUPPORTED;
+
+    // ring depth: everything the CTA will ever stream if that is small (keeps two CTAs resident per SM, so
+    // the next kernel's prefetch overlaps this kernel's tail), else as deep as shared memory allows
+    const int total_stages = max_tiles * MATS * p.n_kc;
+    int stages = tuning_get("gemv.stages");
+    if (stages <= 0) stages = kMaxStages;
+    stages = std::min({stages, kMaxStages, std::max(2, total_stages)});
     while (stages > 2 && off + (uint64_t)stages * p.stage_bytes > smem_cap) --stages;
     p.stages = stages;
     const uint64_t total = off + (uint64_t)stages * p.stage_bytes;
-    if (total > smem_cap) return B200Q_ERR_UNSUPPORTED;
 
     auto kernel = qgemv_kernel<BITS, NT, GATE_UP>;
     static bool configured[64] = {};   // per instantiation and device; a race only repeats the call
@@ -714,14 +797,15 @@ int launch_generic(const GemvParams& p, int bits, cudaStream_t stream) {
     return finish_launch();
 }
 
-// The generic kernel has no norm prologue: it is run after the stand-alone rmsnorm kernel by the
-// caller (see api.cu) when the fast path does not apply.
+// The generic kernel has no norm prologue: the caller runs the stand-alone rmsnorm kernel first when
+// the fast path does not apply.
 bool fast_path_ok(const GemvParams& p, int bits) {
     const int ks = bits == 4 ? 128 : 64;
     const int kt = ks / 4;
-    if (p.K % ks != 0 || p.G % kt != 0 || p.K % p.G != 0 || (ks * kConsumerWarps) % p.G != 0) return false;
+    if (tuning_get("gemv.force_generic")) return false;
+    if (p.K % ks != 0 || p.G % kt != 0 || p.K % p.G != 0 || (p.G & (p.G - 1)) != 0) return false;
     if (p.B > 16) return false;
-    if ((size_t)p.Gn * kRowBlock * 2 * 10 > 96 * 1024) return false;
+    if ((size_t)p.Gn * kTileRows * 8 * 2 * (p.w[1] ? 2 : 1) > 64 * 1024) return false;
     if (!aligned16(p.x) || !aligned16(p.w[0]) || (p.w[1] != nullptr && !aligned16(p.w[1]))) return false;
     if (p.res_in != nullptr && !aligned16(p.res_in)) return false;
     if (p.z_out != nullptr && !aligned16(p.z_out)) return false;
@@ -744,26 +828,50 @@ int rmsnorm_residual_launch(const void* x, const void* residual, const void* wei
 
 int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scales, const void* zeros,
                  const void* residual, void* y, int B, int64_t N, int64_t K, int group_size, int act_dtype,
-                 int scale_dtype, cudaStream_t stream) {
+                 int scale_dtype, const void* residual_in, const void* norm_weight, int norm_w_dtype, float eps,
+                 void* z_out, void* normed_out, cudaStream_t stream) {
     if ((bits != 4 && bits != 8) || x == nullptr || codes == nullptr || scales == nullptr || y == nullptr)
         return B200Q_ERR_BAD_ARG;
     if (B <= 0 || N <= 0 || K <= 0 || group_size <= 0 || !is_act_dtype(act_dtype) || !is_scale_dtype(scale_dtype))
         return B200Q_ERR_BAD_ARG;
+    if (norm_weight != nullptr && !is_scale_dtype(norm_w_dtype)) return B200Q_ERR_BAD_ARG;
+    if (norm_weight == nullptr && (residual_in != nullptr || z_out != nullptr || normed_out != nullptr))
+        return B200Q_ERR_BAD_ARG;
     if (N > INT32_MAX || K > INT32_MAX) return B200Q_ERR_UNSUPPORTED;
     const int esz = 2;
+    auto off = [&](const void* base, size_t elems) -> const uint8_t* {
+        return base ? reinterpret_cast<const uint8_t*>(base) + elems * esz : nullptr;
+    };
+    auto offw = [&](void* base, size_t elems) -> uint8_t* {
+        return base ? reinterpret_cast<uint8_t*>(base) + elems * esz : nullptr;
+    };
     for (int b0 = 0; b0 < B; b0 += 16) {
         GemvParams p = {};
         const int bn = std::min(16, B - b0);
-        p.x = reinterpret_cast<const uint8_t*>(x) + (size_t)b0 * K * esz;
+        p.x = off(x, (size_t)b0 * K);
+        p.res_in = off(residual_in, (size_t)b0 * K);
+        p.norm_w = norm_weight; p.eps = eps; p.norm_w_dtype = norm_w_dtype;
+        p.z_out = offw(z_out, (size_t)b0 * K);
+        p.normed_out = offw(normed_out, (size_t)b0 * K);
         p.w[0] = codes; p.s[0] = scales; p.z[0] = zeros;
-        p.residual = residual ? reinterpret_cast<const uint8_t*>(residual) + (size_t)b0 * N * esz : nullptr;
-        p.y = reinterpret_cast<uint8_t*>(y) + (size_t)b0 * N * esz;
+        p.residual = off(residual, (size_t)b0 * N);
+        p.y = offw(y, (size_t)b0 * N);
         p.B = bn; p.N = (int)N; p.K = (int)K; p.G = group_size; p.Gn = (int)((K + group_size - 1) / group_size);
         p.act_dtype = act_dtype; p.scale_dtype = scale_dtype;
         p.row_bytes = bits == 4 ? (int)((K + 1) / 2) : (int)K;
-        int rc;
-        if (fast_path_ok(p, bits)) rc = dispatch_fast<false>(bits, p, stream);
-        else rc = launch_generic<false>(p, bits, stream);
+        int rc = fast_path_ok(p, bits) ? dispatch_fast<false>(bits, p, stream) : B200Q_ERR_UNSUPPORTED;
+        if (rc == B200Q_ERR_UNSUPPORTED) {
+            if (norm_weight != nullptr) {
+                // generic route: materialise the normalised rows first (normed_out is required as the buffer)
+                if (p.normed_out == nullptr) return B200Q_ERR_UNSUPPORTED;
+                rc = rmsnorm_residual_launch(p.x, p.res_in, norm_weight, p.normed_out, p.z_out, bn, K, eps, act_dtype,
+                                             norm_w_dtype, stream);
+                if (rc != B200Q_OK) return rc;
+                p.x = p.normed_out;
+                p.norm_w = nullptr; p.res_in = nullptr; p.z_out = nullptr; p.normed_out = nullptr;
+            }
+            rc = launch_generic<false>(p, bits, stream);
+        }
         if (rc != B200Q_OK) return rc;
     }
     return B200Q_OK;
@@ -808,9 +916,8 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
         p.act_dtype = act_dtype; p.scale_dtype = scale_dtype;
         p.row_bytes = bits == 4 ? (int)((K + 1) / 2) : (int)K;
         int rc;
-        if (fast_path_ok(p, bits)) {
-            rc = dispatch_fast<true>(bits, p, stream);
-        } else {
+        rc = fast_path_ok(p, bits) ? dispatch_fast<true>(bits, p, stream) : B200Q_ERR_UNSUPPORTED;
+        if (rc == B200Q_ERR_UNSUPPORTED) {
             if (norm_weight != nullptr) {
                 // generic route: materialise the normalised rows first (normed_out is required as the buffer)
                 if (p.normed_out == nullptr) return B200Q_ERR_UNSUPPORTED;

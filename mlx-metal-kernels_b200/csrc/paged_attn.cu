@@ -3,24 +3,27 @@
 //   out[b, hq] = softmax_j( scale * q[b, hq] . Khat[j, hkv] ) . Vhat[j, hkv],  hkv = hq / (Hq/Hkv)
 //   Khat = fp16((code - 8|128) * |k_scale|)   over the valid tokens j of sequence b.
 //
-// Fast kernel (head_dim 128, q in fp16, group size a multiple of 32, <= 16 query heads per kv
-// head):
+// Fast kernel (head_dim 128, page size 16, q in fp16, fp16 scales, group size 32 or 64, at most 8
+// query heads per kv head, at most 8 kv heads):
 //   * the (sequence, page) pairs of the whole batch form one flattened list that is cut into
 //     equal contiguous ranges, one per CTA ("stream-K" over ragged lengths: every CTA streams the
 //     same number of pages whatever the length distribution).  A CTA writes one partial
 //     (max, sum, accumulator) per sequence it touches; a second small kernel merges them.
-//   * a producer warp walks the block table and stages whole pages - every token row of K and V
-//     for ALL kv heads plus their scales - into a ring of shared-memory slots with 1-D bulk
-//     copies (TMA engine) completing on mbarriers.  Row strides in shared memory are padded
-//     (K: = 64 mod 128 bytes, V: = 16 mod 64 bytes) so both read patterns are conflict-free.
-//   * consumer warp w owns kv head w: scores S^T[head, token] = Q K^T on mma.sync.m16n8k16 with
-//     the query heads of the group as the 16 rows and in-register dequantised K as the B operand
-//     (a thread dequantises exactly the 16 bytes it loaded); online softmax in fp32; the
-//     probabilities are already in B-operand layout for O^T[d, head] += V^T P, where V^T is the
-//     A operand built from 8-byte pieces of four token rows with one byte-permute per word pair.
-//     KV bytes are read once per kv head, not once per query head.
+//   * warp w of a CTA owns kv head w % Hkv (and, when there are fewer than 8 kv heads, every
+//     (8/Hkv)-th page of the range).  It is self-contained: it looks up its page ids 32 at a time,
+//     and every lane copies exactly the bytes IT will consume (16 bytes of two K token rows,
+//     8 bytes of four V token rows) with cp.async into a private ring in shared memory, several
+//     pages ahead.  No CTA-wide barrier, no bank conflicts (the ring is laid out [piece][lane]).
+//     Measured on B200: the bulk-copy (TMA) engine needs >= 2 KB per copy to reach HBM speed,
+//     and a token row of one page is 512 B, so per-lane asynchronous copies are the faster route.
+//   * scores S^T[head, token] = Q K^T on mma.sync.m16n8k16 with the query heads of the group as
+//     rows and in-register dequantised K as the B operand; online softmax in fp32; the
+//     probabilities are already in B-operand layout for O^T[d, head] += V^T P, where V^T is the A
+//     operand built from the four token rows with one byte-permute per word pair.  KV bytes are
+//     read once per kv head, not once per query head; Khat / Vhat are bit-identical to the
+//     reference's fp16 dequantised cache.
 //
-// Everything else (other head dims, bf16 queries, odd group sizes) runs the simple kernel: one
+// Everything else (other head dims, bf16 queries, other group sizes) runs the simple kernel: one
 // warp per (sequence, query head), the reference's streaming-softmax loop.
 #include "common.cuh"
 
@@ -33,12 +36,10 @@ B200Q_DEFINE_STATUS_WORD(attn_read_status)
 
 namespace {
 
-constexpr int kAttnConsumerWarps = 8;
-constexpr int kAttnThreads = (kAttnConsumerWarps + 1) * 32;
-constexpr int kAttnMaxStages = 16;
-constexpr int kMaxGrid = 512;             // upper bound on CTAs of the fast kernel (sizes the workspace)
+constexpr int kAttnWarps = 8;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kMaxGrid = 304;             // upper bound on CTAs of the fast kernel (sizes the workspace)
 constexpr int kMaxBatchFast = 2048;       // prefix sums of page counts live in shared memory
-constexpr uint32_t kAttnWaitLimit = 1u << 21;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnParams {
@@ -49,22 +50,36 @@ struct AttnParams {
     const __half* v_scales;
     const int32_t* block_table; // [B, max_blocks]
     const int32_t* lengths;     // [B]
-    float* partial;             // [(grid + B)][Hq][D + 2]  (acc[D], max, sum)
+    float* partial;             // [(grid + B) * subs][Hq][D + 2]  (acc[D], max, sum)
     void* out;                  // [B, Hq, D]
     int B, Hq, Hkv, D, P, max_blocks, G, Gd, group;
     int64_t num_pages;
     float scale;
     int q_dtype;
     int bits;
-    int stages;
+    int stages;                 // pages in flight per warp
+    int subs;                   // warps per kv head inside a CTA (8 / Hkv)
     int row_bytes;              // bytes of one token row of codes, all kv heads
-    int k_stride, v_stride;     // padded shared-memory strides of a token row
-    int scale_row_bytes;        // bytes of one token row of scales, all kv heads
-    uint32_t off_meta, off_prefix, off_ring, slot_bytes, off_k, off_v, off_ks, off_vs;
+    int scale_row_halves;       // halves of one token row of scales, all kv heads
+    uint32_t off_prefix, off_ring, slot_bytes;
     int grid;
 };
 
 __device__ __forceinline__ int clamp_len(int len, int cap) { return max(0, min(len, cap)); }
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // Prefix sums of per-sequence page counts into shared memory; returns the total.
 __device__ int build_prefix(const AttnParams& p, int* prefix) {
@@ -91,310 +106,351 @@ __device__ int build_prefix(const AttnParams& p, int* prefix) {
     return prefix[p.B];
 }
 
-template <int BITS>
+// largest b with prefix[b] <= f (f < prefix[B])
+__device__ __forceinline__ int find_sequence(const int* prefix, int B, int f) {
+    int lo = 0, hi = B - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (prefix[mid] <= f) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int BITS, int LOGG>
 __global__ void __launch_bounds__(kAttnThreads, 1) paged_attn_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int D = 128;
-    constexpr int DP = BITS == 4 ? 64 : 128;       // code bytes per head and token
+    constexpr int DP = BITS == 4 ? 64 : 128;          // code bytes per head and token
+    constexpr int K_BYTES = BITS == 4 ? 1024 : 2048;  // per page and head
+    constexpr int V_BYTES = K_BYTES;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-    uint64_t* empty = full + kAttnMaxStages;
-    int* meta = reinterpret_cast<int*>(smem + p.off_meta);       // [stages][4]: page id, b, page index in sequence
     int* prefix = reinterpret_cast<int*>(smem + p.off_prefix);   // [B + 1]
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], (uint32_t)min(p.Hkv, kAttnConsumerWarps));   // one arrival per working warp
-        }
-        mbar_fence_init();
-    }
-    __syncthreads();
     pdl_launch_dependents();
-    pdl_wait();   // lengths / block table / q may be produced by the previous kernel
+    pdl_wait();   // lengths / block table / q / the cache itself may be produced by the previous kernel
 
     const int total = build_prefix(p, prefix);
     const int ppc = (total + p.grid - 1) / p.grid;               // pages per CTA
     const int lo = min(total, (int)blockIdx.x * ppc);
     const int hi = min(total, lo + ppc);
-    if (lo >= hi) return;
+    const int subs = p.subs;
+    const int h = warp % p.Hkv;                                  // kv head of this warp
+    const int sub = warp / p.Hkv;
+    if (lo >= hi || sub >= subs) return;
 
-    uint8_t* ring = smem + p.off_ring;
-
-    if (warp == kAttnConsumerWarps) {
-        // ------------------------------- producer ------------------------------------------------
-        int b = 0;
-        bool ok = true;
-        const uint32_t tx_bytes = 2u * p.P * p.row_bytes + 2u * p.P * p.scale_row_bytes;
-        for (int f = lo, it = 0; f < hi; ++f, ++it) {
-            while (f >= prefix[b + 1]) ++b;
-            const int pg = f - prefix[b];
-            const int slot = it % p.stages;
-            if (it >= p.stages) {
-                ok = mbar_wait_bounded(&empty[slot], ((it / p.stages) - 1) & 1, &g_device_status, EV_ATTN_EMPTY_WAIT,
-                                       ok ? kAttnWaitLimit : 64u) && ok;
-            }
-            int page = p.block_table[(int64_t)b * p.max_blocks + pg];
-            if (page < 0 || page >= p.num_pages) page = -1;
-            uint8_t* slotp = ring + (size_t)slot * p.slot_bytes;
-            if (lane == 0) {
-                meta[slot * 4 + 0] = page;
-                meta[slot * 4 + 1] = b;
-                meta[slot * 4 + 2] = pg;
-                meta[slot * 4 + 3] = min(p.P, clamp_len(p.lengths[b], p.max_blocks * p.P) - pg * p.P);
-                if (page >= 0) mbar_arrive_expect_tx(&full[slot], tx_bytes);
-                else mbar_arrive(&full[slot]);
-            }
-            __syncwarp();
-            if (page >= 0) {
-                const uint8_t* ksrc = p.k_codes + (size_t)page * p.P * p.row_bytes;
-                const uint8_t* vsrc = p.v_codes + (size_t)page * p.P * p.row_bytes;
-                for (int i = lane; i < 2 * p.P; i += 32) {
-                    const int r = i < p.P ? i : i - p.P;
-                    if (i < p.P) bulk_g2s(slotp + p.off_k + (size_t)r * p.k_stride, ksrc + (size_t)r * p.row_bytes, p.row_bytes, &full[slot]);
-                    else bulk_g2s(slotp + p.off_v + (size_t)r * p.v_stride, vsrc + (size_t)r * p.row_bytes, p.row_bytes, &full[slot]);
-                }
-                if (lane == 0) {
-                    const uint32_t sb = p.P * p.scale_row_bytes;
-                    bulk_g2s(slotp + p.off_ks, reinterpret_cast<const uint8_t*>(p.k_scales) + (size_t)page * sb, sb, &full[slot]);
-                    bulk_g2s(slotp + p.off_vs, reinterpret_cast<const uint8_t*>(p.v_scales) + (size_t)page * sb, sb, &full[slot]);
-                }
-            }
-        }
-        return;
-    }
-
-    // ----------------------------------- consumers ------------------------------------------------
     const int g = lane >> 2;
     const int t = lane & 3;
     const int group = p.group;
     const float sm_scale = p.scale;
-    bool ok = true;
+    constexpr int NS = BITS == 4 ? 8 : 5;                        // pages in flight per warp
+    constexpr int SLOT = K_BYTES + V_BYTES + 256;                // bytes of one ring slot
+    uint8_t* my_ring = smem + p.off_ring + (size_t)warp * NS * SLOT;
+    // number of pages this warp walks: f = lo + sub + j * subs < hi
+    const int n_my = (hi - lo - sub + subs - 1) / subs;
 
-    for (int h = warp; h < p.Hkv; h += kAttnConsumerWarps) {
-        // The ring is walked once per kv head handled by this warp; with Hkv <= 8 that is once.
-        // (Hkv > 8 is routed to the simple kernel by the host, see fast_ok().)
-        uint32_t qa[8][4];          // Q as A operand: [mma][a0a1 (row g), a2a3 (row g+8), a4a5, a6a7]
-        float o[8][4];              // O^T tiles: rows d, cols heads
-        float m_run = -INFINITY;    // running max / sum of query head g of the group
-        float l_run = 0.0f;
-        int cur_b = -1;
+    uint32_t qa[8][2];          // Q as A operand: [mma][a0a1 (row g), a4a5 (row g)]; rows 8..15 are zero
+    float o[8][4];              // O^T tiles: rows d, cols heads
+    float m_run = -INFINITY;    // running max / sum of query head g of the group
+    float l_run = 0.0f;
+    int cur_b = -1;
 
-        auto flush = [&](int b) {
-            // partial slot: (cta + b), see merge kernel
-            float* dst = p.partial + ((size_t)(blockIdx.x + b) * p.Hq) * (D + 2);
-            // reduce l over the quad
-            float l0 = l_run;
-            l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-            // O^T[d][head]: thread (g,t) holds d = 16g + 2i (+1), heads 2t, 2t+1
+    // Page descriptors (page id, sequence, valid tokens) of 32 consecutive pages of this warp, one per
+    // lane.  Two windows: one for the page being consumed, one for the page being issued ahead.
+    struct Desc { int page, b, valid; };
+    auto lookup = [&](int base) -> Desc {
+        const int j = base + lane;
+        Desc d = {-1, 0, 0};
+        if (j < n_my) {
+            const int f = lo + sub + j * subs;
+            const int b = find_sequence(prefix, p.B, f);
+            const int pg = f - prefix[b];
+            int page = p.block_table[(int64_t)b * p.max_blocks + pg];
+            if (page < 0 || page >= p.num_pages) page = -1;
+            d.page = page;
+            d.b = b;
+            d.valid = min(p.P, clamp_len(p.lengths[b], p.max_blocks * p.P) - pg * p.P);
+        }
+        return d;
+    };
+    Desc win_c = lookup(0);     // consume window
+    Desc win_i = win_c;         // issue window
+    // per-lane source offsets inside a page (bytes) and destination offsets inside a slot
+    const uint32_t row_bytes = (uint32_t)p.row_bytes;
+    const uint32_t k_src0 = (uint32_t)g * row_bytes + h * DP + 16 * t;            // token g
+    const uint32_t k_src1 = k_src0 + 8 * row_bytes;                               // token g + 8
+    uint32_t v_src[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i)
+        v_src[i] = (uint32_t)(2 * t + (i & 1) + 8 * (i >> 1)) * row_bytes + h * DP + (BITS == 4 ? 8 : 16) * g;
+    const uint32_t sc_src = (uint32_t)(lane & 15) * p.scale_row_halves + h * p.Gd;  // halves
+    const uint32_t sc_dst = K_BYTES + V_BYTES + (lane < 16 ? 0 : 128) + (lane & 15) * 8;
+    const __half* sc_base = lane < 16 ? p.k_scales : p.v_scales;
+    const size_t page_code_bytes = (size_t)p.P * row_bytes;
+    const size_t page_scale_halves = (size_t)p.P * p.scale_row_halves;
+    int slot_i = 0;      // ring slot of the next page to issue
+    // issue the asynchronous copies of page j (descriptor held by lane j % 32 of the issue window)
+    auto issue = [&](int j) {
+        if (j > 0 && (j & 31) == 0) win_i = lookup(j);
+        const int src_lane = j & 31;
+        const int page = __shfl_sync(0xffffffffu, win_i.page, src_lane);
+        const int valid = __shfl_sync(0xffffffffu, win_i.valid, src_lane);
+        if (page >= 0) {
+            uint8_t* slot = my_ring + slot_i * SLOT;
+            const uint8_t* kbase = p.k_codes + (size_t)page * page_code_bytes;
+            const uint8_t* vbase = p.v_codes + (size_t)page * page_code_bytes;
+            if (BITS == 4) {
+                // K: 16 bytes of token g and of token g + 8 ; V: 8 bytes of tokens 2t, 2t+1, 2t+8, 2t+9
+                if (g < valid) cp_async_16(slot + lane * 16, kbase + k_src0);
+                if (g + 8 < valid) cp_async_16(slot + 512 + lane * 16, kbase + k_src1);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int head = 2 * t + (e & 1);
-                    const int d = 16 * g + 2 * i + (e >> 1);
-                    if (head < group) dst[(size_t)(h * group + head) * (D + 2) + d] = o[i][e];
+                for (int i = 0; i < 4; ++i) {
+                    const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
+                    if (tok < valid) cp_async_8(slot + K_BYTES + i * 256 + lane * 8, vbase + v_src[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int tok = g + 8 * (i >> 1);
+                    if (tok < valid)
+                        cp_async_16(slot + i * 512 + lane * 16, kbase + (i >> 1 ? k_src1 : k_src0) + 64 * (i & 1));
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
+                    if (tok < valid) cp_async_16(slot + K_BYTES + i * 512 + lane * 16, vbase + v_src[i]);
                 }
             }
-            if (t == 0 && g < group) {
-                dst[(size_t)(h * group + g) * (D + 2) + D] = m_run;
-                dst[(size_t)(h * group + g) * (D + 2) + D + 1] = l0;
+            // scales of the 16 tokens for this head: lanes 0-15 K, lanes 16-31 V
+            if ((lane & 15) < valid) {
+                const __half* src = sc_base + (size_t)page * page_scale_halves + sc_src;
+                if (LOGG == 5) cp_async_8(slot + sc_dst, src);
+                else cp_async_4(slot + sc_dst, src);
             }
-        };
+        }
+        cp_async_commit();
+        slot_i = (slot_i + 1 == NS) ? 0 : slot_i + 1;
+    };
 
-        for (int f = lo, it = 0; f < hi; ++f, ++it) {
-            const int slot = it % p.stages;
-            ok = mbar_wait_bounded(&full[slot], (it / p.stages) & 1, &g_device_status, EV_ATTN_FULL_WAIT,
-                                   ok ? kAttnWaitLimit : 64u) && ok;
-            const int page = meta[slot * 4 + 0];
-            const int b = meta[slot * 4 + 1];
-            const int valid = meta[slot * 4 + 3];    // tokens of this page that exist
-            if (b != cur_b) {
-                if (cur_b >= 0) flush(cur_b);
-                cur_b = b;
-                m_run = -INFINITY;
-                l_run = 0.0f;
+    auto flush = [&](int b) {
+        float* dst = p.partial + ((size_t)((blockIdx.x + b) * subs + sub) * p.Hq) * (D + 2);
+        float l0 = l_run;
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        // O^T[d][head]: thread (g,t) holds d = 16g + 2i (+1), heads 2t, 2t+1
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 8; ++i) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
-                // Q fragments for (b, kv head h): row r of the tile is query head h*group + r
+            for (int e = 0; e < 4; ++e) {
+                const int head = 2 * t + (e & 1);
+                const int d = 16 * g + 2 * i + (e >> 1);
+                if (head < group) dst[(size_t)(h * group + head) * (D + 2) + d] = o[i][e];
+            }
+        }
+        if (t == 0 && g < group) {
+            dst[(size_t)(h * group + g) * (D + 2) + D] = m_run;
+            dst[(size_t)(h * group + g) * (D + 2) + D + 1] = l0;
+        }
+    };
+
+    // prologue: copies of the first NS - 1 pages
+    for (int j = 0; j < NS - 1; ++j) {
+        if (j < n_my) issue(j);
+        else { cp_async_commit(); slot_i = (slot_i + 1 == NS) ? 0 : slot_i + 1; }
+    }
+
+    int slot_c = 0;     // ring slot of the page being consumed
+    for (int j = 0; j < n_my; ++j) {
+        if (j > 0 && (j & 31) == 0) win_c = lookup(j);
+        const int page = __shfl_sync(0xffffffffu, win_c.page, j & 31);
+        const int b = __shfl_sync(0xffffffffu, win_c.b, j & 31);
+        const int valid = __shfl_sync(0xffffffffu, win_c.valid, j & 31);
+        // look-ahead: copies of page j + NS - 1 (an empty group keeps the count uniform at the end)
+        if (j + NS - 1 < n_my) issue(j + NS - 1);
+        else cp_async_commit();
+        cp_async_wait<NS - 1>();     // at most NS - 1 groups pending: page j has landed
+        __syncwarp();
+
+        if (b != cur_b) {
+            if (cur_b >= 0) flush(cur_b);
+            cur_b = b;
+            m_run = -INFINITY;
+            l_run = 0.0f;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+            for (int i = 0; i < 8; ++i)
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int r = g + 8 * half;
-                        uint4 u = make_uint4(0, 0, 0, 0);
-                        int d0;
-                        if (BITS == 4) d0 = 32 * t + 8 * c;
-                        else d0 = (c < 2 ? 16 * t + 8 * c : 64 + 16 * t + 8 * (c - 2));
-                        if (r < group)   // group <= 8: rows 8..15 of the tile stay zero
-                            u = *reinterpret_cast<const uint4*>(p.q + ((size_t)b * p.Hq + h * group + r) * D + d0);
-                        const uint32_t w[4] = {u.x, u.y, u.z, u.w};   // halves d0..d0+7
-                        if (BITS == 4) {
-                            // mma 2c: pairs (0,4) (1,5); mma 2c+1: pairs (2,6) (3,7)
-                            const uint32_t p04 = prmt(w[0], w[2], 0x5410), p15 = prmt(w[0], w[2], 0x7632);
-                            const uint32_t p26 = prmt(w[1], w[3], 0x5410), p37 = prmt(w[1], w[3], 0x7632);
-                            qa[2 * c][half] = p04;     qa[2 * c][2 + half] = p15;
-                            qa[2 * c + 1][half] = p26; qa[2 * c + 1][2 + half] = p37;
-                        } else {
-                            // mma 2c: codes 0..3 -> pairs (0,1) (2,3); mma 2c+1: codes 4..7
-                            qa[2 * c][half] = w[0];     qa[2 * c][2 + half] = w[1];
-                            qa[2 * c + 1][half] = w[2]; qa[2 * c + 1][2 + half] = w[3];
-                        }
+                for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
+            // Q fragments for (b, kv head h): row r of the tile is query head h*group + r (r < group <= 8)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint4 u = make_uint4(0, 0, 0, 0);
+                int d0;
+                if (BITS == 4) d0 = 32 * t + 8 * c;
+                else d0 = (c < 2 ? 16 * t + 8 * c : 64 + 16 * t + 8 * (c - 2));
+                if (g < group) u = *reinterpret_cast<const uint4*>(p.q + ((size_t)b * p.Hq + h * group + g) * D + d0);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};   // halves d0..d0+7
+                if (BITS == 4) {
+                    // mma 2c: pairs (0,4) (1,5); mma 2c+1: pairs (2,6) (3,7)
+                    qa[2 * c][0] = prmt(w[0], w[2], 0x5410);     qa[2 * c][1] = prmt(w[0], w[2], 0x7632);
+                    qa[2 * c + 1][0] = prmt(w[1], w[3], 0x5410); qa[2 * c + 1][1] = prmt(w[1], w[3], 0x7632);
+                } else {
+                    // mma 2c: codes 0..3 -> pairs (0,1) (2,3); mma 2c+1: codes 4..7
+                    qa[2 * c][0] = w[0];     qa[2 * c][1] = w[1];
+                    qa[2 * c + 1][0] = w[2]; qa[2 * c + 1][1] = w[3];
+                }
+            }
+        }
+        if (page >= 0) {
+            const uint8_t* slot = my_ring + slot_c * SLOT;
+            const __half* ksc = reinterpret_cast<const __half*>(slot + K_BYTES + V_BYTES);         // [16][4]
+            const __half* vsc = ksc + 64;                                                             // [16][4]
+
+            // ---------------- S^T = Q K^T : two n-tiles (tokens g and g + 8) ------------------
+            float s[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+                const int tok = g + 8 * nt;
+                if (BITS == 4) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(slot + nt * 512 + lane * 16);
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                    const uint32_t s2 = half_dup(__habs(ksc[tok * 4 + ((32 * t) >> LOGG)]));
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t w2 = w[c] >> 8;
+                        // exact (code - 8), then one rounding in the multiply: fp16((code-8)*s)
+                        const uint32_t v0 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                        const uint32_t v1 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                        const uint32_t v2 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                        const uint32_t v3 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                        mma_m16n8k16(s[nt], qa[2 * c][0], 0u, qa[2 * c][1], 0u, v0, v1);
+                        mma_m16n8k16(s[nt], qa[2 * c + 1][0], 0u, qa[2 * c + 1][1], 0u, v2, v3);
                     }
-                }
-            }
-            if (page >= 0) {
-                const uint8_t* slotp = ring + (size_t)slot * p.slot_bytes;
-
-                // ---------------- S^T = Q K^T : two n-tiles (tokens g and g + 8) ------------------
-                float s[2][4];
+                } else {
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
-                    const int tok = g + 8 * nt;
-                    const uint8_t* krow = slotp + p.off_k + (size_t)tok * p.k_stride + h * DP;
-                    const __half* ksc = reinterpret_cast<const __half*>(slotp + p.off_ks + (size_t)tok * p.scale_row_bytes) + h * p.Gd;
-                    if (BITS == 4) {
-                        const uint4 u = *reinterpret_cast<const uint4*>(krow + 16 * t);
+                    for (int hb = 0; hb < 2; ++hb) {
+                        const uint4 u = *reinterpret_cast<const uint4*>(slot + (2 * nt + hb) * 512 + lane * 16);
                         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-                        const uint32_t s2 = half_dup(__habs(ksc[(32 * t) / p.G]));
+                        const uint32_t s2 = half_dup(__habs(ksc[tok * 4 + ((64 * hb + 16 * t) >> LOGG)]));
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
-                            const uint32_t w2 = w[c] >> 8;
-                            // exact (code - 8), then one rounding in the multiply: fp16((code-8)*s)
-                            const uint32_t v0 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                            const uint32_t v1 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                            const uint32_t v2 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                            const uint32_t v3 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                            mma_m16n8k16(s[nt], qa[2 * c][0], qa[2 * c][1], qa[2 * c][2], qa[2 * c][3], v0, v1);
-                            mma_m16n8k16(s[nt], qa[2 * c + 1][0], qa[2 * c + 1][1], qa[2 * c + 1][2], qa[2 * c + 1][3], v2, v3);
-                        }
-                    } else {
-#pragma unroll
-                        for (int hb = 0; hb < 2; ++hb) {
-                            const uint4 u = *reinterpret_cast<const uint4*>(krow + 64 * hb + 16 * t);
-                            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-                            const uint32_t s2 = half_dup(__habs(ksc[(64 * hb + 16 * t) / p.G]));
-#pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const uint32_t v0 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4140u), 0x64806480u), s2);
-                                const uint32_t v1 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4342u), 0x64806480u), s2);
-                                const int mi = 4 * hb + c;
-                                mma_m16n8k16(s[nt], qa[mi][0], qa[mi][1], qa[mi][2], qa[mi][3], v0, v1);
-                            }
+                            const uint32_t v0 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4140u), 0x64806480u), s2);
+                            const uint32_t v1 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4342u), 0x64806480u), s2);
+                            const int mi = 4 * hb + c;
+                            mma_m16n8k16(s[nt], qa[mi][0], 0u, qa[mi][1], 0u, v0, v1);
                         }
                     }
                 }
-                // ---------------- online softmax (row g = query head g of the group; rows 8..15 are padding) ----
-                float pr[2][2];
-                float alpha;
-                {
-                    float mx = -INFINITY;
-#pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int tok = 8 * nt + 2 * t + e;
-                            float v = s[nt][e] * sm_scale;
-                            if (tok >= valid) v = -INFINITY;
-                            s[nt][e] = v;
-                            mx = fmaxf(mx, v);
-                        }
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    const float m_new = fmaxf(m_run, mx);          // finite: every staged page has a valid token
-                    alpha = exp2f((m_run - m_new) * kLog2e);       // exp(-inf) = 0 on the first page
-                    float lsum = 0.0f;
-#pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const float pv = exp2f((s[nt][e] - m_new) * kLog2e);
-                            pr[nt][e] = pv;
-                            lsum += pv;
-                        }
-                    l_run = l_run * alpha + lsum;
-                    m_run = m_new;
-                }
-                // ---------------- rescale O^T columns (heads 2t, 2t+1); alpha of head r lives in lanes g == r ----
-                {
-                    const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * t);
-                    const float a1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
-                    if (__any_sync(0xffffffffu, (a0 != 1.0f) || (a1 != 1.0f))) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            o[i][0] *= a0; o[i][1] *= a1; o[i][2] *= a0; o[i][3] *= a1;
-                        }
-                    }
-                }
-                // ---------------- O^T += V^T P ---------------------------------------------------------
-                // B operand: P[token][head]: b0b1 = tokens 2t,2t+1 ; b2b3 = tokens 2t+8,2t+9 ; column = head g
-                uint32_t pb0, pb1;
-                {
-                    const __half2 x0 = __floats2half2_rn(pr[0][0], pr[0][1]);   // tokens 2t, 2t+1
-                    const __half2 x1 = __floats2half2_rn(pr[1][0], pr[1][1]);   // tokens 2t+8, 2t+9
-                    pb0 = *reinterpret_cast<const uint32_t*>(&x0);
-                    pb1 = *reinterpret_cast<const uint32_t*>(&x1);
-                }
-                const __half* vsc = reinterpret_cast<const __half*>(slotp + p.off_vs) + h * p.Gd + (16 * g) / p.G;
-                const int srow = p.scale_row_bytes / 2;   // halves per token row of scales
-                uint32_t vreg[2][16];   // [token pair][j]: (Vhat[tokA][16g + j], Vhat[tokB][16g + j])
-#pragma unroll
-                for (int tp = 0; tp < 2; ++tp) {
-                    const int tokA = 2 * t + 8 * tp, tokB = tokA + 1;
-                    const uint8_t* ra = slotp + p.off_v + (size_t)tokA * p.v_stride + h * DP;
-                    const uint8_t* rbp = ra + p.v_stride;
-                    // slots past the end of the sequence may hold anything: their weight is 0, make the value 0 too
-                    const __half sA = tokA < valid ? __habs(vsc[(size_t)tokA * srow]) : __ushort_as_half(0);
-                    const __half sB = tokB < valid ? __habs(vsc[(size_t)tokB * srow]) : __ushort_as_half(0);
-                    const uint32_t s2 = (uint32_t)__half_as_ushort(sA) | ((uint32_t)__half_as_ushort(sB) << 16);
-                    if (BITS == 4) {
-                        const uint2 ua = *reinterpret_cast<const uint2*>(ra + 8 * g);
-                        const uint2 ub = *reinterpret_cast<const uint2*>(rbp + 8 * g);
-                        const uint32_t wa[2] = {ua.x, ua.y}, wb[2] = {ub.x, ub.y};
-#pragma unroll
-                        for (int w = 0; w < 2; ++w) {
-                            const uint32_t r0 = prmt(wa[w], wb[w], 0x5410);   // nibbles 0..3 of A | of B
-                            const uint32_t r1 = prmt(wa[w], wb[w], 0x7632);   // nibbles 4..7
-                            const uint32_t r0s = r0 >> 8, r1s = r1 >> 8;
-                            vreg[tp][8 * w + 0] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                            vreg[tp][8 * w + 1] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                            vreg[tp][8 * w + 2] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                            vreg[tp][8 * w + 3] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                            vreg[tp][8 * w + 4] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                            vreg[tp][8 * w + 5] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                            vreg[tp][8 * w + 6] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                            vreg[tp][8 * w + 7] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                        }
-                    } else {
-                        const uint4 ua = *reinterpret_cast<const uint4*>(ra + 16 * g);
-                        const uint4 ub = *reinterpret_cast<const uint4*>(rbp + 16 * g);
-                        const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
-#pragma unroll
-                        for (int w = 0; w < 4; ++w) {
-                            const uint32_t e = prmt(wa[w], wb[w], 0x5140);   // A.b0 B.b0 A.b1 B.b1
-                            const uint32_t f2 = prmt(wa[w], wb[w], 0x7362);  // A.b2 B.b2 A.b3 B.b3
-                            vreg[tp][4 * w + 0] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4140u), 0x64806480u), s2);
-                            vreg[tp][4 * w + 1] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4342u), 0x64806480u), s2);
-                            vreg[tp][4 * w + 2] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4140u), 0x64806480u), s2);
-                            vreg[tp][4 * w + 3] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4342u), 0x64806480u), s2);
-                        }
-                    }
-                }
-                // tile i: row g <-> d = 16g + 2i, row g+8 <-> d = 16g + 2i + 1
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    mma_m16n8k16(o[i], vreg[0][2 * i], vreg[0][2 * i + 1], vreg[1][2 * i], vreg[1][2 * i + 1], pb0, pb1);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
+            // ---------------- online softmax (row g = query head g of the group; rows 8..15 are padding) ----
+            float pr[2][2];
+            float alpha;
+            {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int tok = 8 * nt + 2 * t + e;
+                        float v = s[nt][e] * sm_scale;
+                        if (tok >= valid) v = -INFINITY;     // also discards whatever stale bytes sit in unused slots
+                        s[nt][e] = v;
+                        mx = fmaxf(mx, v);
+                    }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run, mx);          // finite: every staged page has a valid token
+                alpha = fast_exp2((m_run - m_new) * kLog2e);   // exp(-inf) = 0 on the first page
+                float lsum = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float pv = fast_exp2((s[nt][e] - m_new) * kLog2e);
+                        pr[nt][e] = pv;
+                        lsum += pv;
+                    }
+                l_run = l_run * alpha + lsum;
+                m_run = m_new;
+            }
+            // ---------------- rescale O^T columns (heads 2t, 2t+1); alpha of head r lives in lanes g == r ----
+            {
+                const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * t);
+                const float a1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
+                if (__any_sync(0xffffffffu, (a0 != 1.0f) || (a1 != 1.0f))) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        o[i][0] *= a0; o[i][1] *= a1; o[i][2] *= a0; o[i][3] *= a1;
+                    }
+                }
+            }
+            // ---------------- O^T += V^T P ---------------------------------------------------------
+            // B operand: P[token][head]: b0b1 = tokens 2t,2t+1 ; b2b3 = tokens 2t+8,2t+9 ; column = head g
+            uint32_t pb0, pb1;
+            {
+                const __half2 x0 = __floats2half2_rn(pr[0][0], pr[0][1]);   // tokens 2t, 2t+1
+                const __half2 x1 = __floats2half2_rn(pr[1][0], pr[1][1]);   // tokens 2t+8, 2t+9
+                pb0 = *reinterpret_cast<const uint32_t*>(&x0);
+                pb1 = *reinterpret_cast<const uint32_t*>(&x1);
+            }
+            const int vgrp = (16 * g) >> LOGG;
+            uint32_t vreg[2][16];   // [token pair][j]: (Vhat[tokA][16g + j], Vhat[tokB][16g + j])
+#pragma unroll
+            for (int tp = 0; tp < 2; ++tp) {
+                const int tokA = 2 * t + 8 * tp, tokB = tokA + 1;
+                // slots past the end of the sequence may hold anything: their weight is 0, make the value 0 too
+                const __half sA = tokA < valid ? __habs(vsc[tokA * 4 + vgrp]) : __ushort_as_half(0);
+                const __half sB = tokB < valid ? __habs(vsc[tokB * 4 + vgrp]) : __ushort_as_half(0);
+                const uint32_t s2 = (uint32_t)__half_as_ushort(sA) | ((uint32_t)__half_as_ushort(sB) << 16);
+                if (BITS == 4) {
+                    const uint2 ua = *reinterpret_cast<const uint2*>(slot + K_BYTES + (2 * tp) * 256 + lane * 8);
+                    const uint2 ub = *reinterpret_cast<const uint2*>(slot + K_BYTES + (2 * tp + 1) * 256 + lane * 8);
+                    const uint32_t wa[2] = {ua.x, ua.y}, wb[2] = {ub.x, ub.y};
+#pragma unroll
+                    for (int w = 0; w < 2; ++w) {
+                        const uint32_t r0 = prmt(wa[w], wb[w], 0x5410);   // nibbles 0..3 of A | of B
+                        const uint32_t r1 = prmt(wa[w], wb[w], 0x7632);   // nibbles 4..7
+                        const uint32_t r0s = r0 >> 8, r1s = r1 >> 8;
+                        vreg[tp][8 * w + 0] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                        vreg[tp][8 * w + 1] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                        vreg[tp][8 * w + 2] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                        vreg[tp][8 * w + 3] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                        vreg[tp][8 * w + 4] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                        vreg[tp][8 * w + 5] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                        vreg[tp][8 * w + 6] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                        vreg[tp][8 * w + 7] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                    }
+                } else {
+                    const uint4 ua = *reinterpret_cast<const uint4*>(slot + K_BYTES + (2 * tp) * 512 + lane * 16);
+                    const uint4 ub = *reinterpret_cast<const uint4*>(slot + K_BYTES + (2 * tp + 1) * 512 + lane * 16);
+                    const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const uint32_t e = prmt(wa[w], wb[w], 0x5140);   // A.b0 B.b0 A.b1 B.b1
+                        const uint32_t f2 = prmt(wa[w], wb[w], 0x7362);  // A.b2 B.b2 A.b3 B.b3
+                        vreg[tp][4 * w + 0] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4140u), 0x64806480u), s2);
+                        vreg[tp][4 * w + 1] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4342u), 0x64806480u), s2);
+                        vreg[tp][4 * w + 2] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4140u), 0x64806480u), s2);
+                        vreg[tp][4 * w + 3] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4342u), 0x64806480u), s2);
+                    }
+                }
+            }
+            // tile i: row g <-> d = 16g + 2i, row g+8 <-> d = 16g + 2i + 1
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                mma_m16n8k16(o[i], vreg[0][2 * i], vreg[0][2 * i + 1], vreg[1][2 * i], vreg[1][2 * i + 1], pb0, pb1);
         }
-        if (cur_b >= 0) flush(cur_b);
+        __syncwarp();   // every lane is done with this slot before it is refilled
+        slot_c = (slot_c + 1 == NS) ? 0 : slot_c + 1;
     }
+    if (cur_b >= 0) flush(cur_b);
 }
 
 // Merges the partials of every (sequence, query head): one warp each, lanes over d.
@@ -415,20 +471,33 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const __grid_cons
     float l_tot = 0.0f;
     if (s_hi > s_lo) {
         const int c_first = s_lo / ppc, c_last = (s_hi - 1) / ppc;
+        // (cta c, sub) wrote a partial for b iff it walked at least one page of b:
+        // pages f = lo_c + sub + j*subs inside [max(lo_c, s_lo), min(hi_c, s_hi))
+        auto wrote = [&](int c, int sub) {
+            const int lo_c = c * ppc, hi_c = min(total, lo_c + ppc);
+            const int a = max(lo_c, s_lo), e = min(hi_c, s_hi);
+            const int rel = a - lo_c - sub;
+            const int first = lo_c + sub + (rel <= 0 ? 0 : (rel + p.subs - 1) / p.subs) * p.subs;
+            return first < e;
+        };
         float m_tot = -INFINITY;
         for (int c = c_first; c <= c_last; ++c)
-            m_tot = fmaxf(m_tot, p.partial[((size_t)(c + b) * p.Hq + hq) * (D + 2) + D]);
-        for (int c = c_first; c <= c_last; ++c) {
-            const float* src = p.partial + ((size_t)(c + b) * p.Hq + hq) * (D + 2);
-            const float m = src[D];
-            const float w = (m == -INFINITY) ? 0.0f : exp2f((m - m_tot) * kLog2e);
-            l_tot += w * src[D + 1];
+            for (int sub = 0; sub < p.subs; ++sub)
+                if (wrote(c, sub))
+                    m_tot = fmaxf(m_tot, p.partial[((size_t)((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2) + D]);
+        for (int c = c_first; c <= c_last; ++c)
+            for (int sub = 0; sub < p.subs; ++sub) {
+                if (!wrote(c, sub)) continue;
+                const float* src = p.partial + ((size_t)((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2);
+                const float m = src[D];
+                const float w = (m == -INFINITY) ? 0.0f : exp2f((m - m_tot) * kLog2e);
+                l_tot += w * src[D + 1];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int d = lane + 32 * j;
-                if (d < D) acc[j] = fmaf(w, src[d], acc[j]);
+                for (int j = 0; j < 4; ++j) {
+                    const int d = lane + 32 * j;
+                    if (d < D) acc[j] = fmaf(w, src[d], acc[j]);
+                }
             }
-        }
     }
     const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
 #pragma unroll
@@ -520,18 +589,13 @@ __global__ void __launch_bounds__(128) paged_attn_simple_kernel(const __grid_con
 }
 
 inline uint32_t align_up_u32(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
-inline int pad_stride(int bytes, int mod, int rem) {
-    // smallest stride >= bytes with stride % mod == rem and stride % 16 == 0
-    int s = (bytes + 15) / 16 * 16;
-    while (s % mod != rem) s += 16;
-    return s;
-}
+inline int subs_for(int Hkv) { return (Hkv <= kAttnWarps && kAttnWarps % Hkv == 0) ? kAttnWarps / Hkv : 1; }
 
 }  // namespace
 
-size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int D) {
-    if (B <= 0 || Hq <= 0 || D <= 0) return 0;
-    return (size_t)(kMaxGrid + B) * Hq * (D + 2) * sizeof(float);
+size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int Hkv, int D) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return 0;
+    return (size_t)(kMaxGrid + B) * subs_for(Hkv) * Hq * (D + 2) * sizeof(float);
 }
 
 int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes, const void* k_scales,
@@ -551,11 +615,10 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     const int dp = bits == 4 ? D / 2 : D;
 
     const bool fast_ok = tuning_get("attn.force_simple") == 0 && D == 128 && q_dtype == B200Q_F16 &&
-                         scale_dtype == B200Q_F16 && group_size % 32 == 0 && D % group_size == 0 && group <= 8 &&
-                         Hkv <= kAttnConsumerWarps && page_size == 16 && B <= kMaxBatchFast &&
+                         scale_dtype == B200Q_F16 && (group_size == 32 || group_size == 64) && group <= 8 &&
+                         Hkv <= kAttnWarps && page_size == 16 && B <= kMaxBatchFast &&
                          ((uintptr_t)q % 16 == 0) && ((uintptr_t)k_codes % 16 == 0) && ((uintptr_t)v_codes % 16 == 0) &&
-                         ((uintptr_t)k_scales % 16 == 0) && ((uintptr_t)v_scales % 16 == 0) &&
-                         ((Hkv * dp) % 16 == 0) && ((page_size * Hkv * Gd * 2) % 16 == 0);
+                         ((uintptr_t)k_scales % 8 == 0) && ((uintptr_t)v_scales % 8 == 0);
     if (!fast_ok) {
         SimpleParams sp = {q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out,
                            B, Hq, Hkv, D, page_size, max_blocks, group_size, Gd, bits, q_dtype, scale_dtype,
@@ -564,7 +627,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
         paged_attn_simple_kernel<<<(B * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(sp);
         return finish_launch();
     }
-    if (workspace == nullptr || workspace_bytes < paged_gqa_workspace_bytes_impl(B, Hq, D)) return B200Q_ERR_WORKSPACE;
+    if (workspace == nullptr || workspace_bytes < paged_gqa_workspace_bytes_impl(B, Hq, Hkv, D)) return B200Q_ERR_WORKSPACE;
 
     AttnParams p = {};
     p.q = (const __half*)q; p.k_codes = k_codes; p.v_codes = v_codes;
@@ -572,43 +635,35 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     p.block_table = block_table; p.lengths = lengths; p.partial = (float*)workspace; p.out = out;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.P = page_size; p.max_blocks = max_blocks; p.G = group_size; p.Gd = Gd;
     p.group = group; p.num_pages = num_pages; p.scale = scale; p.q_dtype = q_dtype; p.bits = bits;
+    p.subs = subs_for(Hkv);
     p.row_bytes = Hkv * dp;
-    p.k_stride = pad_stride(p.row_bytes, 128, 64);
-    p.v_stride = pad_stride(p.row_bytes, 64, 16);
-    p.scale_row_bytes = Hkv * Gd * 2;
+    p.scale_row_halves = Hkv * Gd;
+    p.slot_bytes = (bits == 4 ? 2048 : 4096) + 256;
+    const int stages = bits == 4 ? 8 : 5;      // must match NS in the kernel
 
-    uint32_t off = 2 * kAttnMaxStages * sizeof(uint64_t);
-    p.off_meta = off; off += kAttnMaxStages * 4 * sizeof(int);
+    uint32_t off = 0;
     p.off_prefix = off; off += align_up_u32((B + 1) * sizeof(int), 16);
     off = align_up_u32(off, 128);
     p.off_ring = off;
-    uint32_t so = 0;
-    p.off_k = so; so += align_up_u32(page_size * p.k_stride, 128);
-    p.off_v = so; so += align_up_u32(page_size * p.v_stride, 128);
-    p.off_ks = so; so += align_up_u32(page_size * p.scale_row_bytes, 128);
-    p.off_vs = so; so += align_up_u32(page_size * p.scale_row_bytes, 128);
-    p.slot_bytes = so;
-    int stages = tuning_get("attn.stages");
-    if (stages <= 0) stages = 8;
-    stages = std::min(stages, kAttnMaxStages);
     const uint32_t cap = (uint32_t)max_smem_optin();
-    while (stages > 2 && off + (uint64_t)stages * p.slot_bytes > cap) --stages;
-    if (off + (uint64_t)stages * p.slot_bytes > cap) return B200Q_ERR_UNSUPPORTED;
+    if (off + (uint64_t)stages * kAttnWarps * p.slot_bytes > cap) return B200Q_ERR_UNSUPPORTED;
     p.stages = stages;
-    const uint32_t total_smem = off + stages * p.slot_bytes;
+    const uint32_t total_smem = off + stages * kAttnWarps * p.slot_bytes;
 
     int ctas_per_sm = tuning_get("attn.ctas_per_sm");
     if (ctas_per_sm <= 0) ctas_per_sm = 1;
     p.grid = std::min(kMaxGrid, sm_count() * ctas_per_sm);
 
-    auto kernel = bits == 4 ? paged_attn_kernel<4> : paged_attn_kernel<8>;
-    static bool configured[2][64] = {};
+    const bool g32 = group_size == 32;
+    auto kernel = bits == 4 ? (g32 ? paged_attn_kernel<4, 5> : paged_attn_kernel<4, 6>)
+                            : (g32 ? paged_attn_kernel<8, 5> : paged_attn_kernel<8, 6>);
+    static bool configured[2][2][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[bits == 4][dev & 63]) {
+    if (!configured[bits == 4][g32][dev & 63]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap) != cudaSuccess)
             return B200Q_ERR_LAUNCH;
-        configured[bits == 4][dev & 63] = true;
+        configured[bits == 4][g32][dev & 63] = true;
     }
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -29,13 +29,17 @@ SIGNATURES = {
     "b200q_set_tuning": (_i, [_c.c_char_p, _i]),
     "b200q_dequant": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _i, _vp]),
     "b200q_qmatvec": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _i, _i, _vp]),
+    "b200q_norm_qmatvec": (_i, [_i, _vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _i, _i,
+                                _vp]),
+    "b200q_rope_kv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i, _i,
+                                  _i, _vp]),
     "b200q_gate_up_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _vp, _vp,
                                   _i, _i64, _i64, _i, _i, _i, _vp]),
     "b200q_swiglu": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _vp]),
     "b200q_residual_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "b200q_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _i, _vp]),
     "b200q_block_table_lookup": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
-    "b200q_paged_gqa_workspace_bytes": (_sz, [_i, _i, _i]),
+    "b200q_paged_gqa_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "b200q_paged_gqa_decode": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64,
                                     _i, _i, _f, _i, _i, _vp]),
 }

@@ -292,7 +292,7 @@ def paged_attention_launch(q3d, paged_qkv, scale, out=None, workspace=None):
     ln = _cabi.contiguous(paged_qkv.lengths.reshape(B).to(torch.int32))
     if out is None:
         out = torch.empty_like(q3d)
-    nbytes = lib.b200q_paged_gqa_workspace_bytes(B, Hq, D)
+    nbytes = lib.b200q_paged_gqa_workspace_bytes(B, Hq, Hkv, D)
     if workspace is None:
         workspace = _workspace(q3d.device, nbytes)
     _cabi.check(

@@ -1,0 +1,296 @@
+"""Llama-shaped q4/q8 decode stack on the hot-path kernels: the caller side of the matvec / MLP /
+paged-attention operators for the layer-stack benchmark.
+
+One decode step per layer is six launches through the C ABI:
+  [RMSNorm + QKV matvec] -> [split + RoPE + quantised KV append] -> [paged GQA decode attention
+  (+ merge)] -> [O matvec + residual] -> [RMSNorm + gate/up + SwiGLU] -> [down matvec + residual]
+and the whole step is captured in a CUDA graph (positions and lengths live on the device and are
+advanced inside the graph).
+
+Tensor parallelism over ``tp_size`` GPUs of one node: every matrix is sharded by OUTPUT rows (QKV by
+heads, so the KV cache is sharded by kv head) and the activations are re-assembled with an NCCL
+all-gather after attention, O, SwiGLU and down.  Row sharding leaves every output element's
+arithmetic untouched, so the sharded stack is bitwise identical to the single-GPU stack.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import synth
+from .ops import _cabi
+
+
+@dataclass
+class StackConfig:
+    hidden: int = 4096
+    intermediate: int = 14336
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    vocab: int = 128256
+    bits: int = 4
+    group_size: int = 64
+    kv_bits: int = 8
+    kv_group_size: int = 32
+    page_size: int = 16
+
+    def oracle_dict(self):
+        return {"n_heads": self.n_heads, "n_kv_heads": self.n_kv_heads, "head_dim": self.head_dim,
+                "bits": self.bits, "group_size": self.group_size, "eps": self.eps}
+
+
+def rope_tables(head_dim: int, theta: float, length: int, device):
+    inv_freq = 1.0 / (float(theta) ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / float(head_dim)))
+    freqs = torch.arange(length, dtype=torch.float32, device=device).reshape(length, 1) * inv_freq.reshape(1, -1)
+    return torch.cos(freqs).contiguous(), torch.sin(freqs).contiguous()
+
+
+def shard_rows(n_rows: int, rank: int, world: int):
+    """Row range [lo, hi) of an output dimension owned by ``rank`` (equal shards)."""
+    if n_rows % world:
+        raise ValueError(f"{n_rows} rows do not split evenly over {world} ranks")
+    per = n_rows // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_layer(full: dict, cfg: StackConfig, rank: int, world: int) -> dict:
+    """Output-row shards of one layer's quantised matrices.  QKV is sharded by heads: the rank's
+    q heads, then its k heads, then its v heads, so that its fused row keeps the [q | k | v] layout."""
+    if world == 1:
+        return full
+    D = cfg.head_dim
+    hq_lo, hq_hi = shard_rows(cfg.n_heads, rank, world)
+    hk_lo, hk_hi = shard_rows(cfg.n_kv_heads, rank, world)
+    q_rows = torch.arange(hq_lo * D, hq_hi * D)
+    k_rows = cfg.n_heads * D + torch.arange(hk_lo * D, hk_hi * D)
+    v_rows = (cfg.n_heads + cfg.n_kv_heads) * D + torch.arange(hk_lo * D, hk_hi * D)
+    qkv_rows = torch.cat([q_rows, k_rows, v_rows])
+
+    def take(triple, rows):
+        return tuple(None if t is None else t[rows.to(t.device)].contiguous() for t in triple)
+
+    def take_range(triple, n):
+        lo, hi = shard_rows(n, rank, world)
+        return tuple(None if t is None else t[lo:hi].contiguous() for t in triple)
+
+    return {
+        "input_norm": full["input_norm"], "post_norm": full["post_norm"],
+        "qkv": take(full["qkv"], qkv_rows),
+        "o": take_range(full["o"], cfg.hidden),
+        "gate": take_range(full["gate"], cfg.intermediate),
+        "up": take_range(full["up"], cfg.intermediate),
+        "down": take_range(full["down"], cfg.hidden),
+    }
+
+
+def random_layer(cfg: StackConfig, seed: int, device) -> dict:
+    """Random-init layer: W ~ N(0, 0.02) quantised affine group-wise, norm weights = 1."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def qw(n, k):
+        w = torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * 0.02
+        return synth.quantize_affine(w, cfg.bits, cfg.group_size)
+
+    D = cfg.head_dim
+    return {
+        "input_norm": torch.ones(cfg.hidden, dtype=torch.float16, device=device),
+        "post_norm": torch.ones(cfg.hidden, dtype=torch.float16, device=device),
+        "qkv": qw((cfg.n_heads + 2 * cfg.n_kv_heads) * D, cfg.hidden),
+        "o": qw(cfg.hidden, cfg.n_heads * D),
+        "gate": qw(cfg.intermediate, cfg.hidden),
+        "up": qw(cfg.intermediate, cfg.hidden),
+        "down": qw(cfg.hidden, cfg.intermediate),
+    }
+
+
+class PagedKV:
+    """Per-layer quantised page pool of the local kv heads plus the shared block table."""
+
+    def __init__(self, cfg: StackConfig, n_kv_local: int, num_pages: int, device):
+        D, P = cfg.head_dim, cfg.page_size
+        dp = D // 2 if cfg.kv_bits == 4 else D
+        gd = D // cfg.kv_group_size
+        self.k_codes = torch.zeros((num_pages, P, n_kv_local, dp), dtype=torch.uint8, device=device)
+        self.v_codes = torch.zeros_like(self.k_codes)
+        self.k_scales = torch.zeros((num_pages, P, n_kv_local, gd), dtype=torch.float16, device=device)
+        self.v_scales = torch.zeros_like(self.k_scales)
+
+    def fill_random(self, cfg: StackConfig, seed: int):
+        """Pre-fill with K/V ~ N(0,1) quantised by the cache rule (context that was 'already decoded')."""
+        dev = self.k_codes.device
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        shape = (*self.k_codes.shape[:3], cfg.head_dim)
+        for codes, scales in ((self.k_codes, self.k_scales), (self.v_codes, self.v_scales)):
+            vals = torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)
+            c, s = synth.quantize_kv_symmetric(vals, cfg.kv_bits, cfg.kv_group_size)
+            codes.copy_(c)
+            scales.copy_(s)
+
+
+class DecodeStack:
+    """Runs decode steps of ``cfg.n_layers`` layers on one GPU (or one tensor-parallel rank)."""
+
+    def __init__(self, cfg: StackConfig, layers, final_norm, embedding, batch: int, max_context: int, device,
+                 tp_rank: int = 0, tp_size: int = 1, process_group=None):
+        self.cfg, self.B, self.device = cfg, batch, device
+        self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
+        self.lib = _cabi.load()
+        self.layers = [shard_layer(l, cfg, tp_rank, tp_size) for l in layers]
+        self.final_norm, self.embedding = final_norm, embedding
+        self.hq = cfg.n_heads // tp_size
+        self.hkv = cfg.n_kv_heads // tp_size
+        if cfg.n_heads % tp_size or cfg.n_kv_heads % tp_size:
+            raise ValueError("heads must split evenly over the tensor-parallel ranks")
+        P = cfg.page_size
+        self.max_blocks = (max_context + P - 1) // P
+        self.num_pages = batch * self.max_blocks
+        self.block_table = torch.arange(self.num_pages, dtype=torch.int32, device=device).reshape(batch, self.max_blocks)
+        self.caches = [PagedKV(cfg, self.hkv, self.num_pages, device) for _ in range(cfg.n_layers)]
+        self.positions = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.lengths = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.cos, self.sin = rope_tables(cfg.head_dim, cfg.rope_theta, max_context, device)
+        f16 = dict(dtype=torch.float16, device=device)
+        D = cfg.head_dim
+        self.h = torch.zeros((batch, cfg.hidden), **f16)
+        self.h2 = torch.zeros((batch, cfg.hidden), **f16)
+        self.qkv = torch.zeros((batch, (self.hq + 2 * self.hkv) * D), **f16)
+        self.q_rot = torch.zeros((batch, self.hq * D), **f16)
+        self.attn = torch.zeros((batch, self.hq * D), **f16)
+        self.act = torch.zeros((batch, cfg.intermediate // tp_size), **f16)
+        self.out = torch.zeros((batch, cfg.hidden), **f16)
+        if tp_size > 1:
+            self.o_loc = torch.zeros((batch, cfg.hidden // tp_size), **f16)
+            self.gather_attn = torch.zeros((tp_size, batch, self.hq * D), **f16)
+            self.gather_h = torch.zeros((tp_size, batch, cfg.hidden // tp_size), **f16)
+            self.gather_act = torch.zeros((tp_size, batch, cfg.intermediate // tp_size), **f16)
+            self.attn_full = torch.zeros((batch, cfg.n_heads * D), **f16)
+            self.act_full = torch.zeros((batch, cfg.intermediate), **f16)
+        ws_bytes = self.lib.b200q_paged_gqa_workspace_bytes(batch, self.hq, self.hkv, D)
+        self.workspace = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+        self.token_ids = torch.zeros(batch, dtype=torch.int64, device=device)
+        self.graph = None
+        self.launches_per_step = 0
+
+    # -- context management ------------------------------------------------------------------
+    def set_context(self, context_len: int, seed: int = 0):
+        """Pretend ``context_len`` tokens were already decoded: random quantised KV, positions = context_len."""
+        for i, c in enumerate(self.caches):
+            c.fill_random(self.cfg, seed + 131 * i + self.tp_rank)
+        self.positions.fill_(context_len)
+        self.lengths.fill_(context_len + 1)
+
+    # -- one decode step -----------------------------------------------------------------------
+    def _all_gather_rows(self, local, gathered, full=None):
+        """[B, n_loc] on every rank -> [B, tp * n_loc] in rank-major column order."""
+        import torch.distributed as dist
+        dist.all_gather_into_tensor(gathered, local, group=self.pg)
+        out = gathered.permute(1, 0, 2).reshape(local.shape[0], -1)
+        if full is not None:
+            full.copy_(out)
+            return full
+        return out
+
+    def _launch_step(self):
+        cfg, lib, B = self.cfg, self.lib, self.B
+        st = torch.cuda.current_stream().cuda_stream
+        D, G, bits = cfg.head_dim, cfg.group_size, cfg.bits
+        F16, ck = _cabi.F16, _cabi.check
+        n = 0
+        torch.index_select(self.embedding, 0, self.token_ids, out=self.h)
+        for w, cache in zip(self.layers, self.caches):
+            qw, qs, qz = w["qkv"]
+            ck(lib.b200q_norm_qmatvec(bits, self.h.data_ptr(), None, w["input_norm"].data_ptr(), F16, cfg.eps, None, None,
+                                      qw.data_ptr(), qs.data_ptr(), qz.data_ptr(), None, self.qkv.data_ptr(), B,
+                                      qw.shape[0], cfg.hidden, G, F16, F16, st), "norm_qmatvec")
+            ck(lib.b200q_rope_kv_append(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                        self.positions.data_ptr(), self.block_table.data_ptr(), self.q_rot.data_ptr(),
+                                        cache.k_codes.data_ptr(), cache.v_codes.data_ptr(), cache.k_scales.data_ptr(),
+                                        cache.v_scales.data_ptr(), cfg.kv_bits, B, self.hq, self.hkv, D, cfg.page_size,
+                                        self.num_pages, self.max_blocks, cfg.kv_group_size, self.cos.shape[0], st),
+               "rope_kv_append")
+            ck(lib.b200q_paged_gqa_decode(cfg.kv_bits, self.q_rot.data_ptr(), cache.k_codes.data_ptr(),
+                                          cache.v_codes.data_ptr(), cache.k_scales.data_ptr(), cache.v_scales.data_ptr(),
+                                          self.block_table.data_ptr(), self.lengths.data_ptr(), self.attn.data_ptr(),
+                                          self.workspace.data_ptr(), self.workspace.numel(), B, self.hq, self.hkv, D,
+                                          cfg.page_size, self.num_pages, self.max_blocks, cfg.kv_group_size,
+                                          1.0 / math.sqrt(D), F16, F16, st), "paged_gqa_decode")
+            ow, os_, oz = w["o"]
+            gw, gs, gz = w["gate"]
+            uw, us, uz = w["up"]
+            dw, ds, dz = w["down"]
+            if self.tp_size == 1:
+                ck(lib.b200q_qmatvec(bits, self.attn.data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(),
+                                     self.h.data_ptr(), self.h2.data_ptr(), B, cfg.hidden, cfg.n_heads * D, G, F16, F16, st),
+                   "o_proj")
+                ck(lib.b200q_gate_up_swiglu(bits, self.h2.data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
+                                            us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, self.act.data_ptr(),
+                                            None, w["post_norm"].data_ptr(), F16, cfg.eps, None, None, B,
+                                            cfg.intermediate, cfg.hidden, G, F16, F16, st), "gate_up")
+                ck(lib.b200q_qmatvec(bits, self.act.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
+                                     self.h2.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.intermediate, G, F16, F16, st),
+                   "down_proj")
+                n += 7
+            else:
+                attn_full = self._all_gather_rows(self.attn, self.gather_attn, self.attn_full)
+                ck(lib.b200q_qmatvec(bits, attn_full.data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
+                                     self.o_loc.data_ptr(), B, ow.shape[0], cfg.n_heads * D, G, F16, F16, st), "o_proj")
+                o_full = self._all_gather_rows(self.o_loc, self.gather_h)
+                torch.add(self.h, o_full, out=self.h2)                       # cast(h + o), the layer's residual add
+                ck(lib.b200q_gate_up_swiglu(bits, self.h2.data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
+                                            us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, self.act.data_ptr(),
+                                            None, w["post_norm"].data_ptr(), F16, cfg.eps, None, None, B, gw.shape[0],
+                                            cfg.hidden, G, F16, F16, st), "gate_up")
+                act_full = self._all_gather_rows(self.act, self.gather_act, self.act_full)
+                ck(lib.b200q_qmatvec(bits, act_full.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(), None,
+                                     self.o_loc.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
+                d_full = self._all_gather_rows(self.o_loc, self.gather_h)
+                torch.add(self.h2, d_full, out=self.h)
+                n += 7
+        ck(lib.b200q_rmsnorm_residual(self.h.data_ptr(), None, self.final_norm.data_ptr(), self.out.data_ptr(), None, B,
+                                      cfg.hidden, cfg.eps, F16, _cabi.dtype_code(self.final_norm.dtype), st), "final_norm")
+        self.positions.add_(1)
+        self.lengths.add_(1)
+        self.launches_per_step = n + 1
+        return self.out
+
+    def capture(self):
+        """Captures one decode step in a CUDA graph (after one eager warm-up step, whose effect on the
+        positions is undone)."""
+        pos, ln = self.positions.clone(), self.lengths.clone()
+        self._launch_step()
+        torch.cuda.synchronize()
+        self.positions.copy_(pos)
+        self.lengths.copy_(ln)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._launch_step()
+        self.positions.copy_(pos)
+        self.lengths.copy_(ln)
+        return self.graph
+
+    def step(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """token_ids [B] (device) -> final-normed hidden state [B, hidden]."""
+        self.token_ids.copy_(token_ids)
+        if self.graph is not None:
+            self.graph.replay()
+            return self.out
+        return self._launch_step()
+
+    def weight_bytes_per_step(self) -> int:
+        total = 0
+        for w in self.layers:
+            for key in ("qkv", "o", "gate", "up", "down"):
+                total += sum(t.numel() * t.element_size() for t in w[key] if t is not None)
+        return total
+
+    def kv_bytes_per_step(self, context_len: int) -> int:
+        cfg = self.cfg
+        dp = cfg.head_dim // 2 if cfg.kv_bits == 4 else cfg.head_dim
+        per_tok = 2 * (dp + (cfg.head_dim // cfg.kv_group_size) * 2) * self.hkv
+        return cfg.n_layers * self.B * context_len * per_tok
