@@ -42,7 +42,7 @@ constexpr int kConsumerWarps = 16;           // the reduction below assumes 16
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kTileRows = 16;
-constexpr int kMaxBlockTiles = 2;             // tiles whose accumulators stay live across activation chunks
+constexpr int kMaxBlockTiles = 4;             // tiles of a row block (one constants pass, one reduction)
 constexpr int kRowPad = 64;                   // stage row stride = chunk bytes + 64: conflict-free 16-byte reads
 constexpr uint32_t kWaitLimit = 1u << 21;
 constexpr int kMaxStages = 8;
@@ -76,8 +76,8 @@ struct GemvParams {
     int logG;               // group size is a power of two on the fast path
     int meta_by_tma;        // scales / zeros are fp16 and 16-byte aligned per tile: bulk-copied with the tile
     int rows_lo, rem;       // CTA c owns rows_lo (+1 if c < rem) rows
-    uint32_t off_xperm, off_xsum, off_xscale, off_slots, off_red, off_ring;
-    uint32_t stage_bytes, row_stride, stage_meta_off, slots_buf_elems, red_buf_elems;
+    uint32_t off_xperm, off_xsum, off_xscale, off_slots, off_red, off_meta, off_ring;
+    uint32_t stage_bytes, row_stride, slots_buf_elems, red_buf_elems;
 };
 
 // ---- activation source: 8 consecutive values of batch row b at k, as the reference would hold them --------
@@ -159,11 +159,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     constexpr int NMMA = BITS == 4 ? 8 : 4;      // tensor-core instructions per k-step and tile
     constexpr int CH = NMMA / 2;                 // 16-byte activation chunks per k-step, thread and batch row
     constexpr int KT = KS / 4;                   // k owned by one thread of a quad in a k-step
+    constexpr int MAXTB = kMaxBlockTiles / (MATS * NT);   // accumulator tiles kept in registers: 16 floats in all
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
+    uint64_t* meta_full = empty + kMaxStages;    // [2]
+    uint64_t* meta_empty = meta_full + 2;        // [2]
 
     const int cta = blockIdx.x;
     const int r_lo = cta * p.rows_lo + min(cta, p.rem);
@@ -171,14 +174,20 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int r_hi = r_lo + r_cnt;
     const int n_tiles = (r_cnt + kTileRows - 1) / kTileRows;
     const int TB = p.block_tiles;
+    const int TBR = TB * kTileRows;              // rows of a full row block
     const int n_rb = (n_tiles + TB - 1) / TB;
     const int n_xc = (p.K + p.xk - 1) / p.xk;
     const int kc_per_xc = p.xk / p.kc;           // ring stages per (matrix, tile, activation chunk)
+    const int Gn = p.Gn;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kConsumerWarps);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&meta_full[s], 1);
+            mbar_init(&meta_empty[s], kConsumerWarps);
         }
         mbar_fence_init();
     }
@@ -186,15 +195,42 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     pdl_launch_dependents();
 
     uint8_t* ring = smem + p.off_ring;
+    uint8_t* raw_meta = smem + p.off_meta;       // [2 buffers][MATS][scales | zeros][TBR][Gn] halves
+    const uint32_t raw_mat_bytes = (uint32_t)2 * TBR * Gn * 2;
+    const uint32_t raw_buf_bytes = MATS * raw_mat_bytes;
 
     // Both sides walk the stages in the same order: row block, activation chunk, tile, matrix, k-chunk.
     if (warp == kConsumerWarps) {
         // ------------------------------ producer warp ------------------------------------------
         bool ok = true;
         int p_slot = 0;
-        uint32_t p_phase = 1;            // first pass over the ring does not wait
+        uint32_t p_phase = 1;
         bool first_pass = true;
         for (int rb = 0; rb < n_rb; ++rb) {
+            const int brow0 = r_lo + rb * TBR;
+            const int brows = min(TBR, r_hi - brow0);
+            if (p.meta_by_tma) {
+                // scales / zero points of the whole row block: contiguous over rows, one copy each
+                const int mb = rb & 1;
+                if (rb >= 2)
+                    ok = mbar_wait_bounded(&meta_empty[mb], ((rb >> 1) - 1) & 1, &g_device_status, EV_GEMV_EMPTY_WAIT,
+                                           ok ? kWaitLimit : 64u) && ok;
+                const uint32_t bytes = (uint32_t)brows * Gn * 2;
+                if (lane == 0) {
+                    uint32_t tx = 0;
+                    for (int m = 0; m < MATS; ++m) tx += bytes * (p.z[m] != nullptr ? 2 : 1);
+                    mbar_arrive_expect_tx(&meta_full[mb], tx);
+                }
+                __syncwarp();
+                if (lane < 2 * MATS) {
+                    const int m = lane >> 1;
+                    const bool is_z = lane & 1;
+                    const void* src = is_z ? p.z[m] : p.s[m];
+                    if (src != nullptr)
+                        bulk_g2s(raw_meta + mb * raw_buf_bytes + m * raw_mat_bytes + (is_z ? TBR * Gn * 2 : 0),
+                                 reinterpret_cast<const uint8_t*>(src) + (size_t)brow0 * Gn * 2, bytes, &meta_full[mb]);
+                }
+            }
             for (int xc = 0; xc < n_xc; ++xc) {
                 const int c_begin = xc * kc_per_xc;
                 const int c_end = min(p.n_kc, c_begin + kc_per_xc);
@@ -211,28 +247,12 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                             const int k0 = c * p.kc;
                             const int kcur = min(p.kc, p.K - k0);
                             const uint32_t bytes_row = (uint32_t)(kcur * BITS / 8);
-                            const bool with_meta = (c == 0) && p.meta_by_tma;
-                            const uint32_t meta_bytes = (uint32_t)rows * p.Gn * 2;
                             uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-                            if (lane == 0) {
-                                uint32_t tx = bytes_row * rows;
-                                if (with_meta) tx += meta_bytes * (p.z[m] != nullptr ? 2 : 1);
-                                mbar_arrive_expect_tx(&full[slot], tx);
-                            }
+                            if (lane == 0) mbar_arrive_expect_tx(&full[slot], bytes_row * rows);
                             __syncwarp();
                             if (lane < rows) {
                                 const uint8_t* src = p.w[m] + (size_t)(row0 + lane) * p.row_bytes + (size_t)k0 * BITS / 8;
                                 bulk_g2s(stage + (size_t)lane * p.row_stride, src, bytes_row, &full[slot]);
-                            }
-                            if (with_meta) {
-                                if (lane == 16)
-                                    bulk_g2s(stage + p.stage_meta_off,
-                                             reinterpret_cast<const uint8_t*>(p.s[m]) + (size_t)row0 * p.Gn * 2, meta_bytes,
-                                             &full[slot]);
-                                if (lane == 17 && p.z[m] != nullptr)
-                                    bulk_g2s(stage + p.stage_meta_off + kTileRows * p.Gn * 2,
-                                             reinterpret_cast<const uint8_t*>(p.z[m]) + (size_t)row0 * p.Gn * 2, meta_bytes,
-                                             &full[slot]);
                             }
                         }
                     }
@@ -248,34 +268,30 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int g = lane >> 2;
     const int t = lane & 3;
     const int B = p.B;
-    const int Gn = p.Gn;
 
     uint8_t* xperm = smem + p.off_xperm;
     float* xsum_e = reinterpret_cast<float*>(smem + p.off_xsum);      // [Gn][B] sums over even k (all k for q8)
     float* xsum_o = xsum_e + Gn * B;                                  // [Gn][B] sums over odd k
     float* xscale = reinterpret_cast<float*>(smem + p.off_xscale);    // [B]: 2^e ; [B..2B): inv_rms
-    uint2* slots_base = reinterpret_cast<uint2*>(smem + p.off_slots); // [2][MATS][TB][16][Gn] dequant constants
-    float* red_base = reinterpret_cast<float*>(smem + p.off_red);     // [2]{ red [MATS][TB][16][B][W] ; corr [MATS][TB][16][B] }
+    uint2* slots_base = reinterpret_cast<uint2*>(smem + p.off_slots); // [2][MATS][TBR][Gn] dequant constants
+    float* red_base = reinterpret_cast<float*>(smem + p.off_red);     // [2]{ red [MATS][TBR][B][W] ; corr [MATS][TBR][B] }
     const bool has_zero = (p.z[0] != nullptr) || (MATS == 2 && p.z[1] != nullptr);
 
     // Dequant constants of one (row, group): the kernel computes fp16((off + q) * s + c) with
     // c = fp16(-(off + zr) * s), zr = rint(zero), off = 1024 (even k / q8) or 64 (odd k, q4): the
     // fused multiply-add rounds (q - zr) * s + e once, where e = c + (off + zr) * s is the (exactly
-    // known) rounding error of c.  e and the fractional part of the zero point go into the fp32
-    // correction term of the epilogue.  Slot = {s, c1024, c64, zero} as four halves; built with
-    // fp16 arithmetic only (off + zr is an exact integer, the product is rounded once).
-    // The correction coefficients (ke, ko) = (z - zr) * s + e are also formed here, in fp16: e is the
-    // rounding error of an fp16 product and therefore exact in fp16; (z - zr) is exact; only the small
-    // product (z - zr) * s is rounded (relative 2^-11 of at most half a quantisation step).
-    auto make_slot = [&](__half s16, __half z16, uint32_t& kk) -> uint2 {
+    // known) rounding error of c.  The zero-point term of the epilogue uses (ke, ko) = (z - zr) * s + e,
+    // formed here in fp16: e is the rounding error of an fp16 product and therefore exact in fp16,
+    // (z - zr) is exact, and only the small product (z - zr) * s is rounded.
+    auto make_slot = [&](__half s16, __half z16, float& ke, float& ko) -> uint2 {
         const __half2 z2 = __half2half2(z16);
         const __half2 s2 = __half2half2(s16);
         const __half2 zr2 = __hmax2(__hmin2(h2rint(z2), __float2half2_rn(512.0f)), __float2half2_rn(-512.0f));
         const __half2 a2 = __hadd2(zr2, __halves2half2(__float2half_rn(1024.0f), __float2half_rn(64.0f)));
         const __half2 c2 = __hneg2(__hmul2(a2, s2));                                    // (c1024, c64)
-        const __half2 e2 = __hfma2(a2, s2, c2);                                         // exact rounding errors
-        const __half2 k2 = __hfma2(__hsub2(z2, zr2), s2, e2);                           // (ke, ko)
-        kk = *reinterpret_cast<const uint32_t*>(&k2);
+        const __half2 k2 = __hfma2(__hsub2(z2, zr2), s2, __hfma2(a2, s2, c2));          // (ke, ko)
+        ke = __low2float(k2);
+        ko = __high2float(k2);
         uint2 v;
         v.x = (uint32_t)__half_as_ushort(s16) | ((uint32_t)__half_as_ushort(__low2half(c2)) << 16);
         v.y = (uint32_t)__half_as_ushort(__high2half(c2));
@@ -322,6 +338,30 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         }
         named_bar_sync(1, kConsumerThreads);
     }
+    const int logG = p.logG;
+    if (has_zero) {
+        // per-group sums of the activations exactly as the tensor cores will see them (scaled, fp16):
+        // over even k and odd k separately for q4 (the two nibble positions use different offsets)
+        for (int i = ctid; i < Gn * B; i += kConsumerThreads) {
+            const int gi = i / B;
+            const int b = i - gi * B;
+            const float inv = need_row_pass ? xscale[B + b] : 1.0f;
+            const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
+            float se = 0.0f, so = 0.0f;
+            for (int kk = gi << logG; kk < ((gi + 1) << logG); kk += 8) {
+                float v[8];
+                load8_act(p, b, kk, inv, false, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float h = __half2float(__float2half_rn(v[j] * down));
+                    if (BITS == 4 && (j & 1)) so += h; else se += h;
+                }
+            }
+            xsum_e[i] = se;
+            xsum_o[i] = so;
+        }
+        named_bar_sync(1, kConsumerThreads);
+    }
 
     bool ok = true;
     int buf = 0;
@@ -334,26 +374,76 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     uint32_t x_nt[NT];                                                // byte offset of this lane's batch row per n-tile
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) x_nt[nt] = (uint32_t)min(nt * 8 + g, B - 1) * 64;
-    const int logG = p.logG;
     const int n_stages = p.stages;
     const uint32_t stage_bytes = p.stage_bytes;
     int c_slot = 0;                  // ring slot and phase parity of the stage the consumer is at
     uint32_t c_phase = 0;
 
+#pragma unroll 1
     for (int rb = 0; rb < n_rb; ++rb, buf ^= 1) {
         const int tile_begin = rb * TB;
         const int tile_end = min(n_tiles, tile_begin + TB);
-        uint2* slots = slots_base + (size_t)buf * p.slots_buf_elems;      // [MATS][TB][16][Gn] {s, c1024, c64, -}
-        uint32_t* kks = reinterpret_cast<uint32_t*>(slots_base + 2 * (size_t)p.slots_buf_elems) +
-                        (size_t)buf * p.slots_buf_elems;                  // [MATS][TB][16][Gn] (ke, ko) halves
-        float* red = red_base + (size_t)buf * p.red_buf_elems;            // [MATS][TB][16][B][W] then corr [MATS][TB][16][B]
-        float* corr = red + (size_t)MATS * TB * kTileRows * B * kConsumerWarps;
+        const int brow0 = r_lo + rb * TBR;
+        const int block_rows = min(TBR, r_hi - brow0);
+        uint2* slots = slots_base + (uint32_t)buf * p.slots_buf_elems;    // [MATS][TBR][Gn]
+        float* red = red_base + (uint32_t)buf * p.red_buf_elems;          // [MATS][TBR][B][W] then corr [MATS][TBR][B]
+        float* corr = red + (uint32_t)MATS * TBR * B * kConsumerWarps;
 
-        float acc[MATS][kMaxBlockTiles][NT][4];
+        // ---- dequant constants and zero-point term of the row block: warp per row, lanes over groups ----
+        {
+            const int mb = rb & 1;
+            const __half* raw = reinterpret_cast<const __half*>(raw_meta + mb * raw_buf_bytes);
+            if (p.meta_by_tma)
+                ok = mbar_wait_bounded(&meta_full[mb], (rb >> 1) & 1, &g_device_status, EV_GEMV_FULL_WAIT,
+                                       ok ? kWaitLimit : 64u) && ok;
+            for (int rr = cw; rr < block_rows; rr += kConsumerWarps) {
+#pragma unroll
+                for (int m = 0; m < MATS; ++m) {
+                    const bool hz = p.z[m] != nullptr;
+                    const __half* rs = raw + (uint32_t)m * 2 * TBR * Gn + (uint32_t)rr * Gn;
+                    const __half* rz = rs + (uint32_t)TBR * Gn;
+                    const int64_t grow = (int64_t)(brow0 + rr) * Gn;
+                    uint2* dst = slots + ((uint32_t)m * TBR + rr) * Gn;
+                    float part[NT * 8];
+#pragma unroll
+                    for (int b = 0; b < NT * 8; ++b) part[b] = 0.0f;
+                    for (int gi = lane; gi < Gn; gi += 32) {
+                        __half s16, z16 = __ushort_as_half(0);
+                        if (p.meta_by_tma) {
+                            s16 = rs[gi];
+                            if (hz) z16 = rz[gi];
+                        } else {
+                            s16 = __float2half_rn(load_as_f32(p.s[m], p.scale_dtype, grow + gi));
+                            if (hz) z16 = __float2half_rn(load_as_f32(p.z[m], p.scale_dtype, grow + gi));
+                        }
+                        float ke, ko;
+                        dst[gi] = make_slot(s16, z16, ke, ko);
+                        if (hz) {
+#pragma unroll
+                            for (int b = 0; b < NT * 8; ++b)
+                                if (b < B) part[b] = fmaf(ke, xsum_e[gi * B + b], fmaf(ko, xsum_o[gi * B + b], part[b]));
+                        }
+                    }
+                    if (has_zero) {
+#pragma unroll
+                        for (int b = 0; b < NT * 8; ++b) {
+                            if (b < B) {
+                                const float sum = warp_sum(part[b]);
+                                if (lane == 0) corr[((uint32_t)m * TBR + rr) * B + b] = sum;
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (p.meta_by_tma && lane == 0) mbar_arrive(&meta_empty[mb]);
+        }
+
+        float acc[MATS][MAXTB][NT][4];
 #pragma unroll
         for (int m = 0; m < MATS; ++m)
 #pragma unroll
-            for (int tb = 0; tb < kMaxBlockTiles; ++tb)
+            for (int tb = 0; tb < MAXTB; ++tb)
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -394,78 +484,19 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         out.z = __half_as_ushort(h[4]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
                         out.w = __half_as_ushort(h[6]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
                     }
-                    *reinterpret_cast<uint4*>(xperm + ((size_t)((ksx * CH + c) * B + b) * 4 + tt) * 16) = out;
-                }
-                named_bar_sync(1, kConsumerThreads);
-                if (has_zero && rb == 0) {
-                    // per-group sums of the staged (fp16) activations for the zero-point term; they are read
-                    // only after a later barrier (the one that publishes the dequant constants)
-                    const int g0 = xk0 >> logG;
-                    const int gn = xkn >> logG;
-                    for (int i = ctid; i < gn * B; i += kConsumerThreads) {
-                        const int gi = i / B;
-                        const int b = i - gi * B;
-                        float se = 0.0f, so = 0.0f;
-                        for (int kk = gi << logG; kk < ((gi + 1) << logG); kk += 8) {
-                            const int ksx = kk / KS;
-                            const int rem = kk - ksx * KS;
-                            const int tt = rem / KT;
-                            const int c = (rem - tt * KT) / 8;
-                            const uint4 u = *reinterpret_cast<const uint4*>(
-                                xperm + ((size_t)((ksx * CH + c) * B + b) * 4 + tt) * 16);
-                            const __half2 h0 = *reinterpret_cast<const __half2*>(&u.x);
-                            const __half2 h1 = *reinterpret_cast<const __half2*>(&u.y);
-                            const __half2 h2 = *reinterpret_cast<const __half2*>(&u.z);
-                            const __half2 h3 = *reinterpret_cast<const __half2*>(&u.w);
-                            const float a0 = __low2float(h0) + __high2float(h0), a1 = __low2float(h1) + __high2float(h1);
-                            const float a2 = __low2float(h2) + __high2float(h2), a3 = __low2float(h3) + __high2float(h3);
-                            if (BITS == 4) {            // registers 0 and 2 hold even k, 1 and 3 odd k
-                                se += a0 + a2;
-                                so += a1 + a3;
-                            } else {
-                                se += (a0 + a1) + (a2 + a3);
-                            }
-                        }
-                        xsum_e[(g0 + gi) * B + b] = se;
-                        xsum_o[(g0 + gi) * B + b] = so;
-                    }
+                    *reinterpret_cast<uint4*>(xperm + ((uint32_t)((ksx * CH + c) * B + b) * 4 + tt) * 16) = out;
                 }
             }
+            if (xc == 0 || n_xc > 1) named_bar_sync(1, kConsumerThreads);   // constants / activations visible
 
             const int c_begin = xc * kc_per_xc;
             const int c_end = min(p.n_kc, c_begin + kc_per_xc);
 #pragma unroll
-            for (int tb = 0; tb < kMaxBlockTiles; ++tb) {
-                const int tl = tile_begin + tb;
-                if (tl < tile_end) {
-                    const int row0 = r_lo + tl * kTileRows;
-                    const int rows = min(kTileRows, r_hi - row0);
+            for (int tb = 0; tb < MAXTB; ++tb) {
+                if (tile_begin + tb < tile_end) {
 #pragma unroll
                     for (int m = 0; m < MATS; ++m) {
-                        uint2* tslots = slots + (size_t)(m * TB + tb) * kTileRows * Gn;
-                        uint32_t* tkk = kks + (size_t)(m * TB + tb) * kTileRows * Gn;
-                        if (xc == 0) {
-                            // ---- dequant constants of this (matrix, tile): from the scales / zeros that were
-                            //      bulk-copied with its first stage, or straight from global memory ----
-                            if (p.meta_by_tma) {
-                                ok = mbar_wait_bounded(&full[c_slot], c_phase, &g_device_status,
-                                                       EV_GEMV_FULL_WAIT, ok ? kWaitLimit : 64u) && ok;
-                                const __half* rs = reinterpret_cast<const __half*>(ring + (size_t)c_slot * stage_bytes + p.stage_meta_off);
-                                const __half* rz = rs + kTileRows * Gn;
-                                const bool hz = p.z[m] != nullptr;
-                                for (int i = ctid; i < rows * Gn; i += kConsumerThreads)
-                                    tslots[i] = make_slot(rs[i], hz ? rz[i] : __ushort_as_half(0), tkk[i]);
-                            } else {
-                                for (int i = ctid; i < rows * Gn; i += kConsumerThreads) {
-                                    const int64_t gidx = (int64_t)row0 * Gn + i;
-                                    tslots[i] = make_slot(__float2half_rn(load_as_f32(p.s[m], p.scale_dtype, gidx)),
-                                                          p.z[m] != nullptr ? __float2half_rn(load_as_f32(p.z[m], p.scale_dtype, gidx))
-                                                                            : __ushort_as_half(0), tkk[i]);
-                                }
-                            }
-                            named_bar_sync(1, kConsumerThreads);     // constants visible to every warp
-                        }
-                        const uint2* slotsA = tslots + g * Gn;
+                        const uint2* slotsA = slots + ((uint32_t)m * TBR + tb * kTileRows + g) * Gn;
                         const uint2* slotsB = slotsA + 8 * Gn;
 #pragma unroll 1
                         for (int c = c_begin; c < c_end; ++c) {
@@ -476,8 +507,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                             const int k0 = c * p.kc;
                             const int kcur = min(p.kc, p.K - k0);
                             const int nks = kcur / KS;
-                            const uint8_t* stage_w = ring + (size_t)slot * stage_bytes + w_off;
-                            const uint8_t* xbase = xperm + (size_t)((k0 - xk0) / KS) * CH * x_step + x_lane;
+                            const uint8_t* stage_w = ring + (uint32_t)slot * stage_bytes + w_off;
+                            const uint8_t* xbase = xperm + (uint32_t)((k0 - xk0) / KS) * CH * x_step + x_lane;
 #pragma unroll 1
                             for (int ksl = cw; ksl < nks; ksl += kConsumerWarps) {
                                 const int gi = (k0 + ksl * KS + t * KT) >> logG;
@@ -491,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                                 sb.s2 = prmt(kb.x, kb.x, 0x1010); sb.c1024 = prmt(kb.x, kb.x, 0x3232); sb.c64 = prmt(kb.y, kb.y, 0x1010);
                                 const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w};
                                 const uint32_t wb[4] = {ub.x, ub.y, ub.z, ub.w};
-                                const uint8_t* xk = xbase + (size_t)ksl * CH * x_step;
+                                const uint8_t* xk = xbase + (uint32_t)ksl * CH * x_step;
 #pragma unroll
                                 for (int ch = 0; ch < CH; ++ch) {
                                     // A fragments of MMA 2ch and 2ch+1
@@ -528,53 +559,21 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             }
         }
 
-        // ---- partial tiles -> shared memory, layout [m][tb][row][b][warp] ----
+        // ---- partial tiles -> shared memory, layout [m][row][b][warp] ----
 #pragma unroll
         for (int m = 0; m < MATS; ++m)
 #pragma unroll
-            for (int tb = 0; tb < kMaxBlockTiles; ++tb)
+            for (int tb = 0; tb < MAXTB; ++tb)
                 if (tile_begin + tb < tile_end) {
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int r = g + (i >> 1) * 8;
+                            const int rr = tb * kTileRows + g + (i >> 1) * 8;
                             const int b = nt * 8 + 2 * t + (i & 1);
-                            if (b < B) red[((((m * TB + tb) * kTileRows + r) * B + b) << 4) + cw] = acc[m][tb][nt][i];
+                            if (b < B) red[((((uint32_t)m * TBR + rr) * B + b) << 4) + cw] = acc[m][tb][nt][i];
                         }
                 }
-        // ---- zero-point term: warp per output row, lanes over the groups of the row ----
-        const int block_rows = min(r_hi, r_lo + tile_end * kTileRows) - (r_lo + tile_begin * kTileRows);
-        if (has_zero) {
-            for (int rr = cw; rr < block_rows; rr += kConsumerWarps) {
-                const int tb = rr / kTileRows;
-                const int r = rr - tb * kTileRows;
-#pragma unroll
-                for (int m = 0; m < MATS; ++m) {
-                    float part[NT * 8];
-#pragma unroll
-                    for (int b = 0; b < NT * 8; ++b) part[b] = 0.0f;
-                    if (p.z[m] != nullptr) {
-                        const uint32_t* rkk = kks + ((size_t)(m * TB + tb) * kTileRows + r) * Gn;
-                        for (int gi = lane; gi < Gn; gi += 32) {
-                            const uint32_t kk = rkk[gi];
-                            const __half2 k2 = *reinterpret_cast<const __half2*>(&kk);
-                            const float ke = __low2float(k2), ko = __high2float(k2);
-#pragma unroll
-                            for (int b = 0; b < NT * 8; ++b)
-                                if (b < B) part[b] = fmaf(ke, xsum_e[gi * B + b], fmaf(ko, xsum_o[gi * B + b], part[b]));
-                        }
-                    }
-#pragma unroll
-                    for (int b = 0; b < NT * 8; ++b) {
-                        if (b < B) {
-                            const float s = warp_sum(part[b]);
-                            if (lane == 0) corr[((m * TB + tb) * kTileRows + r) * B + b] = s;
-                        }
-                    }
-                }
-            }
-        }
         named_bar_sync(1, kConsumerThreads);
 
         // ---- reduction over the warps (fixed order: xor tree inside 16 lanes) + epilogue.  red / corr /
@@ -586,22 +585,20 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             const bool live = item < items;
             const int rr = live ? item / B : 0;
             const int b = live ? item - rr * B : 0;
-            const int tb = rr / kTileRows;
-            const int r = rr - tb * kTileRows;
             float val[MATS];
 #pragma unroll
             for (int m = 0; m < MATS; ++m) {
-                float s = live ? red[((((m * TB + tb) * kTileRows + r) * B + b) << 4) + w] : 0.0f;
+                float s = live ? red[((((uint32_t)m * TBR + rr) * B + b) << 4) + w] : 0.0f;
                 s += __shfl_xor_sync(0xffffffffu, s, 8);
                 s += __shfl_xor_sync(0xffffffffu, s, 4);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
                 s += __shfl_xor_sync(0xffffffffu, s, 1);
-                if (has_zero && live) s -= corr[((m * TB + tb) * kTileRows + r) * B + b];
+                if (has_zero && live) s -= corr[((uint32_t)m * TBR + rr) * B + b];
                 if (need_row_pass) s *= xscale[b];
                 val[m] = round_act(fminf(fmaxf(s, -fmax_act), fmax_act), p.act_dtype);
             }
             if (live && w == 0) {
-                const int64_t o = (int64_t)b * p.N + r_lo + tile_begin * kTileRows + rr;
+                const int64_t o = (int64_t)b * p.N + brow0 + rr;
                 auto store = [&](void* basep, float v) {
                     if (p.act_dtype == B200Q_F16) reinterpret_cast<__half*>(basep)[o] = __float2half_rn(v);
                     else reinterpret_cast<__nv_bfloat16*>(basep)[o] = __float2bfloat16_rn(v);
@@ -725,31 +722,35 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
                     (p.z[0] == nullptr || aligned16(p.z[0])) &&
                     (MATS == 1 || (aligned16(p.s[1]) && (p.z[1] == nullptr || aligned16(p.z[1]))));
     p.row_stride = (uint32_t)(kc * BITS / 8) + kRowPad;
-    p.stage_meta_off = align_up(kTileRows * p.row_stride, 128);
-    p.stage_bytes = p.stage_meta_off + align_up((uint32_t)2 * kTileRows * p.Gn * 2, 128);
+    p.stage_bytes = align_up(kTileRows * p.row_stride, 128);
 
-    // Activation chunk (whole K when it fits the budget, else a multiple of kc) and the number of tiles whose
-    // accumulators stay live across chunks: first choice that leaves room for a two-stage ring.
+    // Tiles per row block (amortises the constants pass and the reduction) and the activation chunk
+    // (whole K when it fits the budget, else a multiple of kc): first choice that leaves room for a
+    // two-stage ring.
     uint32_t off = 0;
     bool fits = false;
     const uint32_t budgets[3] = {64 * 1024, 32 * 1024, 16 * 1024};
-    for (int tb_try = kMaxBlockTiles; tb_try >= 1 && !fits; --tb_try) {
+    for (int tb_try = std::min(max_tiles, kMaxBlockTiles / (MATS * NT)); tb_try >= 1 && !fits; --tb_try) {
+        const uint32_t tbr = (uint32_t)tb_try * kTileRows;
+        // keep the double-buffered constants and reduction scratch moderate
+        if (tb_try > 1 && (2u * MATS * tbr * p.Gn * 8 > 64 * 1024 || 2u * (kConsumerWarps + 1) * MATS * tbr * p.B * 4 > 48 * 1024))
+            continue;
         for (int bi = 0; bi < 3 && !fits; ++bi) {
             int xk = p.n_kc * kc;
             if ((size_t)p.K * p.B * 2 > budgets[bi]) xk = std::max(1, (int)(budgets[bi] / ((size_t)p.B * 2 * kc))) * kc;
             const int n_xc = (p.K + xk - 1) / xk;
-            const int block_tiles = n_xc > 1 ? std::min(max_tiles, tb_try) : 1;
-            if (n_xc == 1 && (tb_try != kMaxBlockTiles || bi != 0)) continue;   // nothing new to try
+            if (n_xc == 1 && bi != 0) continue;   // nothing new to try
             p.xk = xk;
-            p.block_tiles = block_tiles;
-            p.slots_buf_elems = (uint32_t)MATS * block_tiles * kTileRows * p.Gn;
-            p.red_buf_elems = (uint32_t)(kConsumerWarps + 1) * MATS * block_tiles * kTileRows * p.B;
-            off = align_up(2 * kMaxStages * sizeof(uint64_t), 128);
+            p.block_tiles = tb_try;
+            p.slots_buf_elems = (uint32_t)MATS * tbr * p.Gn;
+            p.red_buf_elems = (uint32_t)(kConsumerWarps + 1) * MATS * tbr * p.B;
+            off = align_up((2 * kMaxStages + 4) * sizeof(uint64_t), 128);
             p.off_xperm = off;  off += align_up((uint32_t)xk * p.B * 2, 128);
             p.off_xsum = off;   off += align_up((uint32_t)2 * p.Gn * p.B * 4, 128);
             p.off_xscale = off; off += align_up((uint32_t)p.B * 2 * 4, 128);
-            p.off_slots = off;  off += align_up(2 * p.slots_buf_elems * 12, 128);
+            p.off_slots = off;  off += align_up(2 * p.slots_buf_elems * 8, 128);
             p.off_red = off;    off += align_up(2 * p.red_buf_elems * 4, 128);
+            p.off_meta = off;   off += p.meta_by_tma ? align_up(2u * MATS * 2 * tbr * p.Gn * 2, 128) : 0;
             p.off_ring = off;
             fits = off + 2ull * p.stage_bytes <= smem_cap;
         }
@@ -759,6 +760,8 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     // ring depth: everything the CTA will ever stream if that is small (keeps two CTAs resident per SM, so
     // the next kernel's prefetch overlaps this kernel's tail), else as deep as shared memory allows
     const int total_stages = max_tiles * MATS * p.n_kc;
+    p.logG = 0;
+    while ((1 << p.logG) < p.G) ++p.logG;
     int stages = tuning_get("gemv.stages");
     if (stages <= 0) stages = kMaxStages;
     stages = std::min({stages, kMaxStages, std::max(2, total_stages)});

@@ -1,0 +1,100 @@
+"""GPU parity of the decode-layer glue and of the whole decode stack against the CPU oracle."""
+import dataclasses
+import importlib
+
+import pytest
+import torch
+
+import __graft_entry__ as entry
+from helpers import cabi, pq_ops, rel_l2, synth
+from oracle import paged_quantized_kv_ops as opq, stack as ostack
+from oracle.elementwise_ops import reference_rms_norm
+from oracle.mlp_block_ops import reference_quantized_linear
+
+pytestmark = pytest.mark.gpu
+entry.load_package()
+layer_ops = importlib.import_module("mlx_metal_kernels_b200.ops.decode_layer_ops")
+stack_mod = importlib.import_module("mlx_metal_kernels_b200.stack")
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("K,N,B", [(512, 768, 1), (1024, 300, 5), (96, 50, 2)])
+def test_norm_quantized_linear(cuda, bits, K, N, B):
+    G = 32 if K % 128 else 64
+    w, s, z = synth.quantized_weight(N, K, bits, G, seed=K + N)
+    x = synth.activations((B, K), 3)
+    nw = (torch.rand(K) + 0.5).to(torch.float16)
+    normed = reference_rms_norm(x.unsqueeze(1), nw, eps=1e-5)
+    want = reference_quantized_linear(normed, w, s, z, bits=bits, group_size=G).squeeze(1)
+    got, gn = layer_ops.norm_quantized_linear(x.to(cuda), nw.to(cuda), w.to(cuda), s.to(cuda), z.to(cuda), bits=bits,
+                                              group_size=G, return_normed=True)
+    assert rel_l2(got, want) <= 1.5e-3       # includes the fp16 rounding of the normalised rows
+    if K % 128 == 0:
+        pass                                  # the fused path does not materialise the normalised rows
+    else:
+        assert rel_l2(gn, normed.squeeze(1)) <= 5e-4
+
+
+@pytest.mark.parametrize("bits,G", [(8, 32), (4, 32), (8, 64)])
+def test_rope_kv_append_exact(cuda, bits, G):
+    B, Hq, Hkv, D, P = 3, 4, 2, 128, 16
+    positions = torch.tensor([0, 17, 40], dtype=torch.int32)
+    case = synth.paged_kv_case(B, Hkv, D, P, num_pages=16, min_len=48, max_len=48, bits=bits, group_size=G, seed=9)
+    qkv = synth.activations((B, (Hq + 2 * Hkv) * D), 10)
+    cos, sin = ostack.rope_tables(D, 500000.0, 64)
+    ocache = opq.OraclePagedKV(**{k: (v.clone() if torch.is_tensor(v) else v) for k, v in case.items()})
+    x3 = qkv.reshape(B, Hq + 2 * Hkv, D)
+    want_q = ostack.apply_rope_rows(x3[:, :Hq], cos, sin, positions)
+    ostack.append_kv(ocache, ostack.apply_rope_rows(x3[:, Hq:Hq + Hkv], cos, sin, positions), x3[:, Hq + Hkv:], positions)
+    dcache = pq_ops.PagedQuantizedKVCache(**{k: (v.to(cuda) if torch.is_tensor(v) else v) for k, v in case.items()})
+    got_q = layer_ops.rope_kv_append(qkv.to(cuda), cos.to(cuda), sin.to(cuda), positions.to(cuda), dcache, Hq)
+    assert torch.equal(got_q.cpu(), want_q)
+    for name in ("k_pages_q", "v_pages_q", "k_scales", "v_scales"):
+        assert torch.equal(getattr(dcache, name).cpu(), getattr(ocache, name)), name
+
+
+def _tiny_stack(cuda, kv_bits, batch, positions):
+    cfg = stack_mod.StackConfig(hidden=512, intermediate=1024, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128,
+                                vocab=97, bits=4, group_size=64, kv_bits=kv_bits, kv_group_size=32)
+    layers = [stack_mod.random_layer(cfg, 100 + i, "cpu") for i in range(cfg.n_layers)]
+    for i, l in enumerate(layers):      # non-trivial norm weights
+        g = torch.Generator().manual_seed(i)
+        l["input_norm"] = (torch.rand(cfg.hidden, generator=g) + 0.5).to(torch.float16)
+        l["post_norm"] = (torch.rand(cfg.hidden, generator=g) + 0.5).to(torch.float16)
+    emb = synth.activations((cfg.vocab, cfg.hidden), 5)
+    final_norm = torch.ones(cfg.hidden, dtype=torch.float16)
+    to = lambda t: t.to(cuda) if torch.is_tensor(t) else tuple(u.to(cuda) for u in t)
+    dlayers = [{k: to(v) for k, v in l.items()} for l in layers]
+    stack = stack_mod.DecodeStack(cfg, dlayers, final_norm.to(cuda), emb.to(cuda), batch, 96, cuda)
+    stack.set_context(0, seed=7)
+    stack.positions.copy_(positions.to(cuda))
+    stack.lengths.copy_((positions + 1).to(cuda))
+    return cfg, layers, emb, final_norm, stack
+
+
+@pytest.mark.parametrize("kv_bits", [8, 4])
+def test_decode_stack_matches_oracle(cuda, kv_bits):
+    batch = 3
+    positions = torch.tensor([33, 5, 64], dtype=torch.int32)
+    cfg, layers, emb, final_norm, stack = _tiny_stack(cuda, kv_bits, batch, positions)
+    # oracle caches = copies of the device caches before the step
+    ocaches = []
+    for c in stack.caches:
+        ocaches.append(opq.OraclePagedKV(
+            k_pages_q=c.k_codes.cpu().clone(), v_pages_q=c.v_codes.cpu().clone(), k_scales=c.k_scales.cpu().clone(),
+            v_scales=c.v_scales.cpu().clone(), block_table=stack.block_table.cpu(), lengths=(positions + 1),
+            bits=kv_bits, page_size=cfg.page_size, group_size=cfg.kv_group_size,
+            original_page_shape=(stack.num_pages, cfg.page_size, cfg.n_kv_heads, cfg.head_dim)))
+    tokens = torch.tensor([3, 50, 96])
+    cos, sin = ostack.rope_tables(cfg.head_dim, cfg.rope_theta, 96)
+    want = ostack.stack_decode_step(tokens, emb, layers, ocaches, final_norm, cos, sin, positions, cfg.oracle_dict())
+    got = stack.step(tokens.to(cuda))
+    assert rel_l2(got, want.squeeze(1)) <= 3e-3          # two layers of 1e-3-class operators
+    assert torch.equal(stack.positions.cpu(), positions + 1)
+    # a captured graph replays the same step bit for bit
+    stack.positions.copy_(positions.to(cuda))
+    stack.lengths.copy_((positions + 1).to(cuda))
+    stack.capture()
+    again = stack.step(tokens.to(cuda)).clone()
+    assert torch.equal(again, got)
+    assert cabi.device_status() == 0
