@@ -1,9 +1,18 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized decode hot path on B200.
+"""Benchmark of the quantized single-token decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch B]
 
-Prints ONE JSON line (rank 0).  See DESIGN.md for the definition of every field.
+One "step" is one decode step of the 32-layer Llama-3-8B-shaped q4 stack (hidden 4096, 32 q / 8 kv
+heads, head_dim 128, MLP 14336, q4 group-64 weights ~N(0,0.02), q8 paged KV cache at context 4096)
+for a batch of random token ids: the composition of the hot-path operators (fused RMSNorm+QKV
+matvec, RoPE + quantised KV append, paged GQA decode attention, O matvec + residual, fused
+RMSNorm + gate/up + SwiGLU, down matvec + residual).  Each step streams about 4.2 GB of weights and
+KV from HBM (far more than L2), so no cache flush is needed between steps.
+
+Rank 0 prints ONE JSON line.  With N > 1 the stack is tensor-parallel over the N GPUs of the node
+(weights sharded by output rows, KV by kv heads, NCCL all-gather at the layer boundaries): total work
+is fixed, so ``scaling`` is "strong".
 """
 from __future__ import annotations
 
@@ -23,20 +32,21 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 import __graft_entry__ as entry  # noqa: E402
 
-L2_BYTES = 126 * 1024 * 1024
-ROTATE_BYTES = 512 * 1024 * 1024          # distinct operand bytes touched per rotation (> 2x L2)
+CONTEXT = 4096
+ROTATE_BYTES = 512 * 1024 * 1024          # distinct operand bytes per rotation of a kernel micro-benchmark (> 2x L2)
+METRIC = "decode tokens/s"
+WORKLOAD = "c5_llama3_8b_shaped_q4_stack_32_layers_q8_paged_kv_ctx4096"
 
 
 def measured_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
-        data = json.loads(path.read_text())
-        return float(data["hbm_gbs"]), "measured"
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
 
 
 # ------------------------------------------------------------------------------------------------
-# clocks sampling during the timed region
+# clocks sampled during the timed region
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -44,18 +54,15 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.rows = []
-        self._stop = threading.Event()
-        self._thread = None
+        self.gpu_index, self.rows = gpu_index, []
+        self._stop, self._thread = threading.Event(), None
 
     def _loop(self):
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                       "-i", str(self.gpu_index)], capture_output=True, text=True, timeout=5).stdout
-                for line in out.strip().splitlines():
-                    self.rows.append([c.strip() for c in line.split(",")])
+                self.rows += [[c.strip() for c in line.split(",")] for line in out.strip().splitlines()]
             except Exception:
                 pass
             self._stop.wait(0.1)
@@ -76,9 +83,7 @@ class ClockSampler:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
-                for name, val in zip(names, r[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
+                reasons |= {n for n, v in zip(names, r[5:9]) if v.lower().startswith("active")}
             except (ValueError, IndexError):
                 continue
         if not sm:
@@ -88,91 +93,115 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# workloads
+# kernel micro-benchmarks (cold cache through rotating operand copies), reported beside the headline
 # ------------------------------------------------------------------------------------------------
-class Workload:
-    """A workload owns R rotating copies of its streamed operands (R * bytes >= ROTATE_BYTES), so
-    that every launch in a rotation reads operands that are not in L2."""
-    name = ""
-    unit_name = ""
-
-    def launches_per_rotation(self):
-        raise NotImplementedError
-
-
-class Q4MatvecC1(Workload):
-    """BASELINE config C1: q4 matvec, batch 1, W[4096,4096] group 64, fp16 scale/zero, seed 1001."""
-    name = "c1_q4_matvec_b1_4096x4096_g64"
-    bits, B, N, K, G, seed = 4, 1, 4096, 4096, 64, 1001
-
-    def __init__(self, pkg, device):
-        self.q = importlib.import_module(f"{entry.PKG_ALIAS}.ops.quant_ops")
-        synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
-        w, s, z = synth.quantized_weight(self.N, self.K, self.bits, self.G, seed=self.seed)
-        self.host = (w, s, z)
-        self.bytes = w.numel() + s.numel() * 2 + z.numel() * 2 + self.B * self.K * 2 + self.B * self.N * 2
-        self.R = max(2, -(-ROTATE_BYTES // self.bytes))
-        self.w = [w.to(device).clone() for _ in range(self.R)]
-        self.s = [s.to(device).clone() for _ in range(self.R)]
-        self.z = [z.to(device).clone() for _ in range(self.R)]
-        self.x_host = synth.activations((self.B, self.K), self.seed + 500).pin_memory()
-        self.x = self.x_host.to(device)
-        self.device = device
-
-    def algorithmic_bytes(self):
-        return self.bytes
-
-    def rotation(self):
-        """One pass over all R copies; returns the last output."""
-        y = None
-        fn = self.q.q4_matvec_decode if self.bits == 4 else self.q.q8_matvec_decode
-        for i in range(self.R):
-            y = fn(self.x, self.w[i], self.s[i], self.z[i], group_size=self.G, backend="cuda")
-        return y
-
-    def launches_per_rotation(self):
-        return self.R
-
-    def e2e_call(self, i):
-        """Public API with host buffers: H2D of the activation row, matvec, D2H of the result."""
-        fn = self.q.q4_matvec_decode if self.bits == 4 else self.q.q8_matvec_decode
-        x = self.x_host.to(self.device, non_blocking=True)
-        y = fn(x, self.w[i % self.R], self.s[i % self.R], self.z[i % self.R], group_size=self.G, backend="cuda")
-        return y.cpu()
-
-    def e2e_bytes(self):
-        return self.B * self.K * 2, self.B * self.N * 2
-
-    def cpu_reference_call(self):
-        from oracle import quant_ops as oq
-        w, s, z = self.host
-        fn = oq.reference_q4_matvec_decode if self.bits == 4 else oq.reference_q8_matvec_decode
-        return fn(self.x_host, w, s, z, group_size=self.G)
-
-
-WORKLOADS = {"c1": Q4MatvecC1}
-
-
-# ------------------------------------------------------------------------------------------------
-def time_graph(workload, steps, warmup, stream):
-    """Captures one rotation in a CUDA graph and replays it; returns seconds per step (rotation)."""
-    torch.cuda.synchronize()
+def _time_graph(fn, iters, stream):
     with torch.cuda.stream(stream):
-        workload.rotation()                      # lazy init outside capture (function attributes, caches)
+        fn()
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            workload.rotation()
-        for _ in range(warmup):
+            fn()
+        for _ in range(3):
             graph.replay()
         stream.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
-        for _ in range(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
             graph.replay()
-        end.record(stream)
-        end.synchronize()
-    return start.elapsed_time(end) / 1e3 / steps
+        e1.record(stream)
+        e1.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / iters
+
+
+def kernel_microbenchmarks(device, peak):
+    """BASELINE configs C1 (q4 matvec 4096x4096, batch 1) and C4 (q4 paged GQA decode attention, batch 16,
+    lengths U[1024, 8192]); achieved = algorithmic bytes / average launch time."""
+    q = importlib.import_module(f"{entry.PKG_ALIAS}.ops.quant_ops")
+    pq = importlib.import_module(f"{entry.PKG_ALIAS}.ops.paged_quantized_kv_ops")
+    synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
+    stream = torch.cuda.Stream(device)
+    out = {}
+    # C1
+    w, s, z = synth.quantized_weight(4096, 4096, 4, 64, seed=1001)
+    nbytes = w.numel() + (s.numel() + z.numel()) * 2 + 4096 * 2 + 4096 * 2
+    R = -(-ROTATE_BYTES // nbytes)
+    ws, ss, zs = [w.to(device).clone() for _ in range(R)], [s.to(device).clone() for _ in range(R)], [z.to(device).clone() for _ in range(R)]
+    x = synth.activations((1, 4096), 1501, device)
+    sec = _time_graph(lambda: [q.q4_matvec_decode(x, ws[i], ss[i], zs[i], group_size=64, backend="cuda") for i in range(R)],
+                      10, stream) / R
+    out["c1_q4_matvec_b1_4096x4096_g64"] = {"us": round(sec * 1e6, 3), "algorithmic_bytes": nbytes,
+                                             "gbs": round(nbytes / sec / 1e9, 1), "frac_of_peak": round(nbytes / sec / 1e9 / peak, 4),
+                                             "rotating_copies": R}
+    del ws, ss, zs
+    # C4
+    case = synth.paged_kv_case(16, 8, 128, 16, num_pages=9000, min_len=1024, max_len=8192, bits=4, group_size=32, seed=1004)
+    total = int(case["lengths"].sum())
+    nbytes = total * 8 * 144 + int(((case["lengths"] + 15) // 16).sum()) * 4 + 2 * 16 * 32 * 128 * 2
+    R = -(-ROTATE_BYTES // nbytes)
+    caches = [pq.PagedQuantizedKVCache(**{k: (v.to(device).clone() if torch.is_tensor(v) else v) for k, v in case.items()})
+              for _ in range(R)]
+    qq = synth.activations((16, 1, 32, 128), 1005, device)
+    sec = _time_graph(lambda: [pq.paged_quantized_kv_gqa_decode_attention(qq, c, backend="cuda") for c in caches], 10, stream) / R
+    out["c4_q4_paged_gqa_decode_b16_h32_kv8_d128_p16"] = {"us": round(sec * 1e6, 3), "algorithmic_bytes": nbytes,
+                                                          "gbs": round(nbytes / sec / 1e9, 1),
+                                                          "frac_of_peak": round(nbytes / sec / 1e9 / peak, 4),
+                                                          "sum_lengths": total, "rotating_copies": R}
+    del caches
+    torch.cuda.empty_cache()
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# own arm
+# ------------------------------------------------------------------------------------------------
+def build_stack(device, batch, steps_total, rank, world, group):
+    stack_mod = importlib.import_module(f"{entry.PKG_ALIAS}.stack")
+    synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
+    cfg = stack_mod.StackConfig()
+    layers = [stack_mod.random_layer(cfg, 1005 + i, device) for i in range(cfg.n_layers)]
+    gen = torch.Generator(device=device).manual_seed(1005)
+    emb = torch.randn((cfg.vocab, cfg.hidden), generator=gen, device=device, dtype=torch.float32).to(torch.float16)
+    final_norm = torch.ones(cfg.hidden, dtype=torch.float16, device=device)
+    stack = stack_mod.DecodeStack(cfg, layers, final_norm, emb, batch, CONTEXT + steps_total + 16, device,
+                                  tp_rank=rank, tp_size=world, process_group=group)
+    del layers
+    torch.cuda.empty_cache()
+    stack.set_context(CONTEXT, seed=2005)
+    return cfg, stack
+
+
+def gemv_only_graph(stack):
+    """The matvec launches of one step (no attention, no glue) for the roofline of the dominant kernel."""
+    cabi = importlib.import_module(f"{entry.PKG_ALIAS}.ops._cabi")
+    lib, cfg, B = stack.lib, stack.cfg, stack.B
+    F16 = cabi.F16
+    D, G, bits = cfg.head_dim, cfg.group_size, cfg.bits
+
+    def run():
+        st = torch.cuda.current_stream().cuda_stream
+        for w in stack.layers:
+            qw, qs, qz = w["qkv"]
+            ow, os_, oz = w["o"]
+            gw, gs, gz = w["gate"]
+            uw, us, uz = w["up"]
+            dw, ds, dz = w["down"]
+            cabi.check(lib.b200q_norm_qmatvec(bits, stack.h.data_ptr(), None, w["input_norm"].data_ptr(), F16, cfg.eps, None,
+                                              None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(), None, stack.qkv.data_ptr(),
+                                              B, qw.shape[0], cfg.hidden, G, F16, F16, st), "qkv")
+            src = stack.attn if stack.tp_size == 1 else stack.attn_full
+            dst = stack.h2 if stack.tp_size == 1 else stack.o_loc
+            cabi.check(lib.b200q_qmatvec(bits, src.data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
+                                         dst.data_ptr(), B, ow.shape[0], cfg.n_heads * D, G, F16, F16, st), "o")
+            cabi.check(lib.b200q_gate_up_swiglu(bits, stack.h2.data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
+                                                us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, stack.act.data_ptr(),
+                                                None, w["post_norm"].data_ptr(), F16, cfg.eps, None, None, B, gw.shape[0],
+                                                cfg.hidden, G, F16, F16, st), "gate_up")
+            src = stack.act if stack.tp_size == 1 else stack.act_full
+            dst = stack.h if stack.tp_size == 1 else stack.o_loc
+            cabi.check(lib.b200q_qmatvec(bits, src.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(), None,
+                                         dst.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down")
+    return run, 4 * len(stack.layers)
 
 
 def run_own(args):
@@ -183,14 +212,17 @@ def run_own(args):
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU path (use --impl reference for the CPU baseline)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    group = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
-    pkg = entry.load_package()
+        group = dist.group.WORLD
+    entry.load_package()
     cabi = importlib.import_module(f"{entry.PKG_ALIAS}.ops._cabi")
     cabi.load()
-    wl = WORKLOADS[args.workload](pkg, device)
-    stream = torch.cuda.Stream(device)
+    peak, peak_kind = measured_peaks()
+    warmup = max(3, args.warmup)
+    B = args.batch
 
     def barrier():
         if world > 1:
@@ -198,115 +230,182 @@ def run_own(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    cfg, stack = build_stack(device, B, args.steps * 3 + warmup * 2 + 64, rank, world, group)
+    gen = torch.Generator(device=device).manual_seed(77)
+    tokens = torch.randint(0, cfg.vocab, (args.steps + warmup, B), generator=gen, device=device)
+    stack.capture()
+
+    # ---- headline: K graph-replayed decode steps, device-timed ----
+    for i in range(warmup):
+        stack.step(tokens[i])
     barrier()
     with ClockSampler(local) as clocks:
-        sec_per_step = time_graph(wl, args.steps, max(3, args.warmup), stream)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            stack.step(tokens[warmup + i])
+        e1.record()
+        e1.synchronize()
     barrier()
+    sec_per_step = e0.elapsed_time(e1) / 1e3 / args.steps
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([sec_per_step], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sec_per_step = float(t.item())
-    launches = wl.launches_per_rotation()
-    sec_per_launch = sec_per_step / launches
-    peak, peak_kind = measured_peaks()
-    achieved = wl.algorithmic_bytes() / sec_per_launch / 1e9
+    tokens_per_s = B / sec_per_step
 
-    # end to end through the public API with host buffers
-    n_e2e = max(20, min(200, args.steps * 4))
-    for i in range(5):
-        wl.e2e_call(i)
-    torch.cuda.synchronize()
+    # ---- end to end: host token ids in, host hidden state out, every step ----
+    host_tokens = tokens.cpu().pin_memory()
+    host_out = torch.empty((B, cfg.hidden), dtype=torch.float16).pin_memory()
+    dev_tok = torch.empty(B, dtype=torch.int64, device=device)
+    for i in range(3):
+        dev_tok.copy_(host_tokens[i], non_blocking=True)
+        host_out.copy_(stack.step(dev_tok), non_blocking=True)
+    barrier()
     t0 = time.perf_counter()
-    for i in range(n_e2e):
-        wl.e2e_call(i)
-    torch.cuda.synchronize()
-    e2e_sec = (time.perf_counter() - t0) / n_e2e
-    h2d, d2h = wl.e2e_bytes()
+    for i in range(args.steps):
+        dev_tok.copy_(host_tokens[warmup + i], non_blocking=True)
+        host_out.copy_(stack.step(dev_tok), non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # the caller reads the result before the next token
+    e2e_sec = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([e2e_sec], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_sec = float(t.item())
+
+    # ---- roofline of the dominant kernel: the matvec launches of one step, timed alone ----
+    run_gemv, n_gemv = gemv_only_graph(stack)
+    stream = torch.cuda.Stream(device)
+    gemv_sec = _time_graph(run_gemv, 10, stream)
+    weight_bytes = stack.weight_bytes_per_step()
+    act_bytes = 0
+    for w in stack.layers:
+        for key, kdim in (("qkv", cfg.hidden), ("o", cfg.n_heads * cfg.head_dim), ("gate", cfg.hidden), ("down", cfg.intermediate)):
+            act_bytes += B * kdim * 2 + B * w[key][0].shape[0] * 2 * (2 if key == "gate" else 1)
+    gemv_bytes = weight_bytes + act_bytes
+    gemv_gbs = gemv_bytes / gemv_sec / 1e9
+    step_bytes = weight_bytes + stack.kv_bytes_per_step(CONTEXT)
 
     status = cabi.device_status()
     line = {
-        "metric": "q4 matvec achieved HBM bandwidth (algorithmic bytes / kernel time)",
-        "value": round(achieved * world, 2),
-        "unit": "GB/s",
+        "metric": METRIC,
+        "value": round(tokens_per_s, 2),
+        "unit": "tokens/s",
         "n_gpus": world,
         "steps": args.steps,
-        "warmup": max(3, args.warmup),
-        "ms_per_step": round(sec_per_step * 1e3, 5),
-        "us_per_launch": round(sec_per_launch * 1e6, 4),
+        "warmup": warmup,
+        "ms_per_step": round(sec_per_step * 1e3, 4),
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "f16 activations, u4 codes, f32 accumulate",
-        "data": "synthetic",
-        "config": {"workload": wl.name, "cache": f"cold: {wl.R} rotating operand copies = {wl.R * wl.algorithmic_bytes() >> 20} MiB > L2",
-                   "launches_per_step": launches},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                     "algorithmic_bytes_per_launch": wl.algorithmic_bytes()},
-        "e2e": {"value": round(wl.algorithmic_bytes() / e2e_sec / 1e9 * world, 3), "unit": "GB/s",
-                "us_per_call": round(e2e_sec * 1e6, 2), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches * args.steps,
+        "dtype": "f16 activations, u4 weight codes, u8 KV codes, f32 accumulate",
+        "data": "synthetic (random-init weights ~N(0,0.02) quantised q4 group 64; KV ~N(0,1) quantised q8 group 32; random token ids)",
+        "config": {"workload": WORKLOAD, "batch": B, "context": CONTEXT, "parallelism": f"tp{world}",
+                   "cache": "each step streams %.2f GB per GPU from HBM (> L2), no flush needed" % (step_bytes / 1e9),
+                   "cuda_graph": True},
+        "step_hbm": {"algorithmic_bytes_per_gpu": step_bytes, "achieved_gbs_per_gpu": round(step_bytes / sec_per_step / 1e9, 1),
+                     "frac_of_peak": round(step_bytes / sec_per_step / 1e9 / peak, 4)},
+        "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (all q4 matvec launches of one step, timed alone)",
+                     "achieved": round(gemv_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gemv_gbs / peak, 4),
+                     "traffic": None, "peak_kind": peak_kind, "launches": n_gemv,
+                     "algorithmic_bytes_per_launch": round(gemv_bytes / n_gemv), "us_per_launch": round(gemv_sec / n_gemv * 1e6, 3)},
+        "e2e": {"value": round(B / e2e_sec, 2), "unit": "tokens/s", "ms_per_step": round(e2e_sec * 1e3, 4),
+                "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * cfg.hidden * 2},
+        "gpu_launches": stack.launches_per_step * args.steps,
         "clocks": clocks.summary(),
         "device_status": status,
     }
+    if rank == 0 and world == 1:
+        del stack
+        torch.cuda.empty_cache()
+        line["kernels"] = kernel_microbenchmarks(device, peak)
+        line["cpu_baseline"] = cpu_baseline(B, budget_s=20.0)
     if rank == 0:
-        if world == 1:
-            line["cpu_baseline"] = cpu_baseline(wl, budget_s=10.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
 
 
-def cpu_baseline(wl, budget_s):
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the torch-CPU restatement of the reference path on a bounded sample
+# ------------------------------------------------------------------------------------------------
+SAMPLE_LAYERS = 1
+
+
+class CpuSample:
+    """SAMPLE_LAYERS layers of the stack at the benchmark shapes; a full step is 32 layers, so
+    tokens/s = batch / (32 / SAMPLE_LAYERS * seconds per sample)."""
+
+    def __init__(self, batch):
+        entry.load_package()
+        stack_mod = importlib.import_module(f"{entry.PKG_ALIAS}.stack")
+        synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
+        from oracle import paged_quantized_kv_ops as opq, stack as ostack
+        self.ostack = ostack
+        self.cfg = cfg = stack_mod.StackConfig()
+        self.batch = batch
+        self.layers = [stack_mod.random_layer(cfg, 1005 + i, "cpu") for i in range(SAMPLE_LAYERS)]
+        P = cfg.page_size
+        blocks = (CONTEXT + 16 + P - 1) // P
+        self.positions = torch.full((batch,), CONTEXT, dtype=torch.int32)
+        self.caches = []
+        for i in range(SAMPLE_LAYERS):
+            case = synth.paged_kv_case(batch, cfg.n_kv_heads, cfg.head_dim, P, num_pages=batch * blocks, min_len=CONTEXT + 1,
+                                       max_len=CONTEXT + 1, bits=cfg.kv_bits, group_size=cfg.kv_group_size, seed=2005 + i)
+            self.caches.append(opq.OraclePagedKV(**case))
+        self.cos, self.sin = ostack.rope_tables(cfg.head_dim, cfg.rope_theta, CONTEXT + 16)
+        self.h = synth.activations((batch, 1, cfg.hidden), 3005)
+
+    def run(self):
+        h = self.h
+        for w, cache in zip(self.layers, self.caches):
+            h = self.ostack.layer_decode_step(h, w, cache, self.cos, self.sin, self.positions, self.cfg.oracle_dict())
+        return h
+
+    def tokens_per_s(self, sec_per_sample):
+        return self.batch / (sec_per_sample * self.cfg.n_layers / SAMPLE_LAYERS)
+
+
+def cpu_baseline(batch, budget_s):
     torch.set_num_threads(os.cpu_count() or 1)
-    wl.cpu_reference_call()
+    sample = CpuSample(batch)
+    sample.run()
     n, t0 = 0, time.perf_counter()
-    while n < 3 or (time.perf_counter() - t0 < budget_s and n < 50):
-        wl.cpu_reference_call()
+    while n < 2 or (time.perf_counter() - t0 < budget_s and n < 20):
+        sample.run()
         n += 1
     sec = (time.perf_counter() - t0) / n
-    return {"value": round(wl.algorithmic_bytes() / sec / 1e9, 4), "unit": "GB/s", "us_per_call": round(sec * 1e6, 1),
-            "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{n} calls of the torch-CPU restatement of the reference path (dequantise W to fp16, fp32 matmul) on {wl.name}"}
-
-
-class _HostOnly:
-    """Workload inputs for the reference arm without touching a GPU."""
+    return {"value": round(sample.tokens_per_s(sec), 4), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n} runs of {SAMPLE_LAYERS} of the 32 layers (torch-CPU restatement of the reference path: dequantise W to "
+                      f"fp16, fp32 matmul, paged q8 attention at context {CONTEXT}), {sec * 1e3:.0f} ms each, scaled to 32 layers"}
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    entry.load_package()
-    synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
-    cls = WORKLOADS[args.workload]
-    wl = _HostOnly()
-    wl.__class__ = type("HostWorkload", (cls,), {"__init__": lambda self: None})
-    w, s, z = synth.quantized_weight(cls.N, cls.K, cls.bits, cls.G, seed=cls.seed)
-    wl.host = (w, s, z)
-    wl.x_host = synth.activations((cls.B, cls.K), cls.seed + 500)
-    wl.bytes = w.numel() + s.numel() * 2 + z.numel() * 2 + cls.B * cls.K * 2 + cls.B * cls.N * 2
     torch.set_num_threads(os.cpu_count() or 1)
-    for _ in range(max(3, args.warmup)):
-        wl.cpu_reference_call()
+    sample = CpuSample(args.batch)
+    warmup = max(3, args.warmup) if args.warmup else 1
+    for _ in range(min(warmup, 3)):
+        sample.run()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        wl.cpu_reference_call()
+        sample.run()
     sec = (time.perf_counter() - t0) / args.steps
-    value = round(wl.bytes / sec / 1e9, 4)
+    value = round(sample.tokens_per_s(sec), 4)
+    desc = (f"each step = {SAMPLE_LAYERS} of the 32 layers of {WORKLOAD} at batch {args.batch} through the torch-CPU "
+            f"restatement of the reference's pure-MLX path (MLX itself cannot be installed here); value scaled to 32 layers")
     line = {
-        "impl": "reference",
-        "metric": "q4 matvec achieved HBM bandwidth (algorithmic bytes / kernel time)",
-        "value": value, "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": round(sec * 1e3, 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16 activations, u4 codes, f32 accumulate", "data": "synthetic",
-        "config": {"workload": cls.name},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": f"each step = one call of the torch-CPU restatement of the reference path on {cls.name}"},
-        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": min(warmup, 3),
+        "ms_per_step": round(sec * 1e3 * 32 / SAMPLE_LAYERS, 2), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 activations, u4 weight codes, u8 KV codes, f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "batch": args.batch, "context": CONTEXT, "parallelism": "cpu"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
@@ -314,10 +413,10 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -46,6 +46,7 @@ constexpr int kMaxBlockTiles = 4;             // tiles of a row block (one const
 constexpr int kRowPad = 64;                   // stage row stride = chunk bytes + 64: conflict-free 16-byte reads
 constexpr uint32_t kWaitLimit = 1u << 21;
 constexpr int kMaxStages = 8;
+constexpr int kMaxGroupsPerLane = 8;          // groups per row <= 256 on the fast path
 
 struct GemvParams {
     // activations
@@ -74,6 +75,7 @@ struct GemvParams {
     int xk;                 // k per staged activation chunk (multiple of kc)
     int block_tiles;        // tiles per row block (1 unless the activations need several chunks)
     int logG;               // group size is a power of two on the fast path
+    int dbg;                // measurement probes: bit 0 = skip the tensor-core work, bit 1 = do not wait for data
     int meta_by_tma;        // scales / zeros are fp16 and 16-byte aligned per tile: bulk-copied with the tile
     int rows_lo, rem;       // CTA c owns rows_lo (+1 if c < rem) rows
     uint32_t off_xperm, off_xsum, off_xscale, off_slots, off_red, off_meta, off_ring;
@@ -151,7 +153,7 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-template <int BITS, int NT, bool GATE_UP>
+template <int BITS, int NT, bool GATE_UP, int GPL>
 __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MATS = GATE_UP ? 2 : 1;
@@ -240,9 +242,10 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                     for (int m = 0; m < MATS; ++m) {
                         for (int c = c_begin; c < c_end; ++c) {
                             const int slot = p_slot;
-                            if (!first_pass)
+                            if (!first_pass && !(p.dbg & 2))
                                 ok = mbar_wait_bounded(&empty[slot], p_phase, &g_device_status, EV_GEMV_EMPTY_WAIT,
                                                        ok ? kWaitLimit : 64u) && ok;
+                            if (p.dbg & 2) { if (++p_slot == p.stages) p_slot = 0; continue; }
                             if (++p_slot == p.stages) { p_slot = 0; p_phase ^= 1; first_pass = false; }
                             const int k0 = c * p.kc;
                             const int kcur = min(p.kc, p.K - k0);
@@ -339,9 +342,10 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         named_bar_sync(1, kConsumerThreads);
     }
     const int logG = p.logG;
-    if (has_zero) {
+    if (has_zero && n_xc > 1) {
         // per-group sums of the activations exactly as the tensor cores will see them (scaled, fp16):
-        // over even k and odd k separately for q4 (the two nibble positions use different offsets)
+        // over even k and odd k separately for q4 (the two nibble positions use different offsets).
+        // (When all activations are staged at once the sums are taken from shared memory below.)
         for (int i = ctid; i < Gn * B; i += kConsumerThreads) {
             const int gi = i / B;
             const int b = i - gi * B;
@@ -361,6 +365,75 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             xsum_o[i] = so;
         }
         named_bar_sync(1, kConsumerThreads);
+    }
+
+    // ---- stage activations of [xk0, xk0+xkn) in tensor-core operand order ----
+    auto stage_x = [&](int xk0, int xkn, bool write_side) {
+                const int chunks = xkn / 8;
+#pragma unroll 4
+                for (int i = ctid; i < B * chunks; i += kConsumerThreads) {
+                    const int b = i / chunks;
+                    const int kk = (i - b * chunks) * 8;
+                    float v[8];
+                    const float inv = need_row_pass ? xscale[B + b] : 1.0f;
+                    const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
+                    load8_act(p, b, xk0 + kk, inv, write_side, v);
+                    __half h[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j] * down);
+                    const int ksx = kk / KS;
+                    const int rem = kk - ksx * KS;
+                    const int tt = rem / KT;
+                    const int c = (rem - tt * KT) / 8;
+                    uint4 out;
+                    if (BITS == 4) {
+                        // nibble order of one weight word after dequantisation: (0,4) (1,5) (2,6) (3,7)
+                        out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[4]) << 16);
+                        out.y = __half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
+                        out.z = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[6]) << 16);
+                        out.w = __half_as_ushort(h[3]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
+                    } else {
+                        out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
+                        out.y = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
+                        out.z = __half_as_ushort(h[4]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
+                        out.w = __half_as_ushort(h[6]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
+                    }
+                    *reinterpret_cast<uint4*>(xperm + ((uint32_t)((ksx * CH + c) * B + b) * 4 + tt) * 16) = out;
+                }
+    };
+    if (n_xc == 1) {
+        stage_x(0, p.K, cta == 0);
+        named_bar_sync(1, kConsumerThreads);
+        if (has_zero) {
+            // per-group sums of the staged (fp16) activations for the zero-point term
+            for (int i = ctid; i < Gn * B; i += kConsumerThreads) {
+                const int gi = i / B;
+                const int b = i - gi * B;
+                float se = 0.0f, so = 0.0f;
+                for (int kk = gi << logG; kk < ((gi + 1) << logG); kk += 8) {
+                    const int ksx = kk / KS;
+                    const int rem = kk - ksx * KS;
+                    const int tt = rem / KT;
+                    const int c = (rem - tt * KT) / 8;
+                    const uint4 u = *reinterpret_cast<const uint4*>(xperm + ((uint32_t)((ksx * CH + c) * B + b) * 4 + tt) * 16);
+                    const __half2 h0 = *reinterpret_cast<const __half2*>(&u.x);
+                    const __half2 h1 = *reinterpret_cast<const __half2*>(&u.y);
+                    const __half2 h2 = *reinterpret_cast<const __half2*>(&u.z);
+                    const __half2 h3 = *reinterpret_cast<const __half2*>(&u.w);
+                    const float a0 = __low2float(h0) + __high2float(h0), a1 = __low2float(h1) + __high2float(h1);
+                    const float a2 = __low2float(h2) + __high2float(h2), a3 = __low2float(h3) + __high2float(h3);
+                    if (BITS == 4) {            // registers 0 and 2 hold even k, 1 and 3 odd k
+                        se += a0 + a2;
+                        so += a1 + a3;
+                    } else {
+                        se += (a0 + a1) + (a2 + a3);
+                    }
+                }
+                xsum_e[i] = se;
+                xsum_o[i] = so;
+            }
+            named_bar_sync(1, kConsumerThreads);
+        }
     }
 
     bool ok = true;
@@ -404,33 +477,38 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                     const __half* rz = rs + (uint32_t)TBR * Gn;
                     const int64_t grow = (int64_t)(brow0 + rr) * Gn;
                     uint2* dst = slots + ((uint32_t)m * TBR + rr) * Gn;
-                    float part[NT * 8];
+                    // lane owns groups lane, lane + 32, ... (GPL of them: template parameter = ceil(Gn / 32) rounded up)
+                    float ke[GPL], ko[GPL];
 #pragma unroll
-                    for (int b = 0; b < NT * 8; ++b) part[b] = 0.0f;
-                    for (int gi = lane; gi < Gn; gi += 32) {
-                        __half s16, z16 = __ushort_as_half(0);
-                        if (p.meta_by_tma) {
-                            s16 = rs[gi];
-                            if (hz) z16 = rz[gi];
-                        } else {
-                            s16 = __float2half_rn(load_as_f32(p.s[m], p.scale_dtype, grow + gi));
-                            if (hz) z16 = __float2half_rn(load_as_f32(p.z[m], p.scale_dtype, grow + gi));
-                        }
-                        float ke, ko;
-                        dst[gi] = make_slot(s16, z16, ke, ko);
-                        if (hz) {
-#pragma unroll
-                            for (int b = 0; b < NT * 8; ++b)
-                                if (b < B) part[b] = fmaf(ke, xsum_e[gi * B + b], fmaf(ko, xsum_o[gi * B + b], part[b]));
+                    for (int j = 0; j < GPL; ++j) {
+                        const int gi = lane + 32 * j;
+                        ke[j] = ko[j] = 0.0f;
+                        if (gi < Gn) {
+                            __half s16, z16 = __ushort_as_half(0);
+                            if (p.meta_by_tma) {
+                                s16 = rs[gi];
+                                if (hz) z16 = rz[gi];
+                            } else {
+                                s16 = __float2half_rn(load_as_f32(p.s[m], p.scale_dtype, grow + gi));
+                                if (hz) z16 = __float2half_rn(load_as_f32(p.z[m], p.scale_dtype, grow + gi));
+                            }
+                            dst[gi] = make_slot(s16, z16, ke[j], ko[j]);
                         }
                     }
                     if (has_zero) {
+                        // zero-point term of this row for every batch row: sum over groups of ke*Xe + ko*Xo
+#pragma unroll 1
+                        for (int b = 0; b < B; ++b) {
+                            float part = 0.0f;
+                            if (hz) {
 #pragma unroll
-                        for (int b = 0; b < NT * 8; ++b) {
-                            if (b < B) {
-                                const float sum = warp_sum(part[b]);
-                                if (lane == 0) corr[((uint32_t)m * TBR + rr) * B + b] = sum;
+                                for (int j = 0; j < GPL; ++j) {
+                                    const int gi = lane + 32 * j;
+                                    if (gi < Gn) part = fmaf(ke[j], xsum_e[gi * B + b], fmaf(ko[j], xsum_o[gi * B + b], part));
+                                }
                             }
+                            part = warp_sum(part);
+                            if (lane == 0) corr[((uint32_t)m * TBR + rr) * B + b] = part;
                         }
                     }
                 }
@@ -439,7 +517,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             if (p.meta_by_tma && lane == 0) mbar_arrive(&meta_empty[mb]);
         }
 
-        float acc[MATS][MAXTB][NT][4];
+        // two accumulator sets per tile: consecutive tensor-core instructions do not depend on each other
+        float acc[MATS][MAXTB][NT][4], acc2[MATS][MAXTB][NT][4];
 #pragma unroll
         for (int m = 0; m < MATS; ++m)
 #pragma unroll
@@ -447,45 +526,15 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[m][tb][nt][i] = 0.0f;
+                    for (int i = 0; i < 4; ++i) acc[m][tb][nt][i] = acc2[m][tb][nt][i] = 0.0f;
 
 #pragma unroll 1
         for (int xc = 0; xc < n_xc; ++xc) {
             const int xk0 = xc * p.xk;
             const int xkn = min(p.xk, p.K - xk0);
-            if (n_xc > 1 || rb == 0) {
-                if (n_xc > 1) named_bar_sync(1, kConsumerThreads);   // everyone is done with the previous chunk
-                // ---- stage activations of [xk0, xk0+xkn) in tensor-core operand order ----
-                const int chunks = xkn / 8;
-                for (int i = ctid; i < B * chunks; i += kConsumerThreads) {
-                    const int b = i / chunks;
-                    const int kk = (i - b * chunks) * 8;
-                    float v[8];
-                    const float inv = need_row_pass ? xscale[B + b] : 1.0f;
-                    const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
-                    load8_act(p, b, xk0 + kk, inv, cta == 0 && rb == 0, v);
-                    __half h[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j] * down);
-                    const int ksx = kk / KS;
-                    const int rem = kk - ksx * KS;
-                    const int tt = rem / KT;
-                    const int c = (rem - tt * KT) / 8;
-                    uint4 out;
-                    if (BITS == 4) {
-                        // nibble order of one weight word after dequantisation: (0,4) (1,5) (2,6) (3,7)
-                        out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[4]) << 16);
-                        out.y = __half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
-                        out.z = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[6]) << 16);
-                        out.w = __half_as_ushort(h[3]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
-                    } else {
-                        out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
-                        out.y = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
-                        out.z = __half_as_ushort(h[4]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
-                        out.w = __half_as_ushort(h[6]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
-                    }
-                    *reinterpret_cast<uint4*>(xperm + ((uint32_t)((ksx * CH + c) * B + b) * 4 + tt) * 16) = out;
-                }
+            if (n_xc > 1) {
+                named_bar_sync(1, kConsumerThreads);   // everyone is done with the previous chunk
+                stage_x(xk0, xkn, cta == 0 && rb == 0);
             }
             if (xc == 0 || n_xc > 1) named_bar_sync(1, kConsumerThreads);   // constants / activations visible
 
@@ -501,12 +550,13 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 #pragma unroll 1
                         for (int c = c_begin; c < c_end; ++c) {
                             const int slot = c_slot;
-                            ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT,
-                                                   ok ? kWaitLimit : 64u) && ok;
+                            if (!(p.dbg & 2))
+                                ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT,
+                                                       ok ? kWaitLimit : 64u) && ok;
                             if (++c_slot == n_stages) { c_slot = 0; c_phase ^= 1; }
                             const int k0 = c * p.kc;
                             const int kcur = min(p.kc, p.K - k0);
-                            const int nks = kcur / KS;
+                            const int nks = (p.dbg & 1) ? 0 : kcur / KS;
                             const uint8_t* stage_w = ring + (uint32_t)slot * stage_bytes + w_off;
                             const uint8_t* xbase = xperm + (uint32_t)((k0 - xk0) / KS) * CH * x_step + x_lane;
 #pragma unroll 1
@@ -547,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                                         // columns >= B read a clamped (valid) batch row; their results are never stored
                                         const uint4 u = *reinterpret_cast<const uint4*>(xk + ch * x_step + x_nt[nt]);
                                         mma_m16n8k16(acc[m][tb][nt], a[0][0], a[0][1], a[0][2], a[0][3], u.x, u.y);
-                                        mma_m16n8k16(acc[m][tb][nt], a[1][0], a[1][1], a[1][2], a[1][3], u.z, u.w);
+                                        mma_m16n8k16(acc2[m][tb][nt], a[1][0], a[1][1], a[1][2], a[1][3], u.z, u.w);
                                     }
                                 }
                             }
@@ -571,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         for (int i = 0; i < 4; ++i) {
                             const int rr = tb * kTileRows + g + (i >> 1) * 8;
                             const int b = nt * 8 + 2 * t + (i & 1);
-                            if (b < B) red[((((uint32_t)m * TBR + rr) * B + b) << 4) + cw] = acc[m][tb][nt][i];
+                            if (b < B) red[((((uint32_t)m * TBR + rr) * B + b) << 4) + cw] = acc[m][tb][nt][i] + acc2[m][tb][nt][i];
                         }
                 }
         named_bar_sync(1, kConsumerThreads);
@@ -687,7 +737,7 @@ __global__ void __launch_bounds__(256) qgemv_generic_kernel(const __grid_constan
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
-template <int BITS, int NT, bool GATE_UP>
+template <int BITS, int NT, bool GATE_UP, int GPL>
 int launch_fast(GemvParams& p, cudaStream_t stream) {
     constexpr int MATS = GATE_UP ? 2 : 1;
     constexpr int KS = BITS == 4 ? 128 : 64;
@@ -762,6 +812,7 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     const int total_stages = max_tiles * MATS * p.n_kc;
     p.logG = 0;
     while ((1 << p.logG) < p.G) ++p.logG;
+    p.dbg = tuning_get("gemv.dbg");
     int stages = tuning_get("gemv.stages");
     if (stages <= 0) stages = kMaxStages;
     stages = std::min({stages, kMaxStages, std::max(2, total_stages)});
@@ -769,7 +820,7 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     p.stages = stages;
     const uint64_t total = off + (uint64_t)stages * p.stage_bytes;
 
-    auto kernel = qgemv_kernel<BITS, NT, GATE_UP>;
+    auto kernel = qgemv_kernel<BITS, NT, GATE_UP, GPL>;
     static bool configured[64] = {};   // per instantiation and device; a race only repeats the call
     int dev = 0;
     cudaGetDevice(&dev);
@@ -807,7 +858,7 @@ bool fast_path_ok(const GemvParams& p, int bits) {
     const int kt = ks / 4;
     if (tuning_get("gemv.force_generic")) return false;
     if (p.K % ks != 0 || p.G % kt != 0 || p.K % p.G != 0 || (p.G & (p.G - 1)) != 0) return false;
-    if (p.B > 16) return false;
+    if (p.B > 16 || p.Gn > 32 * kMaxGroupsPerLane) return false;
     if ((size_t)p.Gn * kTileRows * 8 * 2 * (p.w[1] ? 2 : 1) > 64 * 1024) return false;
     if (!aligned16(p.x) || !aligned16(p.w[0]) || (p.w[1] != nullptr && !aligned16(p.w[1]))) return false;
     if (p.res_in != nullptr && !aligned16(p.res_in)) return false;
@@ -817,10 +868,19 @@ bool fast_path_ok(const GemvParams& p, int bits) {
     return true;
 }
 
+template <int BITS, int NT, bool GATE_UP>
+int dispatch_gpl(GemvParams& p, cudaStream_t stream) {
+    const int gpl = (p.Gn + 31) / 32;      // groups of one row handled per lane in the constants pass
+    if (gpl <= 1) return launch_fast<BITS, NT, GATE_UP, 1>(p, stream);
+    if (gpl <= 2) return launch_fast<BITS, NT, GATE_UP, 2>(p, stream);
+    if (gpl <= 4) return launch_fast<BITS, NT, GATE_UP, 4>(p, stream);
+    return launch_fast<BITS, NT, GATE_UP, 8>(p, stream);
+}
+
 template <bool GATE_UP>
 int dispatch_fast(int bits, GemvParams& p, cudaStream_t stream) {
-    if (bits == 4) return p.B <= 8 ? launch_fast<4, 1, GATE_UP>(p, stream) : launch_fast<4, 2, GATE_UP>(p, stream);
-    return p.B <= 8 ? launch_fast<8, 1, GATE_UP>(p, stream) : launch_fast<8, 2, GATE_UP>(p, stream);
+    if (bits == 4) return p.B <= 8 ? dispatch_gpl<4, 1, GATE_UP>(p, stream) : dispatch_gpl<4, 2, GATE_UP>(p, stream);
+    return p.B <= 8 ? dispatch_gpl<8, 1, GATE_UP>(p, stream) : dispatch_gpl<8, 2, GATE_UP>(p, stream);
 }
 
 }  // namespace
