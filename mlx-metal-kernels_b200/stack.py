@@ -189,7 +189,7 @@ class DecodeStack:
     def _all_gather_rows(self, local, gathered, full=None):
         """[B, n_loc] on every rank -> [B, tp * n_loc] in rank-major column order."""
         import torch.distributed as dist
-        dist.all_gather_into_tensor(gathered, local, group=self.pg)
+        dist.all_gather_into_tensor(gathered.view(-1, local.shape[-1]), local, group=self.pg)
         out = gathered.permute(1, 0, 2).reshape(local.shape[0], -1)
         if full is not None:
             full.copy_(out)
