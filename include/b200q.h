@@ -39,7 +39,8 @@ enum {
     B200Q_ERR_UNSUPPORTED = -2,  /* shape outside what the kernels implement (e.g. head_dim > 128) */
     B200Q_ERR_LAUNCH = -3,       /* cudaGetLastError() after the launch was not cudaSuccess */
     B200Q_ERR_WORKSPACE = -4,    /* workspace pointer NULL or smaller than *_workspace_bytes() */
-    B200Q_ERR_DEVICE_WAIT = -5   /* reported by b200q_device_status(): a bounded device wait gave up */
+    B200Q_ERR_DEVICE_WAIT = -5,  /* reported by b200q_device_status(): a bounded device wait gave up */
+    B200Q_ERR_STATIC_SCRATCH = -6 /* b200q_paged_gqa_decode_static: problem exceeds the built-in scratch array */
 };
 
 int b200q_version(void);
@@ -137,6 +138,32 @@ int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, cons
                            const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
                            int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages, int max_blocks,
                            int group_size, float scale, int q_dtype, int scale_dtype, void* stream);
+
+/* The same attention for callers that cannot allocate device memory at all.  (No counterpart in the
+ * reference: its runtime allocates every kernel output itself.)  Some hosts of this library may not
+ * call cudaMalloc: a plugin running inside another runtime's memory budget, a worker that must not
+ * touch the allocator while a CUDA graph is being captured, or a process whose device memory was
+ * handed out entirely at start-up.  They still own q, the cache and `out`, but have nowhere to put
+ * the split-KV partial results that b200q_paged_gqa_decode keeps in its `workspace` argument.  This
+ * entry point keeps them in a fixed array of b200q_paged_gqa_static_scratch_bytes() (8 MiB) that is
+ * part of the library image: every GPU that loads the library holds those 8 MiB until the process
+ * exits.  It allocates nothing and calls no allocating routine.
+ *   - Limit: returns B200Q_ERR_STATIC_SCRATCH when
+ *     b200q_paged_gqa_workspace_bytes(B, Hq, Hkv, D) exceeds the array (for 32 query heads of
+ *     head_dim 128 over 8 kv heads that is a batch of 200 sequences); use the workspace variant then.
+ *   - The first call on each device looks up the array's device address (with that device current)
+ *     and remembers it.  Make that first call outside any stream capture.
+ *   - Every call on a device shares the one array.  Nothing in it has to start at zero: each call
+ *     writes every partial result it later reads, so leftovers of the previous call are never seen.
+ *     Two calls whose kernels overlap on the GPU (different streams, or graphs replayed
+ *     concurrently) would overwrite each other's partials: keep calls on one device stream-ordered.
+ * Arguments and results are those of b200q_paged_gqa_decode without workspace / workspace_bytes. */
+size_t b200q_paged_gqa_static_scratch_bytes(void);
+int b200q_paged_gqa_decode_static(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                  const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                  const int32_t* lengths, void* out, int B, int Hq, int Hkv, int D,
+                                  int page_size, int64_t num_pages, int max_blocks, int group_size, float scale,
+                                  int q_dtype, int scale_dtype, void* stream);
 
 /* Decode-layer glue: split a fused QKV row [B, (Hq + 2 Hkv) * D] (fp16), apply the interleaved-pair
  * rotary embedding at positions[b] to q and k (tables cos/sin [table_len, D/2] fp32, as

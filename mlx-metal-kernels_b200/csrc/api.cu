@@ -61,6 +61,12 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
                  void* normed_out, int rows, int64_t N, int64_t K, int group_size, int act_dtype, int scale_dtype,
                  int norm_w_dtype, cudaStream_t stream);
 size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int Hkv, int D);
+size_t paged_gqa_static_scratch_bytes_impl();
+int paged_gqa_decode_static_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                 const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                 const int32_t* lengths, void* out, int B, int Hq, int Hkv, int D, int page_size,
+                                 int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                                 int scale_dtype, cudaStream_t stream);
 int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes, const void* k_scales,
                           const void* v_scales, const int32_t* block_table, const int32_t* lengths, void* out,
                           void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size,
@@ -227,6 +233,9 @@ const char* b200q_strerror(int code) {
         case B200Q_ERR_LAUNCH: return "CUDA launch or runtime call failed";
         case B200Q_ERR_WORKSPACE: return "workspace missing or too small";
         case B200Q_ERR_DEVICE_WAIT: return "a bounded device-side wait gave up";
+        case B200Q_ERR_STATIC_SCRATCH:
+            return "problem too large for the library's built-in scratch array (see b200q_paged_gqa_static_scratch_bytes); "
+                   "use b200q_paged_gqa_decode with a caller-allocated workspace";
         default: return "unknown b200q error";
     }
 }
@@ -352,6 +361,18 @@ int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, cons
     return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, workspace,
                                  workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
                                  q_dtype, scale_dtype, (cudaStream_t)stream);
+}
+
+size_t b200q_paged_gqa_static_scratch_bytes(void) { return paged_gqa_static_scratch_bytes_impl(); }
+
+int b200q_paged_gqa_decode_static(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                  const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                  const int32_t* lengths, void* out, int B, int Hq, int Hkv, int D, int page_size,
+                                  int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                                  int scale_dtype, void* stream) {
+    return paged_gqa_decode_static_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, B, Hq,
+                                        Hkv, D, page_size, num_pages, max_blocks, group_size, scale, q_dtype, scale_dtype,
+                                        (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -29,6 +29,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <mutex>
 
 namespace b200q {
 
@@ -690,6 +691,43 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
         if (cudaLaunchKernelEx(&cfg, paged_attn_merge_kernel, p) != cudaSuccess) return B200Q_ERR_LAUNCH;
     }
     return finish_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Variant without a caller-supplied workspace: the split-KV partials live in a fixed array in
+// device memory that belongs to the library image.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 8u << 20;     // 8 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+size_t paged_gqa_static_scratch_bytes_impl() { return kStaticScratchBytes; }
+
+int paged_gqa_decode_static_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                 const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                 const int32_t* lengths, void* out, int B, int Hq, int Hkv, int D, int page_size,
+                                 int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                                 int scale_dtype, cudaStream_t stream) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return B200Q_ERR_BAD_ARG;
+    if (paged_gqa_workspace_bytes_impl(B, Hq, Hkv, D) > kStaticScratchBytes) return B200Q_ERR_STATIC_SCRATCH;
+    // In host code the array's name is only a handle; the device address has to be asked for, once per
+    // device, with that device current.
+    static void* scratch_ptr[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_LAUNCH;
+    void* ptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (scratch_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_attn_static_scratch) != cudaSuccess || p == nullptr) return B200Q_ERR_LAUNCH;
+            scratch_ptr[dev] = p;
+        }
+        ptr = scratch_ptr[dev];
+    }
+    return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, ptr,
+                                 kStaticScratchBytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
+                                 q_dtype, scale_dtype, stream);
 }
 
 }  // namespace b200q

@@ -40,6 +40,9 @@ SIGNATURES = {
     "b200q_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _i, _vp]),
     "b200q_block_table_lookup": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b200q_paged_gqa_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "b200q_paged_gqa_static_scratch_bytes": (_sz, []),
+    "b200q_paged_gqa_decode_static": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i, _i,
+                                           _f, _i, _i, _vp]),
     "b200q_paged_gqa_decode": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64,
                                     _i, _i, _f, _i, _i, _vp]),
 }
