@@ -329,6 +329,17 @@ def run_own(args):
         dist.destroy_process_group()
 
 
+def run_kernels_only():
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(0)
+    entry.load_package()
+    importlib.import_module(f"{entry.PKG_ALIAS}.ops._cabi").load()
+    peak, peak_kind = measured_peaks()
+    print(json.dumps({"kernels": kernel_microbenchmarks(torch.device("cuda", 0), peak), "peak": peak,
+                      "peak_kind": peak_kind}), flush=True)
+
+
 # ------------------------------------------------------------------------------------------------
 # CPU arm: the torch-CPU restatement of the reference path on a bounded sample
 # ------------------------------------------------------------------------------------------------
@@ -417,8 +428,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="run only the C1 matvec / C4 attention micro-benchmarks (the small case used for profiler captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernels_only:
+        run_kernels_only()
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_own(args)

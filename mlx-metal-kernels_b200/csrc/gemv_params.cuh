@@ -1,0 +1,60 @@
+// Parameters shared by the matvec kernels and their host-side dispatch.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200q {
+
+constexpr int kConsumerWarps = 16;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kProducerWarp = kConsumerWarps;
+constexpr int kEpilogueWarp = kConsumerWarps + 1;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;
+constexpr int kTileRows = 16;
+constexpr int kUnitGroups = 8;
+constexpr uint32_t kWaitLimit = 1u << 21;
+constexpr int kMaxStages = 8;
+constexpr int kMaxSlots = 16;
+
+struct GemvParams {
+    // activations
+    const void* x;          // [B, K]
+    const void* res_in;     // norm prologue: x := rmsnorm(x + res_in); may be null
+    const void* norm_w;     // [K]; null = no prologue
+    float eps;
+    void* z_out;            // [B, K] or null
+    void* normed_out;       // [B, K] or null
+    // weights (index 1 only for the fused gate/up kernel)
+    const uint8_t* w[2];
+    const void* s[2];
+    const void* z[2];
+    // outputs
+    const void* residual;   // plain: out = cast(residual + cast(y)); may be null
+    void* y;
+    void* gate_out;
+    void* up_out;
+    void* act_out;
+    int B, N, K, G, Gn;
+    int act_dtype, scale_dtype, norm_w_dtype;
+    int row_bytes;          // bytes of one weight row
+    int kc;                 // k per ring stage (a whole number of units)
+    int n_kc;               // stages per (matrix, tile) over the whole K
+    int nu;                 // units per full stage
+    int stages;
+    int xk;                 // k per staged activation chunk (a whole number of stages)
+    int n_xc;               // activation chunks (1 unless B*K is too large for shared memory)
+    int nslot;              // result slots: 2 (streamed) or one per tile of the CTA (n_xc > 1)
+    int meta_vec;           // scales / zeros are fp16, 16-byte aligned, Gn % 8 == 0: vector loads
+    int rows_lo, rem;       // CTA c owns rows_lo (+1 if c < rem) rows
+    uint32_t off_xs, off_xzero, off_xmx, off_xscale, off_part, off_ring;
+    uint32_t xstride, stage_bytes, row_stride;
+};
+
+// Tensor-core kernels, one translation unit per code width (gemv_q4.cu, gemv_q8.cu).  They return
+// B200Q_ERR_UNSUPPORTED when the problem does not fit their shared-memory plan.
+int gemv_fast_q4(GemvParams& p, bool gate_up, cudaStream_t stream);
+int gemv_fast_q8(GemvParams& p, bool gate_up, cudaStream_t stream);
+int gemv_q4_read_status(int reset, cudaStream_t stream);
+int gemv_q8_read_status(int reset, cudaStream_t stream);
+
+}  // namespace b200q

@@ -455,60 +455,102 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attn_kernel(const __gri
 }
 
 // Merges the partials of every (sequence, query head): one warp each, lanes over d.
-__global__ void __launch_bounds__(128) paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    int* prefix = reinterpret_cast<int*>(smem);
-    pdl_wait();
-    const int total = build_prefix(p, prefix);
+constexpr int kMergeWarps = 8;
+
+// One CTA per (sequence, query head).  The partials of a sequence may sit in every CTA slot of the
+// main kernel (a single long sequence is cut over the whole grid), so the slots are spread over the
+// CTA's warps and their loads are independent of one another; lanes cover the head dimension.
+__global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
+    __shared__ float red[kMergeWarps][128];
+    __shared__ float red_s[2][kMergeWarps];
+    __shared__ int red_i[2][kMergeWarps];
     const int D = p.D;
-    const int ppc = (total + p.grid - 1) / p.grid;
     const int lane = threadIdx.x & 31;
-    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= p.B * p.Hq) return;
-    const int b = item / p.Hq;
-    const int hq = item - b * p.Hq;
-    const int s_lo = prefix[b], s_hi = prefix[b + 1];
+    const int warp = threadIdx.x >> 5;
+    const int b = blockIdx.x / p.Hq;
+    const int hq = blockIdx.x - b * p.Hq;
+    pdl_wait();
+
+    // pages before sequence b and in total (the flattened page list of the main kernel)
+    const int cap = p.max_blocks * p.P;
+    int below = 0, all = 0;
+    for (int i = threadIdx.x; i < p.B; i += kMergeWarps * 32) {
+        const int n = (clamp_len(p.lengths[i], cap) + p.P - 1) / p.P;
+        all += n;
+        if (i < b) below += n;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        below += __shfl_xor_sync(0xffffffffu, below, o);
+        all += __shfl_xor_sync(0xffffffffu, all, o);
+    }
+    if (lane == 0) { red_i[0][warp] = below; red_i[1][warp] = all; }
+    __syncthreads();
+    below = 0; all = 0;
+#pragma unroll
+    for (int w = 0; w < kMergeWarps; ++w) { below += red_i[0][w]; all += red_i[1][w]; }
+    const int total = all;
+    const int s_lo = below;
+    const int s_hi = below + (clamp_len(p.lengths[b], cap) + p.P - 1) / p.P;
+    const int ppc = (total + p.grid - 1) / p.grid;
+
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    float l_tot = 0.0f;
+    float l_part = 0.0f;
     if (s_hi > s_lo) {
         const int c_first = s_lo / ppc, c_last = (s_hi - 1) / ppc;
+        const int n_cand = (c_last - c_first + 1) * p.subs;
         // (cta c, sub) wrote a partial for b iff it walked at least one page of b:
         // pages f = lo_c + sub + j*subs inside [max(lo_c, s_lo), min(hi_c, s_hi))
-        auto wrote = [&](int c, int sub) {
+        auto source = [&](int i) -> const float* {
+            const int c = c_first + i / p.subs;
+            const int sub = i - (i / p.subs) * p.subs;
             const int lo_c = c * ppc, hi_c = min(total, lo_c + ppc);
             const int a = max(lo_c, s_lo), e = min(hi_c, s_hi);
             const int rel = a - lo_c - sub;
             const int first = lo_c + sub + (rel <= 0 ? 0 : (rel + p.subs - 1) / p.subs) * p.subs;
-            return first < e;
+            if (first >= e) return nullptr;
+            return p.partial + ((size_t)((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2);
         };
         float m_tot = -INFINITY;
-        for (int c = c_first; c <= c_last; ++c)
-            for (int sub = 0; sub < p.subs; ++sub)
-                if (wrote(c, sub))
-                    m_tot = fmaxf(m_tot, p.partial[((size_t)((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2) + D]);
-        for (int c = c_first; c <= c_last; ++c)
-            for (int sub = 0; sub < p.subs; ++sub) {
-                if (!wrote(c, sub)) continue;
-                const float* src = p.partial + ((size_t)((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2);
-                const float m = src[D];
-                const float w = (m == -INFINITY) ? 0.0f : exp2f((m - m_tot) * kLog2e);
-                l_tot += w * src[D + 1];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int d = lane + 32 * j;
-                    if (d < D) acc[j] = fmaf(w, src[d], acc[j]);
-                }
-            }
-    }
-    const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int d = lane + 32 * j;
-        if (d < D) {
-            const size_t o = ((size_t)b * p.Hq + hq) * D + d;
-            if (p.q_dtype == B200Q_F16) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(acc[j] * inv);
-            else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(acc[j] * inv);
+        for (int i = threadIdx.x; i < n_cand; i += kMergeWarps * 32) {
+            const float* src = source(i);
+            if (src != nullptr) m_tot = fmaxf(m_tot, src[D]);
         }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m_tot = fmaxf(m_tot, __shfl_xor_sync(0xffffffffu, m_tot, o));
+        if (lane == 0) red_s[0][warp] = m_tot;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < kMergeWarps; ++w) m_tot = fmaxf(m_tot, red_s[0][w]);
+
+#pragma unroll 4
+        for (int i = warp; i < n_cand; i += kMergeWarps) {
+            const float* src = source(i);
+            const bool ok = src != nullptr;
+            const float m = ok ? src[D] : -INFINITY;
+            const float l = ok ? src[D + 1] : 0.0f;
+            const float w = (m == -INFINITY) ? 0.0f : exp2f((m - m_tot) * kLog2e);
+            l_part = fmaf(w, l, l_part);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int d = lane + 32 * j;
+                const float v = (ok && d < D) ? src[d] : 0.0f;
+                acc[j] = fmaf(w, v, acc[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) red[warp][lane + 32 * j] = acc[j];
+    if (lane == 0) red_s[1][warp] = l_part;
+    __syncthreads();
+    if (threadIdx.x < D) {
+        float sum = 0.0f, l_tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kMergeWarps; ++w) { sum += red[w][threadIdx.x]; l_tot += red_s[1][w]; }
+        const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+        const size_t o = ((size_t)b * p.Hq + hq) * D + threadIdx.x;
+        if (p.q_dtype == B200Q_F16) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(sum * inv);
+        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(sum * inv);
     }
 }
 
@@ -680,11 +722,10 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
         if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200Q_ERR_LAUNCH;
     }
     {
-        const int warps = 4;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((B * Hq + warps - 1) / warps);
-        cfg.blockDim = dim3(warps * 32);
-        cfg.dynamicSmemBytes = align_up_u32((B + 1) * sizeof(int), 16);
+        cfg.gridDim = dim3(B * Hq);
+        cfg.blockDim = dim3(kMergeWarps * 32);
+        cfg.dynamicSmemBytes = 0;
         cfg.stream = stream;
         cfg.attrs = attr;
         cfg.numAttrs = tuning_get("no_pdl") ? 0 : 1;

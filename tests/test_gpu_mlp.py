@@ -29,8 +29,9 @@ def test_gate_up_matvec_parity(cuda, bits, shape, N, G, zeros, dtype):
     fn = quant_ops.q4_gate_up_matvec_tiled if bits == 4 else quant_ops.q8_gate_up_matvec_tiled
     gg, gu = fn(*to_dev(cuda, x, gw, uw, gs, us, gz, uz), group_size=G)
     assert gg.shape == wg.shape and gu.shape == wu.shape
-    fast = K % (128 if bits == 4 else 64) == 0
-    tol = TOL if dtype == torch.float16 or not fast else TOL_BF16_TC
+    # bf16 rows are fed to the tensor cores as fp16 (exact power-of-two scaling) against unrounded codes,
+    # while the oracle rounds each dequantised weight to bf16: the bound for bf16 is the oracle's own rounding.
+    tol = TOL if dtype == torch.float16 else TOL_BF16_TC
     assert rel_l2(gg, wg) <= tol and rel_l2(gu, wu) <= tol
     # the projection wrapper takes weights and scales interleaved per projection
     dz = lambda t: None if t is None else t.to(cuda)
