@@ -145,9 +145,10 @@ int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scal
     auto offw = [&](void* base, size_t elems) -> uint8_t* {
         return base ? reinterpret_cast<uint8_t*>(base) + elems * esz : nullptr;
     };
-    for (int b0 = 0; b0 < B; b0 += 16) {
+    int chunk = 16;      // batch rows per launch; halved when the kernel's shared-memory plan does not fit
+    for (int b0 = 0; b0 < B;) {
         GemvParams p = {};
-        const int bn = std::min(16, B - b0);
+        const int bn = std::min(chunk, B - b0);
         p.x = off(x, (size_t)b0 * K);
         p.res_in = off(residual_in, (size_t)b0 * K);
         p.norm_w = norm_weight; p.eps = eps; p.norm_w_dtype = norm_w_dtype;
@@ -160,6 +161,10 @@ int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scal
         p.act_dtype = act_dtype; p.scale_dtype = scale_dtype;
         p.row_bytes = bits == 4 ? (int)((K + 1) / 2) : (int)K;
         int rc = fast_path_ok(p) ? dispatch_fast(bits, p, false, stream) : B200Q_ERR_UNSUPPORTED;
+        if (rc == B200Q_ERR_UNSUPPORTED && bn > 1 && fast_path_ok(p)) {
+            chunk = (bn + 1) / 2;
+            continue;
+        }
         if (rc == B200Q_ERR_UNSUPPORTED) {
             if (norm_weight != nullptr) {
                 // generic route: materialise the normalised rows first (normed_out is required as the buffer)
@@ -173,6 +178,7 @@ int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scal
             rc = launch_generic<false>(p, bits, stream);
         }
         if (rc != B200Q_OK) return rc;
+        b0 += bn;
     }
     return B200Q_OK;
 }
@@ -198,9 +204,10 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
     auto offw = [&](void* base, size_t elems) -> uint8_t* {
         return base ? reinterpret_cast<uint8_t*>(base) + elems * esz : nullptr;
     };
-    for (int b0 = 0; b0 < rows; b0 += 16) {
+    int chunk = 16;      // batch rows per launch; halved when the kernel's shared-memory plan does not fit
+    for (int b0 = 0; b0 < rows;) {
         GemvParams p = {};
-        const int bn = std::min(16, rows - b0);
+        const int bn = std::min(chunk, rows - b0);
         p.x = off(x, (size_t)b0 * K);
         p.res_in = off(residual_in, (size_t)b0 * K);
         p.norm_w = norm_weight; p.eps = eps; p.norm_w_dtype = norm_w_dtype;
@@ -217,6 +224,10 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
         p.row_bytes = bits == 4 ? (int)((K + 1) / 2) : (int)K;
         int rc;
         rc = fast_path_ok(p) ? dispatch_fast(bits, p, true, stream) : B200Q_ERR_UNSUPPORTED;
+        if (rc == B200Q_ERR_UNSUPPORTED && bn > 1 && fast_path_ok(p)) {
+            chunk = (bn + 1) / 2;
+            continue;
+        }
         if (rc == B200Q_ERR_UNSUPPORTED) {
             if (norm_weight != nullptr) {
                 // generic route: materialise the normalised rows first (normed_out is required as the buffer)
@@ -230,6 +241,7 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
             rc = launch_generic<true>(p, bits, stream);
         }
         if (rc != B200Q_OK) return rc;
+        b0 += bn;
     }
     return B200Q_OK;
 }

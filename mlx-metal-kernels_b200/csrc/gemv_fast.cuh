@@ -33,6 +33,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <type_traits>
 
 namespace b200q {
 namespace {
@@ -108,24 +109,42 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds_f128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
 template <int NWORDS>
-__device__ __forceinline__ void load_words(const uint8_t* ptr, uint32_t (&w)[NWORDS]) {
+__device__ __forceinline__ void lds_words(uint32_t addr, uint32_t (&w)[NWORDS]) {
     if constexpr (NWORDS == 1) {
-        w[0] = *reinterpret_cast<const uint32_t*>(ptr);
+        w[0] = lds_u32(addr);
     } else if constexpr (NWORDS == 2) {
-        const uint2 u = *reinterpret_cast<const uint2*>(ptr);
-        w[0] = u.x; w[1] = u.y;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr));
     } else {
 #pragma unroll
         for (int i = 0; i < NWORDS / 4; ++i) {
-            const uint4 u = *reinterpret_cast<const uint4*>(ptr + 16 * i);
+            const uint4 u = lds_u128(addr + 16 * i);
             w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
         }
     }
 }
 
-__device__ __forceinline__ float half_lo(uint32_t u) { return __half2float(__ushort_as_half((unsigned short)(u & 0xFFFFu))); }
-__device__ __forceinline__ float half_hi(uint32_t u) { return __half2float(__ushort_as_half((unsigned short)(u >> 16))); }
+__device__ __forceinline__ float half_bits_to_float(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 
 // BITS: code width.  LOGG: log2(group size) in {5, 6, 7}.  NB: tensor-core columns per quantisation group
 // (batch rows rounded up to 1, 2, 4, 8).  NT: column tiles (2 only with NB == 8: 9..16 batch rows).
@@ -142,7 +161,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     constexpr int NP = NB;                        // passes over a unit
     constexpr int GS = kUnitGroups / NB;          // groups side by side in one accumulator
     constexpr int BC = NB * NT;                   // batch columns kept per row
-    constexpr int MW = (NB < 2 ? 2 : NB) / 2;     // 32-bit words of scales (and of zeros) per lane and row
     constexpr float OFF_ODD = BITS == 4 ? 64.0f : 1024.0f;
     static_assert(NT == 1 || NB == 8, "two column tiles only with eight batch columns per group");
 
@@ -154,14 +172,19 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     uint64_t* slot_free = tile_done + kMaxSlots;   // [kMaxSlots] the epilogue has read (and zeroed) the slot
 
     const int cta = blockIdx.x;
-    const int r_lo = cta * p.rows_lo + min(cta, p.rem);
+    // Rows of this CTA: either one contiguous range (rows dealt evenly), or every gridDim-th tile of 16 rows.
+    const bool interleave = p.interleave != 0;
+    const int total_tiles = (p.N + kTileRows - 1) / kTileRows;
+    const int r_lo = interleave ? cta * kTileRows : cta * p.rows_lo + min(cta, p.rem);
     const int r_cnt = p.rows_lo + (cta < p.rem ? 1 : 0);
-    const int r_hi = r_lo + r_cnt;
-    const int n_tiles = (r_cnt + kTileRows - 1) / kTileRows;
+    const int r_hi = interleave ? p.N : r_lo + r_cnt;
+    const int tile_step = interleave ? (int)gridDim.x * kTileRows : kTileRows;
+    const int n_tiles = interleave ? (total_tiles - cta + (int)gridDim.x - 1) / (int)gridDim.x : (r_cnt + kTileRows - 1) / kTileRows;
     const int n_xc = p.n_xc;
     const int cpx = p.xk / p.kc;                   // stages per (matrix, tile, activation chunk)
     const int nslot = p.nslot;
     const int B = p.B;
+    const int Gn = p.Gn;
 
     float* part = reinterpret_cast<float*>(smem + p.off_part);     // [nslot][MATS][16 warps][16 rows][BC]
     uint8_t* xzero = smem + p.off_xzero;
@@ -170,7 +193,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kConsumerWarps);
         }
-        for (int s = 0; s < kMaxSlots; ++s) {
+        for (int s = 0; s < nslot; ++s) {
             mbar_init(&tile_done[s], kConsumerWarps);
             mbar_init(&slot_free[s], 1);
         }
@@ -182,6 +205,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     pdl_launch_dependents();
 
     uint8_t* ring = smem + p.off_ring;
+    uint8_t* mbuf = smem + p.off_meta;             // [meta_depth][scales | zeros][16 rows][Gn] halves
+    const uint32_t mbuf_half = (uint32_t)kTileRows * Gn * 2;   // bytes of one of the four arrays
 
     // Producer and consumers walk the stages in the same order: activation chunk, tile, matrix, k-chunk.
     if (warp == kProducerWarp) {
@@ -189,13 +214,17 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         int slot = 0;
         uint32_t phase = 1;
         bool first_pass = true;
+        int q = 0;                                  // (tile, matrix) visits so far
         for (int xc = 0; xc < n_xc; ++xc) {
             const int c_begin = xc * cpx;
             const int c_end = min(p.n_kc, c_begin + cpx);
             for (int tl = 0; tl < n_tiles; ++tl) {
-                const int row0 = r_lo + tl * kTileRows;
+                const int row0 = r_lo + tl * tile_step;
                 const int rows = min(kTileRows, r_hi - row0);
-                for (int m = 0; m < MATS; ++m) {
+                for (int m = 0; m < MATS; ++m, ++q) {
+                    const void* sp = (MATS == 2 && m != 0) ? p.s[1] : p.s[0];
+                    const void* zp = (MATS == 2 && m != 0) ? p.z[1] : p.z[0];
+                    const uint8_t* wp = (MATS == 2 && m != 0) ? p.w[1] : p.w[0];
                     for (int c = c_begin; c < c_end; ++c) {
                         if (!first_pass)
                             ok = mbar_wait_bounded(&empty[slot], phase, &g_device_status, EV_GEMV_EMPTY_WAIT,
@@ -204,12 +233,33 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         const int kcur = min(p.kc, p.K - k0);
                         const uint32_t bytes_row = (uint32_t)(kcur * BITS / 8);
                         uint8_t* stage = ring + (size_t)slot * p.stage_bytes;
-                        if (lane == 0) mbar_arrive_expect_tx(&full[slot], bytes_row * rows);
+                        // the scales / zero points of the (tile, matrix) ride on the barrier of its first stage; their
+                        // buffers form a ring deep enough that the buffer being overwritten belongs to a tile whose
+                        // stages have all been released (meta_depth >= stages / stages-per-tile + 1)
+                        const bool with_meta = p.meta_vec && c == c_begin;
+                        const uint32_t meta_bytes = (uint32_t)rows * Gn * 2;
+                        if (lane == 0)
+                            mbar_arrive_expect_tx(&full[slot], bytes_row * rows + (with_meta ? meta_bytes * (zp != nullptr ? 2u : 1u) : 0u));
                         __syncwarp();
+                        // one copy instruction for the whole stage (issuing is costly per instruction, not per lane):
+                        // lanes 0..15 one weight row each, lanes 16 / 17 the scales / zero points
+                        uint8_t* dst = nullptr;
+                        const uint8_t* src = nullptr;
+                        uint32_t nbytes = 0;
                         if (lane < rows) {
-                            const uint8_t* src = ((MATS == 2 && m != 0) ? p.w[1] : p.w[0]) + (size_t)(row0 + lane) * p.row_bytes + (size_t)k0 * BITS / 8;
-                            bulk_g2s(stage + (size_t)lane * p.row_stride, src, bytes_row, &full[slot]);
+                            src = wp + (size_t)(row0 + lane) * p.row_bytes + (size_t)k0 * BITS / 8;
+                            dst = stage + (size_t)lane * p.row_stride;
+                            nbytes = bytes_row;
+                        } else if (with_meta && lane == 16) {
+                            src = reinterpret_cast<const uint8_t*>(sp) + (size_t)row0 * Gn * 2;
+                            dst = mbuf + (size_t)(q % p.meta_depth) * 2 * mbuf_half;
+                            nbytes = meta_bytes;
+                        } else if (with_meta && lane == 17 && zp != nullptr) {
+                            src = reinterpret_cast<const uint8_t*>(zp) + (size_t)row0 * Gn * 2;
+                            dst = mbuf + (size_t)(q % p.meta_depth) * 2 * mbuf_half + mbuf_half;
+                            nbytes = meta_bytes;
                         }
+                        if (nbytes != 0) bulk_g2s(dst, src, nbytes, &full[slot]);
                         if (++slot == p.stages) { slot = 0; phase ^= 1; first_pass = false; }
                     }
                 }
@@ -230,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             const int ps = tl % nslot;
             ok = mbar_wait_bounded(&tile_done[ps], (uint32_t)(tl / nslot) & 1u, &g_device_status, EV_GEMV_FULL_WAIT,
                                    ok ? kWaitLimit : 64u) && ok;
-            const int row0 = r_lo + tl * kTileRows;
+            const int row0 = r_lo + tl * tile_step;
             const int rows = min(kTileRows, r_hi - row0);
             float* slot_base = part + (size_t)ps * MATS * kConsumerWarps * kTileRows * BC;
             for (int it = lane; it < kTileRows * BC; it += 32) {
@@ -281,7 +331,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int ctid = threadIdx.x;               // 0 .. kConsumerThreads-1
     const int g = lane >> 2;
     const int t = lane & 3;
-    const int Gn = p.Gn;
 
     uint8_t* xs = smem + p.off_xs;                                    // [B] rows of xstride bytes, fp16, operand order
     float2* xmx = reinterpret_cast<float2*>(smem + p.off_xmx);        // [groups of the chunk (+ padding)][BC] {M, X}
@@ -329,10 +378,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     // ---- stage activations of [xk0, xk0+xkn) as fp16 in tensor-core operand order, then per-group sums ----
     auto stage_x = [&](int xk0, int xkn, bool write_side) {
         const int chunks = xkn / 8;
-#pragma unroll 2
-        for (int i = ctid; i < B * chunks; i += kConsumerThreads) {
-            const int b = i / chunks;
-            const int kk = (i - b * chunks) * 8;
+        int b = 0, ci = ctid;                    // item = (batch row b, 8-block ci); walked without divisions
+        while (ci >= chunks) { ci -= chunks; ++b; }
+#pragma unroll 1
+        while (b < B) {
+            const int kk = ci * 8;
             float v[8];
             const float inv = need_row_pass ? xscale[B + b] : 1.0f;
             const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
@@ -354,6 +404,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                 out.w = __half_as_ushort(h[6]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
             }
             *reinterpret_cast<uint4*>(xs + (size_t)b * p.xstride + (size_t)kk * 2) = out;
+            ci += kConsumerThreads;
+            while (ci >= chunks && b < B) { ci -= chunks; ++b; }
         }
         named_bar_sync(1, kConsumerThreads);
         // {M, X} per (group, batch column): X = sum of the group's activations, M = sum of offset * activation
@@ -362,10 +414,10 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         const int gpad = (gc + kUnitGroups - 1) / kUnitGroups * kUnitGroups;
         for (int i = ctid; i < gpad * BC; i += kConsumerThreads) {
             const int gi = i / BC;
-            const int b = i - gi * BC;
+            const int bcol = i - gi * BC;
             float se = 0.0f, so = 0.0f;
-            if (gi < gc && b < B) {
-                const uint8_t* src = xs + (size_t)b * p.xstride + (size_t)(gi << LOGG) * 2;
+            if (gi < gc && bcol < B) {
+                const uint8_t* src = xs + (size_t)bcol * p.xstride + (size_t)(gi << LOGG) * 2;
 #pragma unroll
                 for (int j = 0; j < G / 8; ++j) {
                     const uint4 u = *reinterpret_cast<const uint4*>(src + 16 * j);
@@ -388,20 +440,220 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         named_bar_sync(1, kConsumerThreads);
     };
 
-    // ---- this warp's units: global unit number = stage number * nu + index in stage, dealt modulo 16 ----
-    struct Unit { int S, i, tl, m, c; bool valid; };
-    struct Meta { uint32_t s[2][MW], z[2][MW]; };
-    const int NU = p.nu;
-
     bool ok = true;
     int c_slot = 0;
     uint32_t c_phase = 0;
-    uint32_t ph16 = 0;                          // (units before the current activation chunk) mod 16
+    uint32_t ph16 = 0;                          // (units before the current stage) mod the number of consumer warps
+    int q = 0;                                  // (tile, matrix) visits so far
 
-    // column bookkeeping of this lane: as B operand it feeds column g, as accumulator owner columns 2t, 2t+1
+    // per-lane constants.  As B operand this lane feeds column g, as accumulator owner columns 2t, 2t+1.
     const int my_js = g / NB;                   // group slot of column g within a pass
     const int my_b = g % NB;                    // batch row of column g (first column tile)
-    const int goff = NB <= 2 ? 2 * t : (NB == 4 ? 4 * (t >> 1) : 0);   // first group of this lane's scale words
+    const uint32_t ring_u = smem_u32(ring);
+    const uint32_t a_lane = (uint32_t)g * p.row_stride + t * LB;
+    const uint32_t a_row8 = 8u * p.row_stride;
+    const uint32_t xz_u = smem_u32(xzero) + t * XB;
+    const uint32_t xmx_u = smem_u32(xmx);
+    const uint32_t mbuf_u = smem_u32(mbuf);
+    uint32_t x_lane[NT];
+    bool bvalid[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int b = nt * 8 + my_b;
+        bvalid[nt] = b < B;
+        x_lane[nt] = smem_u32(xs) + (uint32_t)min(b, B - 1) * p.xstride + t * XB;
+    }
+    // accumulator columns 2t, 2t+1: two groups (NB == 1) or two batch rows of one group
+    const int jc = NB == 1 ? 0 : (2 * t) / NB;  // group slot of this lane's accumulator columns
+    const int b0 = NB == 1 ? 0 : (2 * t) % NB;  // their first batch row
+    const uint32_t meta_lane = (uint32_t)(g * Gn + (NB == 1 ? 2 * t : jc * NP)) * 2;   // byte offset inside a scales array
+    const uint32_t meta_row8 = (uint32_t)8 * Gn * 2;
+    float* part_lane = part + ((size_t)cw * kTileRows) * BC;
+
+    // ---- one unit: 16 rows x 8 groups ----
+    //   a_u    shared address of this lane's bytes of the unit's first group (row g)
+    //   xoff   byte offset of the unit inside a staged activation row
+    //   gi     first group of the unit inside the staged chunk;  gabs: inside the whole row
+    auto process_unit = [&](auto full_c, uint32_t a_u, uint32_t xoff, int gi, int gabs, int ng, uint32_t mb_u,
+                            int m, int row0, float* dst, bool has_z) {
+        constexpr bool FULL = decltype(full_c)::value;
+        float y[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) y[nt][i] = 0.0f;
+
+        // The unit's 8 groups in execution order e = pass * GS + slot; the operands of group e + 1 are
+        // fetched from shared memory before the tensor-core work of group e is issued.
+        constexpr int NXV = BITS == 4 ? NW : NW / 2;          // 16-byte activation loads per group and column tile
+        constexpr bool PIPE = LOGG <= 6 && NT == 1;           // (wider groups / two column tiles: not enough registers)
+        struct Operands { uint32_t wa[NW], wb[NW]; };
+        auto fetch = [&](int e, Operands& o) {
+            const int pass = e / GS, js = e % GS;
+            const int gl = js * NP + pass;                   // group of the unit handled by slot js in this pass
+            lds_words<NW>(a_u + gl * GB, o.wa);
+            lds_words<NW>(a_u + a_row8 + gl * GB, o.wb);
+        };
+        auto present = [&](int e) { return FULL || ((e % GS) * NP + e / GS) < ng; };
+        Operands ops[PIPE ? 2 : 1];
+        if (PIPE) fetch(0, ops[0]);       // group 0 always exists
+
+#pragma unroll
+        for (int pass = 0; pass < NP; ++pass) {
+            float acc[NT][2][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[nt][a][i] = 0.0f;
+            // This lane's column belongs to one group of the pass (slot my_js): only that group's activations
+            // are fetched; for the other groups of the pass the lane feeds zeros.
+            uint4 xr[NT][NXV];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t xb = bvalid[nt] ? x_lane[nt] + xoff + (uint32_t)(my_js * NP + pass) * (G * 2) : xz_u;
+#pragma unroll
+                for (int v = 0; v < NXV; ++v) xr[nt][v] = lds_u128(xb + v * 16);
+            }
+#pragma unroll
+            for (int js = 0; js < GS; ++js) {
+                const int e = pass * GS + js;
+                const bool mine = GS == 1 || my_js == js;
+                if (PIPE && e + 1 < kUnitGroups && present(e + 1)) fetch(e + 1, ops[(e + 1) & 1]);
+                if (present(e)) {
+                    if (!PIPE) fetch(e, ops[0]);
+                    const Operands& o = ops[PIPE ? (e & 1) : 0];
+                    if constexpr (BITS == 4) {
+#pragma unroll
+                        for (int wd = 0; wd < NW; ++wd) {
+                            const uint32_t a_lo = o.wa[wd], b_lo = o.wb[wd];
+                            const uint32_t a_hi = a_lo >> 8, b_hi = b_lo >> 8;
+                            const uint32_t aL0 = lop3_and_or(a_lo, 0x000F000Fu, 0x64006400u), aH0 = lop3_and_or(a_lo, 0x00F000F0u, 0x54005400u);
+                            const uint32_t bL0 = lop3_and_or(b_lo, 0x000F000Fu, 0x64006400u), bH0 = lop3_and_or(b_lo, 0x00F000F0u, 0x54005400u);
+#if defined(B200Q_DBG_HALF_LOP)
+                            const uint32_t aL1 = a_hi, aH1 = a_hi, bL1 = b_hi, bH1 = b_hi;
+#else
+                            const uint32_t aL1 = lop3_and_or(a_hi, 0x000F000Fu, 0x64006400u), aH1 = lop3_and_or(a_hi, 0x00F000F0u, 0x54005400u);
+                            const uint32_t bL1 = lop3_and_or(b_hi, 0x000F000Fu, 0x64006400u), bH1 = lop3_and_or(b_hi, 0x00F000F0u, 0x54005400u);
+#endif
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const uint4 xq = xr[nt][wd];
+                                const uint4 xv = make_uint4(mine ? xq.x : 0u, mine ? xq.y : 0u, mine ? xq.z : 0u, mine ? xq.w : 0u);
+                                mma_m16n8k16(acc[nt][0], aL0, bL0, aH0, bH0, xv.x, xv.y);
+#if defined(B200Q_DBG_HALF_MMA)
+                                acc[nt][1][0] += __uint_as_float(aL1 ^ bL1 ^ aH1 ^ bH1 ^ xv.z ^ xv.w);
+#else
+                                mma_m16n8k16(acc[nt][1], aL1, bL1, aH1, bH1, xv.z, xv.w);
+#endif
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int wp = 0; wp < NW / 2; ++wp) {
+                            const uint32_t a0 = prmt(o.wa[2 * wp], 0x64646464u, 0x4140u), a1 = prmt(o.wa[2 * wp], 0x64646464u, 0x4342u);
+                            const uint32_t c0 = prmt(o.wb[2 * wp], 0x64646464u, 0x4140u), c1 = prmt(o.wb[2 * wp], 0x64646464u, 0x4342u);
+                            const uint32_t a2 = prmt(o.wa[2 * wp + 1], 0x64646464u, 0x4140u), a3 = prmt(o.wa[2 * wp + 1], 0x64646464u, 0x4342u);
+                            const uint32_t c2 = prmt(o.wb[2 * wp + 1], 0x64646464u, 0x4140u), c3 = prmt(o.wb[2 * wp + 1], 0x64646464u, 0x4342u);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const uint4 xq = xr[nt][wp];
+                                const uint4 xv = make_uint4(mine ? xq.x : 0u, mine ? xq.y : 0u, mine ? xq.z : 0u, mine ? xq.w : 0u);
+                                mma_m16n8k16(acc[nt][0], a0, c0, a1, c1, xv.x, xv.y);
+                                mma_m16n8k16(acc[nt][1], a2, c2, a3, c3, xv.z, xv.w);
+                            }
+                        }
+                    }
+                }
+            }
+            // affine part of the groups of this pass: y += s * (c - M - z * X)
+            {
+                float s0[2], s1[2], z0[2], z1[2];
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    if (p.meta_vec) {
+                        const uint32_t ma = mb_u + meta_lane + rr * meta_row8 + (uint32_t)gabs * 2;
+                        if constexpr (NB == 1) {
+                            const uint32_t sw = lds_u32(ma);
+                            s0[rr] = half_bits_to_float(sw & 0xFFFFu); s1[rr] = half_bits_to_float(sw >> 16);
+                            if (has_z) {
+                                const uint32_t zw = lds_u32(ma + mbuf_half);
+                                z0[rr] = half_bits_to_float(zw & 0xFFFFu); z1[rr] = half_bits_to_float(zw >> 16);
+                            } else {
+                                z0[rr] = z1[rr] = 0.0f;
+                            }
+                        } else {
+                            s0[rr] = s1[rr] = half_bits_to_float(lds_u16(ma + pass * 2));
+                            z0[rr] = z1[rr] = has_z ? half_bits_to_float(lds_u16(ma + mbuf_half + pass * 2)) : 0.0f;
+                        }
+                    } else {
+                        // scales in another dtype or layout: read them where they lie (rounded to fp16 like the copy path)
+                        const void* sp = (MATS == 2 && m != 0) ? p.s[1] : p.s[0];
+                        const void* zp = (MATS == 2 && m != 0) ? p.z[1] : p.z[0];
+                        const int row = min(row0 + g + 8 * rr, p.N - 1);
+                        const int ga = gabs + (NB == 1 ? 2 * t : jc * NP + pass);
+                        const int64_t e = (int64_t)row * Gn + ga;
+                        s0[rr] = ga < Gn ? __half2float(__float2half_rn(load_as_f32(sp, p.scale_dtype, e))) : 0.0f;
+                        z0[rr] = (ga < Gn && zp != nullptr) ? __half2float(__float2half_rn(load_as_f32(zp, p.scale_dtype, e))) : 0.0f;
+                        if constexpr (NB == 1) {
+                            s1[rr] = ga + 1 < Gn ? __half2float(__float2half_rn(load_as_f32(sp, p.scale_dtype, e + 1))) : 0.0f;
+                            z1[rr] = (ga + 1 < Gn && zp != nullptr) ? __half2float(__float2half_rn(load_as_f32(zp, p.scale_dtype, e + 1))) : 0.0f;
+                        } else {
+                            s1[rr] = s0[rr];
+                            z1[rr] = z0[rr];
+                        }
+                    }
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int e = NB == 1 ? (gi + 2 * t) : ((gi + jc * NP + pass) * BC + nt * 8 + b0);
+                    const float4 mx = lds_f128(xmx_u + (uint32_t)e * 8);   // {M, X} of column 2t, {M, X} of 2t+1
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        float v0 = acc[nt][0][2 * rr] + acc[nt][1][2 * rr];
+                        float v1 = acc[nt][0][2 * rr + 1] + acc[nt][1][2 * rr + 1];
+                        v0 = fmaf(-z0[rr], mx.y, v0 - mx.x);
+                        v1 = fmaf(-z1[rr], mx.w, v1 - mx.z);
+                        y[nt][2 * rr] = fmaf(s0[rr], v0, y[nt][2 * rr]);
+                        y[nt][2 * rr + 1] = fmaf(s1[rr], v1, y[nt][2 * rr + 1]);
+                    }
+                }
+            }
+        }
+
+        // ---- fold the lanes that hold pieces of the same (row, batch row), add into this warp's slot ----
+        if constexpr (NB == 1) {
+            float v0 = y[0][0] + y[0][1], v1 = y[0][2] + y[0][3];
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 2); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+            if (t == 0) {
+                dst[g] += v0;
+                dst[g + 8] += v1;
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float v = y[nt][i];
+                    if constexpr (NB == 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    if constexpr (NB <= 4) v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    y[nt][i] = v;
+                }
+                const bool writer = NB == 2 ? (t == 0) : (NB == 4 ? (t < 2) : true);
+                if (writer) {
+                    const int col = nt * 8 + b0;
+                    float2* d0 = reinterpret_cast<float2*>(dst + (size_t)g * BC + col);
+                    float2* d1 = reinterpret_cast<float2*>(dst + (size_t)(g + 8) * BC + col);
+                    float2 a = *d0, b2 = *d1;
+                    a.x += y[nt][0]; a.y += y[nt][1];
+                    b2.x += y[nt][2]; b2.y += y[nt][3];
+                    *d0 = a; *d1 = b2;
+                }
+            }
+        }
+    };
 
 #pragma unroll 1
     for (int xc = 0; xc < n_xc; ++xc) {
@@ -412,252 +664,53 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
         const int c_begin = xc * cpx;
         const int c_end = min(p.n_kc, c_begin + cpx);
-        const int nS = n_tiles * MATS * (c_end - c_begin);
-
-        auto units_in = [&](int c) { return (min(p.kc, p.K - c * p.kc) + UK - 1) / UK; };
-        auto normalize = [&](Unit& u) {
-            for (;;) {
-                while (u.i >= NU) {
-                    u.i -= NU;
-                    ++u.S;
-                    if (++u.c == c_end) {
-                        u.c = c_begin;
-                        if (++u.m == MATS) { u.m = 0; ++u.tl; }
-                    }
-                }
-                if (u.S >= nS) { u.valid = false; return; }
-                if (u.i < units_in(u.c)) { u.valid = true; return; }
-                u.i += 16;
-            }
-        };
-        auto load_meta = [&](const Unit& u, Meta& mt) {
-            const int gi0 = (u.c * p.kc + u.i * UK) >> LOGG;           // first group of the unit
-            const void* sp = (MATS == 2 && u.m != 0) ? p.s[1] : p.s[0];
-            const void* zp = (MATS == 2 && u.m != 0) ? p.z[1] : p.z[0];
-#pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
-                const int row = min(r_lo + u.tl * kTileRows + g + 8 * rr, p.N - 1);
-                const int64_t e = (int64_t)row * Gn + gi0 + goff;
-                if (p.meta_vec && gi0 + kUnitGroups <= Gn) {
-                    const __half* sh = reinterpret_cast<const __half*>(sp) + e;
-                    const __half* zh = reinterpret_cast<const __half*>(zp) + e;
-                    if constexpr (MW == 1) {
-                        mt.s[rr][0] = __ldg(reinterpret_cast<const uint32_t*>(sh));
-                        mt.z[rr][0] = zp != nullptr ? __ldg(reinterpret_cast<const uint32_t*>(zh)) : 0u;
-                    } else if constexpr (MW == 2) {
-                        const uint2 a = __ldg(reinterpret_cast<const uint2*>(sh));
-                        mt.s[rr][0] = a.x; mt.s[rr][1] = a.y;
-                        uint2 c2 = make_uint2(0u, 0u);
-                        if (zp != nullptr) c2 = __ldg(reinterpret_cast<const uint2*>(zh));
-                        mt.z[rr][0] = c2.x; mt.z[rr][1] = c2.y;
-                    } else {
-                        const uint4 a = __ldg(reinterpret_cast<const uint4*>(sh));
-                        mt.s[rr][0] = a.x; mt.s[rr][1] = a.y; mt.s[rr][2] = a.z; mt.s[rr][3] = a.w;
-                        uint4 c4 = make_uint4(0u, 0u, 0u, 0u);
-                        if (zp != nullptr) c4 = __ldg(reinterpret_cast<const uint4*>(zh));
-                        mt.z[rr][0] = c4.x; mt.z[rr][1] = c4.y; mt.z[rr][2] = c4.z; mt.z[rr][3] = c4.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < MW; ++j) {
-                        uint32_t sw = 0u, zw = 0u;
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            const int gidx = gi0 + goff + 2 * j + hh;
-                            if (gidx < Gn) {
-                                const int64_t ee = (int64_t)row * Gn + gidx;
-                                sw |= (uint32_t)__half_as_ushort(__float2half_rn(load_as_f32(sp, p.scale_dtype, ee))) << (16 * hh);
-                                if (zp != nullptr)
-                                    zw |= (uint32_t)__half_as_ushort(__float2half_rn(load_as_f32(zp, p.scale_dtype, ee))) << (16 * hh);
-                            }
-                        }
-                        mt.s[rr][j] = sw;
-                        mt.z[rr][j] = zw;
-                    }
-                }
-            }
-        };
-
-        // ---- one unit: 16 rows x 8 groups of stage `slot` ----
-        auto process_unit = [&](int slot, const Unit& u, const Meta& mt, int ps) {
-            const int k_in_stage = u.i * UK;
-            const int kcur = min(p.kc, p.K - u.c * p.kc);
-            const int ng = min(kUnitGroups, (kcur - k_in_stage) >> LOGG);
-            const uint8_t* aw = ring + (size_t)slot * p.stage_bytes + (size_t)g * p.row_stride + (size_t)u.i * (kUnitGroups * GB) + t * LB;
-            const uint8_t* aw8 = aw + (size_t)8 * p.row_stride;
-            const int kl = u.c * p.kc + k_in_stage - xk0;                 // k of the unit inside the staged activations
-            const int gi = kl >> LOGG;
-            const uint8_t* xz = xzero + t * XB;
-            const uint8_t* xrow[NT];
-            bool bvalid[NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int b = nt * 8 + my_b;
-                bvalid[nt] = b < B;
-                xrow[nt] = xs + (size_t)min(b, B - 1) * p.xstride + (size_t)kl * 2 + t * XB;
-            }
-            float y[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) y[nt][i] = 0.0f;
-
-#pragma unroll
-            for (int pass = 0; pass < NP; ++pass) {
-                float acc[NT][2][4];
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int a = 0; a < 2; ++a)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) acc[nt][a][i] = 0.0f;
-#pragma unroll
-                for (int js = 0; js < GS; ++js) {
-                    const int gl = js * NP + pass;               // group of the unit handled by slot js in this pass
-                    if (gl < ng) {
-                        uint32_t wa[NW], wb[NW];
-                        load_words<NW>(aw + gl * GB, wa);
-                        load_words<NW>(aw8 + gl * GB, wb);
-                        const uint8_t* xb[NT];
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) xb[nt] = ((my_js == js && bvalid[nt]) ? xrow[nt] : xz) + gl * (G * 2);
-                        if constexpr (BITS == 4) {
-#pragma unroll
-                            for (int wd = 0; wd < NW; ++wd) {
-                                const uint32_t a_lo = wa[wd], b_lo = wb[wd];
-                                const uint32_t a_hi = a_lo >> 8, b_hi = b_lo >> 8;
-                                const uint32_t aL0 = lop3_and_or(a_lo, 0x000F000Fu, 0x64006400u), aH0 = lop3_and_or(a_lo, 0x00F000F0u, 0x54005400u);
-                                const uint32_t bL0 = lop3_and_or(b_lo, 0x000F000Fu, 0x64006400u), bH0 = lop3_and_or(b_lo, 0x00F000F0u, 0x54005400u);
-                                const uint32_t aL1 = lop3_and_or(a_hi, 0x000F000Fu, 0x64006400u), aH1 = lop3_and_or(a_hi, 0x00F000F0u, 0x54005400u);
-                                const uint32_t bL1 = lop3_and_or(b_hi, 0x000F000Fu, 0x64006400u), bH1 = lop3_and_or(b_hi, 0x00F000F0u, 0x54005400u);
-#pragma unroll
-                                for (int nt = 0; nt < NT; ++nt) {
-                                    const uint4 xv = *reinterpret_cast<const uint4*>(xb[nt] + wd * 16);
-                                    mma_m16n8k16(acc[nt][0], aL0, bL0, aH0, bH0, xv.x, xv.y);
-                                    mma_m16n8k16(acc[nt][1], aL1, bL1, aH1, bH1, xv.z, xv.w);
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int wp = 0; wp < NW / 2; ++wp) {
-                                const uint32_t a0 = prmt(wa[2 * wp], 0x64646464u, 0x4140u), a1 = prmt(wa[2 * wp], 0x64646464u, 0x4342u);
-                                const uint32_t b0 = prmt(wb[2 * wp], 0x64646464u, 0x4140u), b1 = prmt(wb[2 * wp], 0x64646464u, 0x4342u);
-                                const uint32_t a2 = prmt(wa[2 * wp + 1], 0x64646464u, 0x4140u), a3 = prmt(wa[2 * wp + 1], 0x64646464u, 0x4342u);
-                                const uint32_t b2 = prmt(wb[2 * wp + 1], 0x64646464u, 0x4140u), b3 = prmt(wb[2 * wp + 1], 0x64646464u, 0x4342u);
-#pragma unroll
-                                for (int nt = 0; nt < NT; ++nt) {
-                                    const uint4 xv = *reinterpret_cast<const uint4*>(xb[nt] + wp * 16);
-                                    mma_m16n8k16(acc[nt][0], a0, b0, a1, b1, xv.x, xv.y);
-                                    mma_m16n8k16(acc[nt][1], a2, b2, a3, b3, xv.z, xv.w);
-                                }
-                            }
-                        }
-                    }
-                }
-                // affine part of the groups of this pass: y += s * (c - M - z * X)
-                {
-                    // accumulator columns 2t, 2t+1: two groups (NB == 1) or two batch rows of one group
-                    const int gl_c = NB == 1 ? 2 * t : ((2 * t) / NB) * NP + pass;
-                    const int b0 = NB == 1 ? 0 : (2 * t) % NB;
-                    float s0[2], s1[2], z0[2], z1[2];
-#pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) {
-                        if constexpr (NB == 1) {
-                            s0[rr] = half_lo(mt.s[rr][0]); s1[rr] = half_hi(mt.s[rr][0]);
-                            z0[rr] = half_lo(mt.z[rr][0]); z1[rr] = half_hi(mt.z[rr][0]);
-                        } else {
-                            const uint32_t sw = mt.s[rr][pass >> 1], zw = mt.z[rr][pass >> 1];
-                            s0[rr] = s1[rr] = (pass & 1) ? half_hi(sw) : half_lo(sw);
-                            z0[rr] = z1[rr] = (pass & 1) ? half_hi(zw) : half_lo(zw);
-                        }
-                    }
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const int e = NB == 1 ? (gi + gl_c) : ((gi + gl_c) * BC + nt * 8 + b0);
-                        const float4 mx = *reinterpret_cast<const float4*>(xmx + e);   // {M, X} of column 2t, {M, X} of 2t+1
-#pragma unroll
-                        for (int rr = 0; rr < 2; ++rr) {
-                            float v0 = acc[nt][0][2 * rr] + acc[nt][1][2 * rr];
-                            float v1 = acc[nt][0][2 * rr + 1] + acc[nt][1][2 * rr + 1];
-                            v0 = fmaf(-z0[rr], mx.y, v0 - mx.x);
-                            v1 = fmaf(-z1[rr], mx.w, v1 - mx.z);
-                            y[nt][2 * rr] = fmaf(s0[rr], v0, y[nt][2 * rr]);
-                            y[nt][2 * rr + 1] = fmaf(s1[rr], v1, y[nt][2 * rr + 1]);
-                        }
-                    }
-                }
-            }
-
-            // ---- fold the lanes that hold pieces of the same (row, batch row), add into this warp's slot ----
-            float* dst = part + ((((size_t)ps * MATS + u.m) * kConsumerWarps + cw) * kTileRows) * BC;
-            if constexpr (NB == 1) {
-                float v0 = y[0][0] + y[0][1], v1 = y[0][2] + y[0][3];
-                v0 += __shfl_xor_sync(0xffffffffu, v0, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-                v0 += __shfl_xor_sync(0xffffffffu, v0, 2); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
-                if (t == 0) {
-                    dst[g] += v0;
-                    dst[g + 8] += v1;
-                }
-            } else {
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float v = y[nt][i];
-                        if constexpr (NB == 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
-                        if constexpr (NB <= 4) v += __shfl_xor_sync(0xffffffffu, v, 2);
-                        y[nt][i] = v;
-                    }
-                    const bool writer = NB == 2 ? (t == 0) : (NB == 4 ? (t < 2) : true);
-                    if (writer) {
-                        const int col = nt * 8 + (2 * t) % NB;
-                        float2* d0 = reinterpret_cast<float2*>(dst + (size_t)g * BC + col);
-                        float2* d1 = reinterpret_cast<float2*>(dst + (size_t)(g + 8) * BC + col);
-                        float2 a = *d0, b2 = *d1;
-                        a.x += y[nt][0]; a.y += y[nt][1];
-                        b2.x += y[nt][2]; b2.y += y[nt][3];
-                        *d0 = a; *d1 = b2;
-                    }
-                }
-            }
-        };
-
-        Unit cur = {0, (int)((cw - ph16) & 15u), 0, 0, c_begin, true};
-        normalize(cur);
-        Meta mcur;
-        if (cur.valid) load_meta(cur, mcur);
-        int S = 0;
 #pragma unroll 1
         for (int tl = 0; tl < n_tiles; ++tl) {
             const int ps = tl % nslot;
+            const int row0 = r_lo + tl * tile_step;
             if (xc == 0 && tl >= nslot)
                 ok = mbar_wait_bounded(&slot_free[ps], (uint32_t)(tl / nslot - 1) & 1u, &g_device_status, EV_GEMV_EMPTY_WAIT,
                                        ok ? kWaitLimit : 64u) && ok;
 #pragma unroll 1
-            for (int mc = 0; mc < MATS * (c_end - c_begin); ++mc, ++S) {
-                const int slot = c_slot;
-                ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT, ok ? kWaitLimit : 64u) && ok;
-                if (++c_slot == p.stages) { c_slot = 0; c_phase ^= 1; }
+            for (int m = 0; m < MATS; ++m, ++q) {
+                const int mb = q % p.meta_depth;
+                const uint32_t mb_u = mbuf_u + (uint32_t)mb * 2 * mbuf_half;
+                const bool has_z = ((MATS == 2 && m != 0) ? p.z[1] : p.z[0]) != nullptr;
+                float* dst = part_lane + ((size_t)ps * MATS + m) * kConsumerWarps * kTileRows * BC;
 #pragma unroll 1
-                while (cur.valid && cur.S == S) {
-                    Unit nxt = cur;
-                    nxt.i += 16;
-                    normalize(nxt);
-                    Meta mnext;
-                    if (nxt.valid) load_meta(nxt, mnext);
-                    process_unit(slot, cur, mcur, ps);
-                    cur = nxt;
-                    if (nxt.valid) mcur = mnext;
+                for (int c = c_begin; c < c_end; ++c) {
+                    const int slot = c_slot;
+                    ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT, ok ? kWaitLimit : 64u) && ok;
+                    if (++c_slot == p.stages) { c_slot = 0; c_phase ^= 1; }
+                    const int k0 = c * p.kc;
+                    const int kcur = min(p.kc, p.K - k0);
+                    const int groups = kcur >> LOGG;                         // groups in this stage
+                    const int nu_real = (groups + kUnitGroups - 1) / kUnitGroups;
+                    const uint32_t stage_u = ring_u + (uint32_t)slot * p.stage_bytes + a_lane;
+#pragma unroll 1
+                    for (int i = (int)(((uint32_t)cw + kConsumerWarps - ph16) % kConsumerWarps); i < nu_real; i += kConsumerWarps) {
+                        const int ng = min(kUnitGroups, groups - i * kUnitGroups);
+                        const uint32_t a_u = stage_u + (uint32_t)i * (kUnitGroups * GB);
+                        const int kl = k0 + i * UK - xk0;
+                        const int gabs = (k0 + i * UK) >> LOGG;
+#if defined(B200Q_DBG_NO_COMPUTE)
+                        if (p.K < 0)
+#endif
+                        if (ng == kUnitGroups)
+                            process_unit(std::true_type{}, a_u, (uint32_t)kl * 2, kl >> LOGG, gabs, ng, mb_u, m, row0, dst, has_z);
+                        else
+                            process_unit(std::false_type{}, a_u, (uint32_t)kl * 2, kl >> LOGG, gabs, ng, mb_u, m, row0, dst, has_z);
+                    }
+                    ph16 = (ph16 + (uint32_t)p.nu) % kConsumerWarps;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
             }
             if (xc == n_xc - 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tile_done[ps]);
             }
         }
-        ph16 = (ph16 + (uint32_t)nS * (uint32_t)NU) & 15u;
     }
 }
 
@@ -690,13 +743,18 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     int grid = (int)std::max<int64_t>(1, std::min<int64_t>(sms, tiles));
     p.rows_lo = p.N / grid;
     p.rem = p.N % grid;
-    const int max_tiles = (p.rows_lo + (p.rem ? 1 : 0) + kTileRows - 1) / kTileRows;
+    p.interleave = tuning_get("gemv.interleave");
+    const int max_tiles = p.interleave ? (int)((tiles + grid - 1) / grid) : (p.rows_lo + (p.rem ? 1 : 0) + kTileRows - 1) / kTileRows;
 
     p.meta_vec = p.scale_dtype == B200Q_F16 && (p.Gn % 8 == 0) && aligned16(p.s[0]) &&
                  (p.z[0] == nullptr || aligned16(p.z[0])) &&
                  (MATS == 1 || (aligned16(p.s[1]) && (p.z[1] == nullptr || aligned16(p.z[1]))));
     // stage rows are padded so that the 8 rows a warp reads at once fall into different banks
+#if defined(B200Q_DBG_NO_PAD)
+    const uint32_t row_pad = 0;
+#else
     const uint32_t row_pad = LB == 32 ? 16 : 4 * LB;
+#endif
     p.row_stride = align_up((uint32_t)(kc * BITS / 8), 128) + row_pad;
     p.stage_bytes = align_up(kTileRows * p.row_stride, 128);
     const uint32_t x_pad = G == 32 ? 64 : 16;
@@ -712,7 +770,10 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
         if (n_xc == 1 && bi != 0) break;      // nothing new to try
         p.xk = xk;
         p.n_xc = n_xc;
-        p.nslot = n_xc == 1 ? std::min(2, max_tiles) : max_tiles;
+        // result slots: a consumer warp may start tile t only after the epilogue of tile t - nslot, so a
+        // handful of slots keeps the tiles (often a single stage each) flowing
+        const int slot_bytes = MATS * kConsumerWarps * kTileRows * BC * 4;
+        p.nslot = n_xc == 1 ? std::min(max_tiles, std::max(2, std::min(8, (32 * 1024) / slot_bytes))) : max_tiles;
         if (p.nslot > kMaxSlots) return B200Q_ERR_UNSUPPORTED;
         p.xstride = align_up((uint32_t)xk * 2, 128) + x_pad;
         off = align_up((2 * kMaxStages + 2 * kMaxSlots) * sizeof(uint64_t), 128);
@@ -721,19 +782,29 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
         p.off_xmx = off;    off += align_up((uint32_t)(xk / G + kUnitGroups) * BC * 8, 128);
         p.off_xscale = off; off += align_up((uint32_t)p.B * 2 * 4, 128);
         p.off_part = off;   off += align_up((uint32_t)p.nslot * MATS * kConsumerWarps * kTileRows * BC * 4, 128);
-        p.off_ring = off;
-        fits = off + 3ull * p.stage_bytes <= smem_cap;
+        // Ring depth and the buffers for scales / zero points are chosen together.  The scales of a (tile,
+        // matrix) ride on its first stage and are overwritten meta_depth (tile, matrix) visits later, which is
+        // safe once all stages of the old visit have been released: meta_depth >= ceil(stages / cpass) + 1.
+        const int cpass = std::min(p.n_kc, xk / kc);
+        const int total_stages = max_tiles * MATS * p.n_kc;   // everything the CTA will ever stream
+        int want = tuning_get("gemv.stages");
+        if (want <= 0) want = kMaxStages;
+        want = std::min({want, kMaxStages, std::max(2, total_stages)});
+        const uint32_t meta_one = p.meta_vec ? (uint32_t)2 * kTileRows * p.Gn * 2 : 0;
+        for (int st = want; st >= 2 && !fits; --st) {
+            const int depth = (st + cpass - 1) / cpass + 1;
+            const uint32_t ring_off = off + align_up((uint32_t)depth * meta_one, 128);
+            if (ring_off + (uint64_t)st * p.stage_bytes > smem_cap) continue;
+            if (st < 3 && st < want) break;                   // too shallow to stream: try a smaller activation chunk
+            p.stages = st;
+            p.meta_depth = depth;
+            p.off_meta = off;
+            p.off_ring = ring_off;
+            fits = true;
+        }
     }
     if (!fits) return B200Q_ERR_UNSUPPORTED;
-
-    // ring depth: everything the CTA will ever stream if that is little, else as deep as shared memory allows
-    const int total_stages = max_tiles * MATS * p.n_kc;
-    int stages = tuning_get("gemv.stages");
-    if (stages <= 0) stages = kMaxStages;
-    stages = std::min({stages, kMaxStages, std::max(2, total_stages)});
-    while (stages > 2 && off + (uint64_t)stages * p.stage_bytes > smem_cap) --stages;
-    p.stages = stages;
-    const uint64_t total = off + (uint64_t)stages * p.stage_bytes;
+    const uint64_t total = p.off_ring + (uint64_t)p.stages * p.stage_bytes;
 
     auto kernel = qgemv_kernel<BITS, LOGG, NB, NT, GATE_UP>;
     static bool configured[64] = {};   // per instantiation and device; a race only repeats the call

@@ -5,7 +5,10 @@
 
 namespace b200q {
 
-constexpr int kConsumerWarps = 16;
+#ifndef B200Q_GEMV_WARPS
+#define B200Q_GEMV_WARPS 16
+#endif
+constexpr int kConsumerWarps = B200Q_GEMV_WARPS;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kProducerWarp = kConsumerWarps;
 constexpr int kEpilogueWarp = kConsumerWarps + 1;
@@ -44,9 +47,11 @@ struct GemvParams {
     int xk;                 // k per staged activation chunk (a whole number of stages)
     int n_xc;               // activation chunks (1 unless B*K is too large for shared memory)
     int nslot;              // result slots: 2 (streamed) or one per tile of the CTA (n_xc > 1)
+    int meta_depth;         // buffers for the scales / zero points of a (tile, matrix)
     int meta_vec;           // scales / zeros are fp16, 16-byte aligned, Gn % 8 == 0: vector loads
+    int interleave;         // 1: CTA c takes tiles c, c + grid, ... instead of a contiguous row range
     int rows_lo, rem;       // CTA c owns rows_lo (+1 if c < rem) rows
-    uint32_t off_xs, off_xzero, off_xmx, off_xscale, off_part, off_ring;
+    uint32_t off_xs, off_xzero, off_xmx, off_xscale, off_part, off_meta, off_ring;
     uint32_t xstride, stage_bytes, row_stride;
 };
 
