@@ -38,6 +38,13 @@
 namespace b200q {
 namespace {
 
+#if defined(B200Q_DBG_TRACE)
+__device__ unsigned long long g_trace[4 * 1024];
+#define TRACE(kind, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 1024) g_trace[(kind) * 1024 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE(kind, idx) do { } while (0)
+#endif
+
 // ---- activation source: 8 consecutive values of batch row b at k, as the reference would hold them --------
 __device__ __forceinline__ void load8_raw(const void* base, int dtype, int64_t idx, float (&v)[8]) {
     const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + idx);
@@ -190,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     uint8_t* xzero = smem + p.off_xzero;
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], kProducerWarps);
             mbar_init(&empty[s], kConsumerWarps);
         }
         for (int s = 0; s < nslot; ++s) {
@@ -209,12 +216,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const uint32_t mbuf_half = (uint32_t)kTileRows * Gn * 2;   // bytes of one of the four arrays
 
     // Producer and consumers walk the stages in the same order: activation chunk, tile, matrix, k-chunk.
-    if (warp == kProducerWarp) {
+    if (warp >= kFirstProducerWarp && warp < kFirstProducerWarp + kProducerWarps) {
+        const int pw = warp - kFirstProducerWarp;
         bool ok = true;
         int slot = 0;
         uint32_t phase = 1;
         bool first_pass = true;
         int q = 0;                                  // (tile, matrix) visits so far
+        int trace_n = 0; (void)trace_n;
         for (int xc = 0; xc < n_xc; ++xc) {
             const int c_begin = xc * cpx;
             const int c_end = min(p.n_kc, c_begin + cpx);
@@ -229,6 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         if (!first_pass)
                             ok = mbar_wait_bounded(&empty[slot], phase, &g_device_status, EV_GEMV_EMPTY_WAIT,
                                                    ok ? kWaitLimit : 64u) && ok;
+                        if (pw == 0) { TRACE(2, trace_n); }
                         const int k0 = c * p.kc;
                         const int kcur = min(p.kc, p.K - k0);
                         const uint32_t bytes_row = (uint32_t)(kcur * BITS / 8);
@@ -238,28 +248,30 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         // stages have all been released (meta_depth >= stages / stages-per-tile + 1)
                         const bool with_meta = p.meta_vec && c == c_begin;
                         const uint32_t meta_bytes = (uint32_t)rows * Gn * 2;
-                        if (lane == 0)
-                            mbar_arrive_expect_tx(&full[slot], bytes_row * rows + (with_meta ? meta_bytes * (zp != nullptr ? 2u : 1u) : 0u));
-                        __syncwarp();
-                        // one copy instruction for the whole stage (issuing is costly per instruction, not per lane):
-                        // lanes 0..15 one weight row each, lanes 16 / 17 the scales / zero points
+                        // copy number ci of the stage: 0..15 one weight row each, 16 / 17 the scales / zero points;
+                        // producer warp pw issues ci = pw, pw + kProducerWarps, ... (one per lane)
+                        const int ci = pw + kProducerWarps * lane;
                         uint8_t* dst = nullptr;
                         const uint8_t* src = nullptr;
                         uint32_t nbytes = 0;
-                        if (lane < rows) {
-                            src = wp + (size_t)(row0 + lane) * p.row_bytes + (size_t)k0 * BITS / 8;
-                            dst = stage + (size_t)lane * p.row_stride;
+                        if (ci < rows) {
+                            src = wp + (size_t)(row0 + ci) * p.row_bytes + (size_t)k0 * BITS / 8;
+                            dst = stage + (size_t)ci * p.row_stride;
                             nbytes = bytes_row;
-                        } else if (with_meta && lane == 16) {
+                        } else if (with_meta && ci == 16) {
                             src = reinterpret_cast<const uint8_t*>(sp) + (size_t)row0 * Gn * 2;
                             dst = mbuf + (size_t)(q % p.meta_depth) * 2 * mbuf_half;
                             nbytes = meta_bytes;
-                        } else if (with_meta && lane == 17 && zp != nullptr) {
+                        } else if (with_meta && ci == 17 && zp != nullptr) {
                             src = reinterpret_cast<const uint8_t*>(zp) + (size_t)row0 * Gn * 2;
                             dst = mbuf + (size_t)(q % p.meta_depth) * 2 * mbuf_half + mbuf_half;
                             nbytes = meta_bytes;
                         }
+                        const uint32_t warp_bytes = __reduce_add_sync(0xffffffffu, nbytes);
+                        if (lane == 0) mbar_arrive_expect_tx(&full[slot], warp_bytes);
+                        __syncwarp();
                         if (nbytes != 0) bulk_g2s(dst, src, nbytes, &full[slot]);
+                        if (pw == 0) { TRACE(0, trace_n); } ++trace_n;
                         if (++slot == p.stages) { slot = 0; phase ^= 1; first_pass = false; }
                     }
                 }
@@ -443,8 +455,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     bool ok = true;
     int c_slot = 0;
     uint32_t c_phase = 0;
-    uint32_t ph16 = 0;                          // (units before the current stage) mod the number of consumer warps
-    int q = 0;                                  // (tile, matrix) visits so far
+    int first_unit = cw;                        // index of this warp's first unit in the current stage (units are dealt round-robin)
+    int mb_idx = 0;                             // scale / zero-point buffer of the current (tile, matrix) visit
+    int trace_c = 0; (void)trace_c;
 
     // per-lane constants.  As B operand this lane feeds column g, as accumulator owner columns 2t, 2t+1.
     const int my_js = g / NB;                   // group slot of column g within a pass
@@ -541,8 +554,12 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                             for (int nt = 0; nt < NT; ++nt) {
                                 const uint4 xq = xr[nt][wd];
                                 const uint4 xv = make_uint4(mine ? xq.x : 0u, mine ? xq.y : 0u, mine ? xq.z : 0u, mine ? xq.w : 0u);
+#if defined(B200Q_DBG_NO_MMA)
+                                acc[nt][0][0] += __uint_as_float(aL0 ^ bL0 ^ aH0 ^ bH0 ^ xv.x ^ xv.y);
+#else
                                 mma_m16n8k16(acc[nt][0], aL0, bL0, aH0, bH0, xv.x, xv.y);
-#if defined(B200Q_DBG_HALF_MMA)
+#endif
+#if defined(B200Q_DBG_HALF_MMA) || defined(B200Q_DBG_NO_MMA)
                                 acc[nt][1][0] += __uint_as_float(aL1 ^ bL1 ^ aH1 ^ bH1 ^ xv.z ^ xv.w);
 #else
                                 mma_m16n8k16(acc[nt][1], aL1, bL1, aH1, bH1, xv.z, xv.w);
@@ -664,33 +681,38 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
         const int c_begin = xc * cpx;
         const int c_end = min(p.n_kc, c_begin + cpx);
+        // All counters below are advanced incrementally: a consumer warp touches every stage, most of them
+        // without finding a unit of its own, so the per-stage bookkeeping has to stay a handful of instructions.
+        int ps = 0;                                // result slot of the tile and the parity of its slot_free barrier
+        uint32_t sf_parity = 0;                    // (tile / nslot - 1) & 1, meaningful from tile nslot on
+        int row0 = r_lo;
+        const int nu_stage = p.nu;
+        const uint32_t part_slot_stride = (uint32_t)MATS * kConsumerWarps * kTileRows * BC;
+        const uint32_t part_mat_stride = (uint32_t)kConsumerWarps * kTileRows * BC;
+        float* dst_tile = part_lane;
 #pragma unroll 1
         for (int tl = 0; tl < n_tiles; ++tl) {
-            const int ps = tl % nslot;
-            const int row0 = r_lo + tl * tile_step;
             if (xc == 0 && tl >= nslot)
-                ok = mbar_wait_bounded(&slot_free[ps], (uint32_t)(tl / nslot - 1) & 1u, &g_device_status, EV_GEMV_EMPTY_WAIT,
+                ok = mbar_wait_bounded(&slot_free[ps], sf_parity, &g_device_status, EV_GEMV_EMPTY_WAIT,
                                        ok ? kWaitLimit : 64u) && ok;
 #pragma unroll 1
-            for (int m = 0; m < MATS; ++m, ++q) {
-                const int mb = q % p.meta_depth;
-                const uint32_t mb_u = mbuf_u + (uint32_t)mb * 2 * mbuf_half;
+            for (int m = 0; m < MATS; ++m) {
+                const uint32_t mb_u = mbuf_u + (uint32_t)mb_idx * 2 * mbuf_half;
                 const bool has_z = ((MATS == 2 && m != 0) ? p.z[1] : p.z[0]) != nullptr;
-                float* dst = part_lane + ((size_t)ps * MATS + m) * kConsumerWarps * kTileRows * BC;
+                float* dst = dst_tile + (MATS == 2 && m != 0 ? part_mat_stride : 0u);
+                int k0 = c_begin * p.kc;
 #pragma unroll 1
-                for (int c = c_begin; c < c_end; ++c) {
+                for (int c = c_begin; c < c_end; ++c, k0 += p.kc) {
                     const int slot = c_slot;
+                    if (cw == 0) { TRACE(3, trace_c); }
                     ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT, ok ? kWaitLimit : 64u) && ok;
+                    if (cw == 0) { TRACE(1, trace_c); } ++trace_c;
                     if (++c_slot == p.stages) { c_slot = 0; c_phase ^= 1; }
-                    const int k0 = c * p.kc;
-                    const int kcur = min(p.kc, p.K - k0);
-                    const int groups = kcur >> LOGG;                         // groups in this stage
-                    const int nu_real = (groups + kUnitGroups - 1) / kUnitGroups;
-                    const uint32_t stage_u = ring_u + (uint32_t)slot * p.stage_bytes + a_lane;
+                    const int groups = min(p.kc, p.K - k0) >> LOGG;          // groups in this stage
 #pragma unroll 1
-                    for (int i = (int)(((uint32_t)cw + kConsumerWarps - ph16) % kConsumerWarps); i < nu_real; i += kConsumerWarps) {
+                    for (int i = first_unit; i * kUnitGroups < groups; i += kConsumerWarps) {
                         const int ng = min(kUnitGroups, groups - i * kUnitGroups);
-                        const uint32_t a_u = stage_u + (uint32_t)i * (kUnitGroups * GB);
+                        const uint32_t a_u = ring_u + (uint32_t)slot * p.stage_bytes + a_lane + (uint32_t)i * (kUnitGroups * GB);
                         const int kl = k0 + i * UK - xk0;
                         const int gabs = (k0 + i * UK) >> LOGG;
 #if defined(B200Q_DBG_NO_COMPUTE)
@@ -701,15 +723,21 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         else
                             process_unit(std::false_type{}, a_u, (uint32_t)kl * 2, kl >> LOGG, gabs, ng, mb_u, m, row0, dst, has_z);
                     }
-                    ph16 = (ph16 + (uint32_t)p.nu) % kConsumerWarps;
+                    // index of this warp's first unit in the next stage: units are numbered through the stages
+                    first_unit -= nu_stage;
+                    while (first_unit < 0) first_unit += kConsumerWarps;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[slot]);
                 }
+                if (++mb_idx == p.meta_depth) mb_idx = 0;
             }
             if (xc == n_xc - 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tile_done[ps]);
             }
+            row0 += tile_step;
+            dst_tile += part_slot_stride;
+            if (++ps == nslot) { ps = 0; dst_tile = part_lane; if (tl >= nslot) sf_parity ^= 1; }
         }
     }
 }
