@@ -351,103 +351,146 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
     // per batch row: inv_rms (norm prologue) and the power of two that maps bf16 rows into fp16 range
     if (need_row_pass) {
-        for (int b = cw; b < B; b += kConsumerWarps) {
-            float inv = 1.0f;
-            if (p.norm_w != nullptr) {
-                float ss = 0.0f;
-                for (int k = lane * 8; k < p.K; k += 256) {
-                    float zv[8];
-                    load8_z(p, b, k, zv);
+        float* scratch = xscale + 2 * B;                      // [2][consumer warps] partial sums / maxima
+        if (B <= 4) {
+            // few rows: every consumer thread takes part in each row (fixed-order sums: bitwise reproducible)
+            for (int b = 0; b < B; ++b) {
+                float inv = 1.0f;
+                if (p.norm_w != nullptr) {
+                    float ss = 0.0f;
+                    for (int k = ctid * 8; k < p.K; k += kConsumerThreads * 8) {
+                        float zv[8];
+                        load8_z(p, b, k, zv);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
-                }
-                ss = warp_sum(ss);
-                inv = rsqrtf(ss / (float)p.K + p.eps);
-            }
-            float sc = 1.0f;
-            if (p.act_dtype == B200Q_BF16) {
-                float mx = 0.0f;
-                for (int k = lane * 8; k < p.K; k += 256) {
-                    float v[8];
-                    load8_act(p, b, k, inv, false, v);
+                        for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
+                    }
+                    ss = warp_sum(ss);
+                    if (lane == 0) scratch[cw] = ss;
+                    named_bar_sync(1, kConsumerThreads);
+                    float tot = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
+                    for (int w = 0; w < kConsumerWarps; ++w) tot += scratch[w];
+                    inv = rsqrtf(tot / (float)p.K + p.eps);
                 }
-                mx = warp_max(mx);
-                int ex = 0;
-                if (mx > 0.0f && mx < INFINITY) frexpf(mx, &ex);
-                ex = max(-100, min(114, ex - 14));
-                sc = exp2f((float)ex);
+                float sc = 1.0f;
+                if (p.act_dtype == B200Q_BF16) {
+                    float mx = 0.0f;
+                    for (int k = ctid * 8; k < p.K; k += kConsumerThreads * 8) {
+                        float v[8];
+                        load8_act(p, b, k, inv, false, v);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
+                    }
+                    mx = warp_max(mx);
+                    if (lane == 0) scratch[kConsumerWarps + cw] = mx;
+                    named_bar_sync(1, kConsumerThreads);
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; ++w) mx = fmaxf(mx, scratch[kConsumerWarps + w]);
+                    int ex = 0;
+                    if (mx > 0.0f && mx < INFINITY) frexpf(mx, &ex);
+                    ex = max(-100, min(114, ex - 14));
+                    sc = exp2f((float)ex);
+                }
+                if (ctid == 0) {
+                    xscale[b] = sc;
+                    xscale[B + b] = inv;
+                }
+                named_bar_sync(1, kConsumerThreads);          // scratch may be reused, xscale is visible
             }
-            if (lane == 0) {
-                xscale[b] = sc;
-                xscale[B + b] = inv;
+        } else {
+            for (int b = cw; b < B; b += kConsumerWarps) {
+                float inv = 1.0f;
+                if (p.norm_w != nullptr) {
+                    float ss = 0.0f;
+                    for (int k = lane * 8; k < p.K; k += 256) {
+                        float zv[8];
+                        load8_z(p, b, k, zv);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
+                    }
+                    ss = warp_sum(ss);
+                    inv = rsqrtf(ss / (float)p.K + p.eps);
+                }
+                float sc = 1.0f;
+                if (p.act_dtype == B200Q_BF16) {
+                    float mx = 0.0f;
+                    for (int k = lane * 8; k < p.K; k += 256) {
+                        float v[8];
+                        load8_act(p, b, k, inv, false, v);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
+                    }
+                    mx = warp_max(mx);
+                    int ex = 0;
+                    if (mx > 0.0f && mx < INFINITY) frexpf(mx, &ex);
+                    ex = max(-100, min(114, ex - 14));
+                    sc = exp2f((float)ex);
+                }
+                if (lane == 0) {
+                    xscale[b] = sc;
+                    xscale[B + b] = inv;
+                }
             }
+            named_bar_sync(1, kConsumerThreads);
         }
-        named_bar_sync(1, kConsumerThreads);
     }
 
-    // ---- stage activations of [xk0, xk0+xkn) as fp16 in tensor-core operand order, then per-group sums ----
+    // ---- stage activations of [xk0, xk0+xkn) as fp16 in tensor-core operand order, with their per-group sums ----
     auto stage_x = [&](int xk0, int xkn, bool write_side) {
+        constexpr int CPG = G / 8;                 // 8-value blocks per group: the lanes that share a group
         const int chunks = xkn / 8;
-        int b = 0, ci = ctid;                    // item = (batch row b, 8-block ci); walked without divisions
-        while (ci >= chunks) { ci -= chunks; ++b; }
-#pragma unroll 1
-        while (b < B) {
-            const int kk = ci * 8;
-            float v[8];
-            const float inv = need_row_pass ? xscale[B + b] : 1.0f;
-            const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
-            load8_act(p, b, xk0 + kk, inv, write_side, v);
-            __half h[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j] * down);
-            uint4 out;
-            if (BITS == 4) {
-                // order of the codes of one weight word as the tensor core sees them: (0,4) (1,5) (2,6) (3,7)
-                out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[4]) << 16);
-                out.y = __half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
-                out.z = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[6]) << 16);
-                out.w = __half_as_ushort(h[3]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
-            } else {
-                out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
-                out.y = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
-                out.z = __half_as_ushort(h[4]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
-                out.w = __half_as_ushort(h[6]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
-            }
-            *reinterpret_cast<uint4*>(xs + (size_t)b * p.xstride + (size_t)kk * 2) = out;
-            ci += kConsumerThreads;
-            while (ci >= chunks && b < B) { ci -= chunks; ++b; }
-        }
-        named_bar_sync(1, kConsumerThreads);
-        // {M, X} per (group, batch column): X = sum of the group's activations, M = sum of offset * activation
-        // (offset 1024 for low nibbles / bytes, 64 for high nibbles); zeros for padding groups and columns.
+        const int total = B * chunks;
         const int gc = xkn >> LOGG;
         const int gpad = (gc + kUnitGroups - 1) / kUnitGroups * kUnitGroups;
+        // zeros for padding groups and unused batch columns
         for (int i = ctid; i < gpad * BC; i += kConsumerThreads) {
             const int gi = i / BC;
-            const int bcol = i - gi * BC;
+            if (gi >= gc || i - gi * BC >= B) xmx[i] = make_float2(0.0f, 0.0f);
+        }
+#pragma unroll 1
+        for (int base = 0; base < total; base += kConsumerThreads) {   // same trip count for every thread (shuffles below)
+            const int i = base + ctid;
+            const bool live = i < total;
+            const int b = live ? i / chunks : 0;
+            const int ci = live ? i - b * chunks : 0;
             float se = 0.0f, so = 0.0f;
-            if (gi < gc && bcol < B) {
-                const uint8_t* src = xs + (size_t)bcol * p.xstride + (size_t)(gi << LOGG) * 2;
+            if (live) {
+                const int kk = ci * 8;
+                float v[8];
+                const float inv = need_row_pass ? xscale[B + b] : 1.0f;
+                const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
+                load8_act(p, b, xk0 + kk, inv, write_side, v);
+                __half h[8];
 #pragma unroll
-                for (int j = 0; j < G / 8; ++j) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(src + 16 * j);
-                    const __half2 h0 = *reinterpret_cast<const __half2*>(&u.x);
-                    const __half2 h1 = *reinterpret_cast<const __half2*>(&u.y);
-                    const __half2 h2 = *reinterpret_cast<const __half2*>(&u.z);
-                    const __half2 h3 = *reinterpret_cast<const __half2*>(&u.w);
-                    const float a0 = __low2float(h0) + __high2float(h0), a1 = __low2float(h1) + __high2float(h1);
-                    const float a2 = __low2float(h2) + __high2float(h2), a3 = __low2float(h3) + __high2float(h3);
-                    if (BITS == 4) {            // words 0 and 2 hold even k, 1 and 3 odd k
-                        se += a0 + a2;
-                        so += a1 + a3;
-                    } else {
-                        se += (a0 + a1) + (a2 + a3);
-                    }
+                for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j] * down);
+                uint4 out;
+                if (BITS == 4) {
+                    // order of the codes of one weight word as the tensor core sees them: (0,4) (1,5) (2,6) (3,7)
+                    out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[4]) << 16);
+                    out.y = __half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
+                    out.z = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[6]) << 16);
+                    out.w = __half_as_ushort(h[3]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
+                    se = (__half2float(h[0]) + __half2float(h[2])) + (__half2float(h[4]) + __half2float(h[6]));
+                    so = (__half2float(h[1]) + __half2float(h[3])) + (__half2float(h[5]) + __half2float(h[7]));
+                } else {
+                    out.x = __half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
+                    out.y = __half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
+                    out.z = __half_as_ushort(h[4]) | ((uint32_t)__half_as_ushort(h[5]) << 16);
+                    out.w = __half_as_ushort(h[6]) | ((uint32_t)__half_as_ushort(h[7]) << 16);
+                    se = ((__half2float(h[0]) + __half2float(h[1])) + (__half2float(h[2]) + __half2float(h[3]))) +
+                         ((__half2float(h[4]) + __half2float(h[5])) + (__half2float(h[6]) + __half2float(h[7])));
                 }
+                *reinterpret_cast<uint4*>(xs + (size_t)b * p.xstride + (size_t)kk * 2) = out;
             }
-            xmx[i] = make_float2(1024.0f * se + OFF_ODD * so, se + so);
+            // {M, X} per (group, batch column): X = sum of the group's activations, M = sum of offset * activation
+            // (offset 1024 for low nibbles / bytes, 64 for high nibbles).  The CPG blocks of a group sit in
+            // adjacent lanes (rows hold a whole number of groups), summed in a fixed order.
+#pragma unroll
+            for (int o = 1; o < CPG; o <<= 1) {
+                se += __shfl_xor_sync(0xffffffffu, se, o);
+                so += __shfl_xor_sync(0xffffffffu, so, o);
+            }
+            if (live && (ci & (CPG - 1)) == 0) xmx[(ci / CPG) * BC + b] = make_float2(1024.0f * se + OFF_ODD * so, se + so);
         }
         named_bar_sync(1, kConsumerThreads);
     };
@@ -808,7 +851,7 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
         p.off_xs = off;     off += align_up((uint32_t)p.B * p.xstride, 128);
         p.off_xzero = off;  off += align_up((uint32_t)UK * 2, 128);
         p.off_xmx = off;    off += align_up((uint32_t)(xk / G + kUnitGroups) * BC * 8, 128);
-        p.off_xscale = off; off += align_up((uint32_t)p.B * 2 * 4, 128);
+        p.off_xscale = off; off += align_up((uint32_t)(p.B * 2 + kConsumerWarps * 2) * 4, 128);
         p.off_part = off;   off += align_up((uint32_t)p.nslot * MATS * kConsumerWarps * kTileRows * BC * 4, 128);
         // Ring depth and the buffers for scales / zero points are chosen together.  The scales of a (tile,
         // matrix) ride on its first stage and are overwritten meta_depth (tile, matrix) visits later, which is

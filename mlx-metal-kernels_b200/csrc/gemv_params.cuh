@@ -6,12 +6,12 @@
 namespace b200q {
 
 #ifndef B200Q_GEMV_WARPS
-#define B200Q_GEMV_WARPS 15
+#define B200Q_GEMV_WARPS 16
 #endif
 constexpr int kConsumerWarps = B200Q_GEMV_WARPS;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 #ifndef B200Q_GEMV_PRODUCERS
-#define B200Q_GEMV_PRODUCERS 4
+#define B200Q_GEMV_PRODUCERS 3
 #endif
 // Issuing a bulk copy costs the issuing warp about 40 ns per copy (measured), so the copies of a stage are
 // shared by several producer warps.

@@ -464,6 +464,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
     __shared__ float red[kMergeWarps][128];
     __shared__ float red_s[2][kMergeWarps];
     __shared__ int red_i[2][kMergeWarps];
+    __shared__ int cand_off[kMaxGrid * 8];        // candidates: (CTA of the main kernel, sub-warp) pairs of this sequence
+    __shared__ float cand_m[kMaxGrid * 8];
     const int D = p.D;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -500,21 +502,26 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
         const int c_first = s_lo / ppc, c_last = (s_hi - 1) / ppc;
         const int n_cand = (c_last - c_first + 1) * p.subs;
         // (cta c, sub) wrote a partial for b iff it walked at least one page of b:
-        // pages f = lo_c + sub + j*subs inside [max(lo_c, s_lo), min(hi_c, s_hi))
-        auto source = [&](int i) -> const float* {
+        // pages f = lo_c + sub + j*subs inside [max(lo_c, s_lo), min(hi_c, s_hi)).
+        // Pass 1 (one candidate per thread): resolve the candidate to the offset of its partial (or -1) and
+        // its running maximum, kept in shared memory so that pass 2 is free of index arithmetic.
+        float m_tot = -INFINITY;
+        for (int i = threadIdx.x; i < n_cand; i += kMergeWarps * 32) {
             const int c = c_first + i / p.subs;
             const int sub = i - (i / p.subs) * p.subs;
             const int lo_c = c * ppc, hi_c = min(total, lo_c + ppc);
             const int a = max(lo_c, s_lo), e = min(hi_c, s_hi);
             const int rel = a - lo_c - sub;
             const int first = lo_c + sub + (rel <= 0 ? 0 : (rel + p.subs - 1) / p.subs) * p.subs;
-            if (first >= e) return nullptr;
-            return p.partial + ((size_t)((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2);
-        };
-        float m_tot = -INFINITY;
-        for (int i = threadIdx.x; i < n_cand; i += kMergeWarps * 32) {
-            const float* src = source(i);
-            if (src != nullptr) m_tot = fmaxf(m_tot, src[D]);
+            int off = -1;
+            float m = -INFINITY;
+            if (first < e) {
+                off = (((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2);
+                m = p.partial[(size_t)off + D];
+            }
+            cand_off[i] = off;
+            cand_m[i] = m;
+            m_tot = fmaxf(m_tot, m);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m_tot = fmaxf(m_tot, __shfl_xor_sync(0xffffffffu, m_tot, o));
@@ -525,11 +532,12 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
 
 #pragma unroll 4
         for (int i = warp; i < n_cand; i += kMergeWarps) {
-            const float* src = source(i);
-            const bool ok = src != nullptr;
-            const float m = ok ? src[D] : -INFINITY;
+            const int off = cand_off[i];
+            const float m = cand_m[i];
+            const bool ok = off >= 0 && m != -INFINITY;
+            const float* src = p.partial + (ok ? off : 0);
+            const float w = ok ? exp2f((m - m_tot) * kLog2e) : 0.0f;
             const float l = ok ? src[D + 1] : 0.0f;
-            const float w = (m == -INFINITY) ? 0.0f : exp2f((m - m_tot) * kLog2e);
             l_part = fmaf(w, l, l_part);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
