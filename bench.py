@@ -325,8 +325,15 @@ def run_own(args):
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        # The captured graphs hold NCCL kernels; tearing the communicator down under them can block.  All
+        # ranks are done once they pass this barrier, so leave without the library teardown.
         import torch.distributed as dist
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_kernels_only():
