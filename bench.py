@@ -39,7 +39,7 @@ WORKLOAD = "c5_llama3_8b_shaped_q4_stack_32_layers_q8_paged_kv_ctx4096"
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes of one qgemv_kernel launch (ncu capture of the
-# 4096 x 4096 q4 case, profiles/qgemv_kernel_c1_q4_matvec_b1_4096x4096.md); the kernel reads every weight byte once.
+# 4096 x 4096 q4 case); the kernel reads every weight byte once.
 DRAM_TRAFFIC_RATIO = 1.006
 
 
@@ -119,26 +119,89 @@ def _time_graph(fn, iters, stream):
     return e0.elapsed_time(e1) / 1e3 / iters
 
 
-def kernel_microbenchmarks(device, peak):
+def _cpu_time(fn, budget_s=8.0):
+    """Mean seconds of ``fn`` on the host cores: one warm-up, then runs until ``budget_s`` is spent (at most 5)."""
+    fn()
+    t0 = time.perf_counter()
+    n = 0
+    while n < 5 and (n == 0 or time.perf_counter() - t0 < budget_s):
+        fn()
+        n += 1
+    return (time.perf_counter() - t0) / n, n
+
+
+def kernel_microbenchmarks(device, peak, all_configs=False, cpu=False):
     """BASELINE configs C1 (q4 matvec 4096x4096, batch 1) and C4 (q4 paged GQA decode attention, batch 16,
-    lengths U[1024, 8192]); achieved = algorithmic bytes / average launch time."""
+    lengths U[1024, 8192]); with ``all_configs`` also C2 (q8 matvec 4096->14336, batch 1 / 8) and C3 (q4 MLP
+    block, batch 1 / 8 / 32).  achieved = algorithmic bytes / average launch time, operands rotated through
+    copies totalling more than ROTATE_BYTES so that every launch reads cold data.  With ``cpu`` the same
+    call is timed through the oracle on the host cores."""
     q = importlib.import_module(f"{entry.PKG_ALIAS}.ops.quant_ops")
+    mlp = importlib.import_module(f"{entry.PKG_ALIAS}.ops.mlp_block_ops")
     pq = importlib.import_module(f"{entry.PKG_ALIAS}.ops.paged_quantized_kv_ops")
     synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
     stream = torch.cuda.Stream(device)
     out = {}
-    # C1
-    w, s, z = synth.quantized_weight(4096, 4096, 4, 64, seed=1001)
-    nbytes = w.numel() + (s.numel() + z.numel()) * 2 + 4096 * 2 + 4096 * 2
-    R = -(-ROTATE_BYTES // nbytes)
-    ws, ss, zs = [w.to(device).clone() for _ in range(R)], [s.to(device).clone() for _ in range(R)], [z.to(device).clone() for _ in range(R)]
-    x = synth.activations((1, 4096), 1501, device)
-    sec = _time_graph(lambda: [q.q4_matvec_decode(x, ws[i], ss[i], zs[i], group_size=64, backend="cuda") for i in range(R)],
-                      10, stream) / R
-    out["c1_q4_matvec_b1_4096x4096_g64"] = {"us": round(sec * 1e6, 3), "algorithmic_bytes": nbytes,
-                                             "gbs": round(nbytes / sec / 1e9, 1), "frac_of_peak": round(nbytes / sec / 1e9 / peak, 4),
-                                             "rotating_copies": R}
-    del ws, ss, zs
+    cores = torch.get_num_threads()
+
+    def record(name, sec, nbytes, R, extra=None, cpu_fn=None):
+        row = {"us": round(sec * 1e6, 3), "algorithmic_bytes": nbytes, "gbs": round(nbytes / sec / 1e9, 1),
+               "frac_of_peak": round(nbytes / sec / 1e9 / peak, 4), "rotating_copies": R}
+        if extra:
+            row.update(extra)
+        if cpu and cpu_fn is not None:
+            cs, n = _cpu_time(cpu_fn)
+            row["cpu_oracle_us"] = round(cs * 1e6, 1)
+            row["cpu_cores"] = cores
+            row["cpu_runs"] = n
+        out[name] = row
+
+    def matvec_case(name, bits, B, N, K, seed):
+        w, s, z = synth.quantized_weight(N, K, bits, 64, seed=seed)
+        nbytes = w.numel() + (s.numel() + z.numel()) * 2 + B * K * 2 + B * N * 2
+        R = -(-ROTATE_BYTES // nbytes)
+        ws, ss, zs = ([t.to(device).clone() for _ in range(R)] for t in (w, s, z))
+        x = synth.activations((B, K), seed + 500, device)
+        fn = q.q4_matvec_decode if bits == 4 else q.q8_matvec_decode
+        sec = _time_graph(lambda: [fn(x, ws[i], ss[i], zs[i], group_size=64, backend="cuda") for i in range(R)], 10, stream) / R
+        cpu_fn = None
+        if cpu:
+            from oracle import quant_ops as oq
+            ref = oq.reference_q4_matvec_decode if bits == 4 else oq.reference_q8_matvec_decode
+            xc = x.cpu()
+            cpu_fn = lambda: ref(xc, w, s, z, group_size=64)
+        record(name, sec, nbytes, R, cpu_fn=cpu_fn)
+
+    matvec_case("c1_q4_matvec_b1_4096x4096_g64", 4, 1, 4096, 4096, 1001)
+    if all_configs:
+        matvec_case("c2_q8_matvec_b1_4096to14336_g64", 8, 1, 14336, 4096, 1002)
+        matvec_case("c2_q8_matvec_b8_4096to14336_g64", 8, 8, 14336, 4096, 1002)
+        gw, gs, gz = synth.quantized_weight(14336, 4096, 4, 64, seed=1003)
+        uw, us, uz = synth.quantized_weight(14336, 4096, 4, 64, seed=1013)
+        dw, ds, dz = synth.quantized_weight(4096, 14336, 4, 64, seed=1023)
+        host = (gw, gs, gz, uw, us, uz, dw, ds, dz)
+        wbytes = sum(t.numel() * t.element_size() for t in host)
+        R = -(-ROTATE_BYTES // wbytes)
+        devs = [[t.to(device).clone() for t in host] for _ in range(R)]
+        nw = torch.ones(4096, dtype=torch.float16)
+        nwd = nw.to(device)
+        for B in (1, 8, 32):
+            x = synth.activations((B, 1, 4096), 1503 + B, device)
+            res = torch.zeros_like(x)
+            nbytes = wbytes + B * (4096 * 2 * 3 + 14336 * 2 * 2)   # x, residual, out; the SwiGLU rows written and re-read
+            call = lambda d: mlp.quantized_mlp_block(x, res, nwd, d[0], d[1], d[3], d[4], d[6], d[7], gate_zeros=d[2],
+                                                     up_zeros=d[5], down_zeros=d[8], bits=4, group_size=64,
+                                                     backend_preset="cuda")
+            sec = _time_graph(lambda: [call(d) for d in devs], 10, stream) / R
+            cpu_fn = None
+            if cpu:
+                from oracle import mlp_block_ops as om
+                xc, rc = x.cpu(), res.cpu()
+                cpu_fn = lambda: om.reference_quantized_mlp_block(xc, rc, nw, gw, gs, uw, us, dw, ds, gate_zeros=gz,
+                                                                  up_zeros=uz, down_zeros=dz, bits=4, group_size=64)
+            record(f"c3_q4_mlp_block_b{B}_4096_14336_g64", sec, nbytes, R, extra={"launches_per_block": 2}, cpu_fn=cpu_fn)
+        del devs
+        torch.cuda.empty_cache()
     # C4
     case = synth.paged_kv_case(16, 8, 128, 16, num_pages=9000, min_len=1024, max_len=8192, bits=4, group_size=32, seed=1004)
     total = int(case["lengths"].sum())
@@ -148,10 +211,13 @@ def kernel_microbenchmarks(device, peak):
               for _ in range(R)]
     qq = synth.activations((16, 1, 32, 128), 1005, device)
     sec = _time_graph(lambda: [pq.paged_quantized_kv_gqa_decode_attention(qq, c, backend="cuda") for c in caches], 10, stream) / R
-    out["c4_q4_paged_gqa_decode_b16_h32_kv8_d128_p16"] = {"us": round(sec * 1e6, 3), "algorithmic_bytes": nbytes,
-                                                          "gbs": round(nbytes / sec / 1e9, 1),
-                                                          "frac_of_peak": round(nbytes / sec / 1e9 / peak, 4),
-                                                          "sum_lengths": total, "rotating_copies": R}
+    cpu_fn = None
+    if cpu:
+        from oracle import paged_quantized_kv_ops as opq
+        ocache = opq.OraclePagedKV(**case)
+        qc = qq.cpu()
+        cpu_fn = lambda: opq.reference_paged_quantized_kv_gqa_decode_attention(qc, ocache)
+    record("c4_q4_paged_gqa_decode_b16_h32_kv8_d128_p16", sec, nbytes, R, extra={"sum_lengths": total}, cpu_fn=cpu_fn)
     del caches
     torch.cuda.empty_cache()
     return out
@@ -342,15 +408,15 @@ def run_own(args):
         os._exit(0)
 
 
-def run_kernels_only():
+def run_kernels_only(cpu=False):
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
     torch.cuda.set_device(0)
     entry.load_package()
     importlib.import_module(f"{entry.PKG_ALIAS}.ops._cabi").load()
     peak, peak_kind = measured_peaks()
-    print(json.dumps({"kernels": kernel_microbenchmarks(torch.device("cuda", 0), peak), "peak": peak,
-                      "peak_kind": peak_kind}), flush=True)
+    print(json.dumps({"kernels": kernel_microbenchmarks(torch.device("cuda", 0), peak, all_configs=True, cpu=cpu),
+                      "peak": peak, "peak_kind": peak_kind}), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -442,10 +508,12 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--kernels-only", action="store_true",
-                    help="run only the C1 matvec / C4 attention micro-benchmarks (the small case used for profiler captures)")
+                    help="run only the per-kernel micro-benchmarks of configs C1-C4 (the small cases used for profiler captures)")
+    ap.add_argument("--cpu-baselines", action="store_true",
+                    help="with --kernels-only: also time each config through the oracle on the host cores")
     args = ap.parse_args()
     if args.kernels_only:
-        run_kernels_only()
+        run_kernels_only(cpu=args.cpu_baselines)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -1,6 +1,6 @@
 """Generates tests/golden/hotpath_golden.npz from code the reference itself ships.
 
-Run in a container that has the reference checkout (default /root/reference) and
+Run in a container that has the reference checkout (first argument, or $MLX_METAL_KERNELS_REF) and
 oracle/_ref/libmetalref.so built (``make -C oracle``):
 
     python tests/golden/make_golden.py [/path/to/reference]
@@ -19,6 +19,7 @@ are self-contained.
 from __future__ import annotations
 
 import importlib.util
+import os
 import sys
 from pathlib import Path
 
@@ -38,7 +39,7 @@ def _load_reference_quantizer(ref_root: Path):
 
 
 def main():
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("MLX_METAL_KERNELS_REF", "/root/reference"))
     qw = _load_reference_quantizer(ref_root)
     rng = np.random.default_rng(20240607)
     out = {}
