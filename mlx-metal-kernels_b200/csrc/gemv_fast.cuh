@@ -41,7 +41,11 @@ namespace {
 #if defined(B200Q_DBG_TRACE)
 __device__ unsigned long long g_trace[4 * 1024];
 #define TRACE(kind, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 1024) g_trace[(kind) * 1024 + (idx)] = clock64(); } while (0)
+__device__ unsigned long long g_events[32];
+__device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define EVENT(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_events[(i)] = gtimer(); } while (0)
 #else
+#define EVENT(i) do { } while (0)
 #define TRACE(kind, idx) do { } while (0)
 #endif
 
@@ -173,6 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (warp == 0) EVENT(0);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
     uint64_t* tile_done = empty + kMaxStages;      // [kMaxSlots] all consumer warps have added their share
@@ -195,20 +200,19 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
     float* part = reinterpret_cast<float*>(smem + p.off_part);     // [nslot][MATS][16 warps][16 rows][BC]
     uint8_t* xzero = smem + p.off_xzero;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], kProducerWarps);
-            mbar_init(&empty[s], kConsumerWarps);
-        }
-        for (int s = 0; s < nslot; ++s) {
-            mbar_init(&tile_done[s], kConsumerWarps);
-            mbar_init(&slot_free[s], 1);
-        }
-        mbar_fence_init();
+    // barrier set-up spread over threads (one barrier each), fenced by the thread that also owns full[0]
+    if ((int)threadIdx.x < p.stages) {
+        mbar_init(&full[threadIdx.x], kProducerWarps);
+        mbar_init(&empty[threadIdx.x], kConsumerWarps);
+    } else if ((int)threadIdx.x >= 32 && (int)threadIdx.x < 32 + nslot) {
+        mbar_init(&tile_done[threadIdx.x - 32], kConsumerWarps);
+        mbar_init(&slot_free[threadIdx.x - 32], 1);
     }
+    if (threadIdx.x < 64) mbar_fence_init();
     for (int i = threadIdx.x; i < nslot * MATS * kConsumerWarps * kTileRows * BC; i += kThreads) part[i] = 0.0f;
     for (int i = threadIdx.x; i < UK * 2 / 4; i += kThreads) reinterpret_cast<uint32_t*>(xzero)[i] = 0u;
     __syncthreads();
+    if (warp == 0) EVENT(1);
     pdl_launch_dependents();
 
     uint8_t* ring = smem + p.off_ring;
@@ -292,6 +296,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             const int ps = tl % nslot;
             ok = mbar_wait_bounded(&tile_done[ps], (uint32_t)(tl / nslot) & 1u, &g_device_status, EV_GEMV_FULL_WAIT,
                                    ok ? kWaitLimit : 64u) && ok;
+            if (tl == 0) EVENT(8);
             const int row0 = r_lo + tl * tile_step;
             const int rows = min(kTileRows, r_hi - row0);
             float* slot_base = part + (size_t)ps * MATS * kConsumerWarps * kTileRows * BC;
@@ -335,6 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(&slot_free[ps]);
         }
+        EVENT(9);
         return;
     }
 
@@ -347,7 +353,33 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     uint8_t* xs = smem + p.off_xs;                                    // [B] rows of xstride bytes, fp16, operand order
     float2* xmx = reinterpret_cast<float2*>(smem + p.off_xmx);        // [groups of the chunk (+ padding)][BC] {M, X}
 
+    // per-lane constants.  As B operand this lane feeds column g, as accumulator owner columns 2t, 2t+1.
+    const int my_js = g / NB;                   // group slot of column g within a pass
+    const int my_b = g % NB;                    // batch row of column g (first column tile)
+    const uint32_t ring_u = smem_u32(ring);
+    const uint32_t a_lane = (uint32_t)g * p.row_stride + t * LB;
+    const uint32_t a_row8 = 8u * p.row_stride;
+    const uint32_t xz_u = smem_u32(xzero) + t * XB;
+    const uint32_t xmx_u = smem_u32(xmx);
+    const uint32_t mbuf_u = smem_u32(mbuf);
+    uint32_t x_lane[NT];
+    bool bvalid[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int b = nt * 8 + my_b;
+        bvalid[nt] = b < B;
+        x_lane[nt] = smem_u32(xs) + (uint32_t)min(b, B - 1) * p.xstride + t * XB;
+    }
+    // accumulator columns 2t, 2t+1: two groups (NB == 1) or two batch rows of one group
+    const int jc = NB == 1 ? 0 : (2 * t) / NB;  // group slot of this lane's accumulator columns
+    const int b0 = NB == 1 ? 0 : (2 * t) % NB;  // their first batch row
+    const uint32_t meta_lane = (uint32_t)(g * Gn + (NB == 1 ? 2 * t : jc * NP)) * 2;   // byte offset inside a scales array
+    const uint32_t meta_row8 = (uint32_t)8 * Gn * 2;
+    float* part_lane = part + ((size_t)cw * kTileRows) * BC;
+
+
     pdl_wait();   // activations belong to the previous kernel until here
+    if (warp == 0) EVENT(2);
 
     // per batch row: inv_rms (norm prologue) and the power of two that maps bf16 rows into fp16 range
     if (need_row_pass) {
@@ -435,6 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         }
     }
 
+    if (warp == 0) EVENT(3);
     // ---- stage activations of [xk0, xk0+xkn) as fp16 in tensor-core operand order, with their per-group sums ----
     auto stage_x = [&](int xk0, int xkn, bool write_side) {
         constexpr int CPG = G / 8;                 // 8-value blocks per group: the lanes that share a group
@@ -502,30 +535,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     int mb_idx = 0;                             // scale / zero-point buffer of the current (tile, matrix) visit
     int trace_c = 0; (void)trace_c;
 
-    // per-lane constants.  As B operand this lane feeds column g, as accumulator owner columns 2t, 2t+1.
-    const int my_js = g / NB;                   // group slot of column g within a pass
-    const int my_b = g % NB;                    // batch row of column g (first column tile)
-    const uint32_t ring_u = smem_u32(ring);
-    const uint32_t a_lane = (uint32_t)g * p.row_stride + t * LB;
-    const uint32_t a_row8 = 8u * p.row_stride;
-    const uint32_t xz_u = smem_u32(xzero) + t * XB;
-    const uint32_t xmx_u = smem_u32(xmx);
-    const uint32_t mbuf_u = smem_u32(mbuf);
-    uint32_t x_lane[NT];
-    bool bvalid[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int b = nt * 8 + my_b;
-        bvalid[nt] = b < B;
-        x_lane[nt] = smem_u32(xs) + (uint32_t)min(b, B - 1) * p.xstride + t * XB;
-    }
-    // accumulator columns 2t, 2t+1: two groups (NB == 1) or two batch rows of one group
-    const int jc = NB == 1 ? 0 : (2 * t) / NB;  // group slot of this lane's accumulator columns
-    const int b0 = NB == 1 ? 0 : (2 * t) % NB;  // their first batch row
-    const uint32_t meta_lane = (uint32_t)(g * Gn + (NB == 1 ? 2 * t : jc * NP)) * 2;   // byte offset inside a scales array
-    const uint32_t meta_row8 = (uint32_t)8 * Gn * 2;
-    float* part_lane = part + ((size_t)cw * kTileRows) * BC;
-
     // ---- one unit: 16 rows x 8 groups ----
     //   a_u    shared address of this lane's bytes of the unit's first group (row g)
     //   xoff   byte offset of the unit inside a staged activation row
@@ -587,26 +596,14 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                             const uint32_t a_hi = a_lo >> 8, b_hi = b_lo >> 8;
                             const uint32_t aL0 = lop3_and_or(a_lo, 0x000F000Fu, 0x64006400u), aH0 = lop3_and_or(a_lo, 0x00F000F0u, 0x54005400u);
                             const uint32_t bL0 = lop3_and_or(b_lo, 0x000F000Fu, 0x64006400u), bH0 = lop3_and_or(b_lo, 0x00F000F0u, 0x54005400u);
-#if defined(B200Q_DBG_HALF_LOP)
-                            const uint32_t aL1 = a_hi, aH1 = a_hi, bL1 = b_hi, bH1 = b_hi;
-#else
                             const uint32_t aL1 = lop3_and_or(a_hi, 0x000F000Fu, 0x64006400u), aH1 = lop3_and_or(a_hi, 0x00F000F0u, 0x54005400u);
                             const uint32_t bL1 = lop3_and_or(b_hi, 0x000F000Fu, 0x64006400u), bH1 = lop3_and_or(b_hi, 0x00F000F0u, 0x54005400u);
-#endif
 #pragma unroll
                             for (int nt = 0; nt < NT; ++nt) {
                                 const uint4 xq = xr[nt][wd];
                                 const uint4 xv = make_uint4(mine ? xq.x : 0u, mine ? xq.y : 0u, mine ? xq.z : 0u, mine ? xq.w : 0u);
-#if defined(B200Q_DBG_NO_MMA)
-                                acc[nt][0][0] += __uint_as_float(aL0 ^ bL0 ^ aH0 ^ bH0 ^ xv.x ^ xv.y);
-#else
                                 mma_m16n8k16(acc[nt][0], aL0, bL0, aH0, bH0, xv.x, xv.y);
-#endif
-#if defined(B200Q_DBG_HALF_MMA) || defined(B200Q_DBG_NO_MMA)
-                                acc[nt][1][0] += __uint_as_float(aL1 ^ bL1 ^ aH1 ^ bH1 ^ xv.z ^ xv.w);
-#else
                                 mma_m16n8k16(acc[nt][1], aL1, bL1, aH1, bH1, xv.z, xv.w);
-#endif
                             }
                         }
                     } else {
@@ -721,6 +718,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         const int xkn = min(p.xk, p.K - xk0);
         if (xc > 0) named_bar_sync(1, kConsumerThreads);     // everyone is done with the previous chunk
         stage_x(xk0, xkn, cta == 0);
+        if (warp == 0) EVENT(4);
 
         const int c_begin = xc * cpx;
         const int c_end = min(p.n_kc, c_begin + cpx);
@@ -749,7 +747,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                     const int slot = c_slot;
                     if (cw == 0) { TRACE(3, trace_c); }
                     ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT, ok ? kWaitLimit : 64u) && ok;
-                    if (cw == 0) { TRACE(1, trace_c); } ++trace_c;
+                    if (cw == 0) { TRACE(1, trace_c); if (trace_c == 0) EVENT(5); } ++trace_c;
                     if (++c_slot == p.stages) { c_slot = 0; c_phase ^= 1; }
                     const int groups = min(p.kc, p.K - k0) >> LOGG;          // groups in this stage
 #pragma unroll 1
@@ -758,14 +756,12 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         const uint32_t a_u = ring_u + (uint32_t)slot * p.stage_bytes + a_lane + (uint32_t)i * (kUnitGroups * GB);
                         const int kl = k0 + i * UK - xk0;
                         const int gabs = (k0 + i * UK) >> LOGG;
-#if defined(B200Q_DBG_NO_COMPUTE)
-                        if (p.K < 0)
-#endif
                         if (ng == kUnitGroups)
                             process_unit(std::true_type{}, a_u, (uint32_t)kl * 2, kl >> LOGG, gabs, ng, mb_u, m, row0, dst, has_z);
                         else
                             process_unit(std::false_type{}, a_u, (uint32_t)kl * 2, kl >> LOGG, gabs, ng, mb_u, m, row0, dst, has_z);
                     }
+                    if (cw == 0 && trace_c == 1) EVENT(6);
                     // index of this warp's first unit in the next stage: units are numbered through the stages
                     first_unit -= nu_stage;
                     while (first_unit < 0) first_unit += kConsumerWarps;
@@ -783,6 +779,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             if (++ps == nslot) { ps = 0; dst_tile = part_lane; if (tl >= nslot) sf_parity ^= 1; }
         }
     }
+    if (cw == 0) EVENT(7);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -821,11 +818,7 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
                  (p.z[0] == nullptr || aligned16(p.z[0])) &&
                  (MATS == 1 || (aligned16(p.s[1]) && (p.z[1] == nullptr || aligned16(p.z[1]))));
     // stage rows are padded so that the 8 rows a warp reads at once fall into different banks
-#if defined(B200Q_DBG_NO_PAD)
-    const uint32_t row_pad = 0;
-#else
     const uint32_t row_pad = LB == 32 ? 16 : 4 * LB;
-#endif
     p.row_stride = align_up((uint32_t)(kc * BITS / 8), 128) + row_pad;
     p.stage_bytes = align_up(kTileRows * p.row_stride, 128);
     const uint32_t x_pad = G == 32 ? 64 : 16;

@@ -12,6 +12,9 @@ int gemv_fast_q4(GemvParams& p, bool gate_up, cudaStream_t stream) { return disp
 }  // namespace b200q
 
 #if defined(B200Q_DBG_TRACE)
+extern "C" int b200q_dbg_read_events(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, b200q::g_events, sizeof(unsigned long long) * 32);
+}
 extern "C" int b200q_dbg_read_trace(unsigned long long* out) {
     return (int)cudaMemcpyFromSymbol(out, b200q::g_trace, sizeof(unsigned long long) * 4 * 1024);
 }
