@@ -155,6 +155,47 @@ def test_matvec_benchmark_shapes(cuda, config):
     assert cabi.device_status() == 0
 
 
+# (B, K, N, G, dtype) with fp16 scales / zero points, chosen to reach every branch of the tensor-core kernel's
+# planning: a partial last unit (K / G not a multiple of 8), fewer groups than one unit, activations staged in
+# several passes (B * K too large for shared memory), batches above 16 (split into chunks), every group size
+# and column layout (1, 2, 4, 8 batch columns per group, two column tiles).
+PLAN_CASES = [
+    (1, 11008, 300, 64, torch.float16),
+    (1, 192, 40, 64, torch.float16),
+    (2, 640, 64, 32, torch.float16),
+    (3, 1536, 100, 128, torch.float16),
+    (4, 2560, 130, 32, torch.float16),
+    (7, 4096, 96, 128, torch.float16),
+    (8, 14336, 272, 64, torch.float16),
+    (16, 2048, 80, 64, torch.float16),
+    (32, 4096, 144, 64, torch.float16),
+    (5, 1024, 48, 64, torch.bfloat16),
+]
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("case", PLAN_CASES)
+def test_matvec_kernel_plans(cuda, bits, case):
+    B, K, N, G, dtype = case
+    packed, scales, zeros = synth.quantized_weight(N, K, bits, G, seed=K + N)
+    x = synth.activations((B, K), K + 7).to(dtype)
+    ref = oq.reference_q4_matvec_decode if bits == 4 else oq.reference_q8_matvec_decode
+    fn = quant_ops.q4_matvec_decode if bits == 4 else quant_ops.q8_matvec_decode
+    want = ref(x, packed, scales, zeros, group_size=G)
+    dev = to_dev(cuda, x, packed, scales, zeros)
+    got = fn(*dev, group_size=G)
+    assert rel_l2(got, want) <= (TOL_F16 if dtype == torch.float16 else TOL_BF16_TC)
+    assert torch.equal(got, fn(*dev, group_size=G)), "results must be bitwise reproducible"
+    # the general kernel is the literal reference arithmetic: both kernels must agree with each other too
+    cabi.set_tuning("gemv.force_generic", 1)
+    try:
+        slow = fn(*dev, group_size=G)
+    finally:
+        cabi.set_tuning("gemv.force_generic", 0)
+    assert rel_l2(got, slow) <= (TOL_F16 if dtype == torch.float16 else TOL_BF16_TC)
+    assert cabi.device_status() == 0
+
+
 def test_matvec_linearity_at_full_size(cuda):
     """Size-independent property: y(x1 + x2) == y(x1) + y(x2) up to fp16 rounding of the outputs."""
     packed, scales, zeros = to_dev(cuda, *synth.quantized_weight(4096, 4096, 4, 64, seed=1001))
