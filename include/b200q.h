@@ -178,6 +178,18 @@ int b200q_rope_kv_append(const void* qkv, const float* cos_table, const float* s
                          int D, int page_size, int64_t num_pages, int max_blocks, int group_size, int table_len,
                          void* stream);
 
+/* Tensor-parallel glue (no counterpart in the reference, which is single-device): all-gather of an
+ * activation shard over NVLink peer memory.  `local` [rows, row_bytes_local] is this rank's shard;
+ * peer_full[r] / peer_flags[r] are HOST arrays of `world` device pointers: rank r's full buffer
+ * [rows, world * row_bytes_local] and its flag array (uint32[world], zero-initialised once) as mapped on
+ * THIS GPU (symmetric memory; entry `rank` is the local copy).  `epoch` is a device uint32 owned by this rank,
+ * zero-initialised once, one per full buffer; all ranks must call in the same order.  One small kernel
+ * stores the shard into column block `rank` of every rank's full buffer, publishes a sequence number and
+ * waits (bounded; b200q_device_status() reports B200Q_ERR_DEVICE_WAIT-class events) until all shards of
+ * this call have arrived.  row_bytes_local must be a multiple of 16.  Stream-ordered, capturable. */
+int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch,
+                         int rank, int world, int rows, int64_t row_bytes_local, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -47,6 +47,9 @@ int max_smem_optin() { return props().smem_optin; }
 // implemented in gemv.cu / paged_attn.cu
 int gemv_read_status(int reset, cudaStream_t stream);
 int attn_read_status(int reset, cudaStream_t stream);
+int peer_read_status(int reset, cudaStream_t stream);
+int peer_allgather_impl(const void* local, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch,
+                        int rank, int world, int rows, int64_t row_bytes_local, cudaStream_t stream);
 int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scales, const void* zeros,
                  const void* residual, void* y, int B, int64_t N, int64_t K, int group_size, int act_dtype,
                  int scale_dtype, const void* residual_in, const void* norm_weight, int norm_w_dtype, float eps,
@@ -243,9 +246,17 @@ const char* b200q_strerror(int code) {
 int b200q_device_status(int reset, void* stream) {
     const int a = gemv_read_status(reset, (cudaStream_t)stream);
     const int b = attn_read_status(reset, (cudaStream_t)stream);
+    const int c = peer_read_status(reset, (cudaStream_t)stream);
     if (a < 0) return a;
     if (b < 0) return b;
-    return a > b ? a : b;
+    if (c < 0) return c;
+    return a > b ? (a > c ? a : c) : (b > c ? b : c);
+}
+
+int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch,
+                         int rank, int world, int rows, int64_t row_bytes_local, void* stream) {
+    return peer_allgather_impl(local, peer_full, peer_flags, epoch, rank, world, rows, row_bytes_local,
+                               (cudaStream_t)stream);
 }
 
 int b200q_set_tuning(const char* key, int value) {

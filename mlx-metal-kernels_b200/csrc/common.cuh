@@ -38,6 +38,7 @@ enum DeviceEvent : int {
     EV_GEMV_EMPTY_WAIT = 2,   // producer gave up waiting for a free stage
     EV_ATTN_FULL_WAIT = 3,
     EV_ATTN_EMPTY_WAIT = 4,
+    EV_PEER_WAIT = 5,         // a rank gave up waiting for a peer's shard in the peer all-gather
 };
 
 // ---------------------------------------------------------------------------------------------

@@ -9,8 +9,9 @@ advanced inside the graph).
 
 Tensor parallelism over ``tp_size`` GPUs of one node: every matrix is sharded by OUTPUT rows (QKV by
 heads, so the KV cache is sharded by kv head) and the activations are re-assembled with an NCCL
-all-gather after attention, O, SwiGLU and down.  Row sharding leaves every output element's
-arithmetic untouched, so the sharded stack is bitwise identical to the single-GPU stack.
+all-gather after attention, O, SwiGLU and down (small kernels storing into NVLink peer memory, or NCCL
+when symmetric memory is unavailable).  Row sharding keeps every output element's products; only the order
+in which partial sums are combined changes, so the sharded stack equals the single-GPU stack to rounding.
 """
 from __future__ import annotations
 
@@ -137,7 +138,7 @@ class DecodeStack:
     """Runs decode steps of ``cfg.n_layers`` layers on one GPU (or one tensor-parallel rank)."""
 
     def __init__(self, cfg: StackConfig, layers, final_norm, embedding, batch: int, max_context: int, device,
-                 tp_rank: int = 0, tp_size: int = 1, process_group=None):
+                 tp_rank: int = 0, tp_size: int = 1, process_group=None, use_peer_gather: bool = True):
         self.cfg, self.B, self.device = cfg, batch, device
         self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
         self.lib = _cabi.load()
@@ -164,6 +165,7 @@ class DecodeStack:
         self.attn = torch.zeros((batch, self.hq * D), **f16)
         self.act = torch.zeros((batch, cfg.intermediate // tp_size), **f16)
         self.out = torch.zeros((batch, cfg.hidden), **f16)
+        self.peer_gather = False
         if tp_size > 1:
             self.o_loc = torch.zeros((batch, cfg.hidden // tp_size), **f16)
             self.gather_attn = torch.zeros((tp_size, batch, self.hq * D), **f16)
@@ -171,6 +173,8 @@ class DecodeStack:
             self.gather_act = torch.zeros((tp_size, batch, cfg.intermediate // tp_size), **f16)
             self.attn_full = torch.zeros((batch, cfg.n_heads * D), **f16)
             self.act_full = torch.zeros((batch, cfg.intermediate), **f16)
+            if use_peer_gather:
+                self._setup_peer_gather()
         ws_bytes = self.lib.b200q_paged_gqa_workspace_bytes(batch, self.hq, self.hkv, D)
         self.workspace = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
         self.token_ids = torch.zeros(batch, dtype=torch.int64, device=device)
@@ -186,6 +190,59 @@ class DecodeStack:
         self.lengths.fill_(context_len + 1)
 
     # -- one decode step -----------------------------------------------------------------------
+    def _setup_peer_gather(self):
+        """Maps one symmetric buffer (full attention rows, full hidden rows, full MLP rows, flag words) on all
+        ranks so that the all-gathers of a step are single small kernels storing straight into peer memory.
+        Falls back to NCCL all-gathers (``peer_gather = False``) when symmetric memory cannot be set up."""
+        import ctypes
+        import torch.distributed as dist
+        cfg, B, W = self.cfg, self.B, self.tp_size
+        widths = (cfg.n_heads * cfg.head_dim, cfg.hidden, cfg.intermediate)
+        if any((w // W) * 2 % 16 for w in widths):
+            return
+        try:
+            import torch.distributed._symmetric_memory as symm
+            group = self.pg if self.pg is not None else dist.group.WORLD
+            sizes = [B * w * 2 for w in widths]
+            offsets, off = [], 0
+            for n in sizes:
+                offsets.append(off)
+                off += (n + 255) // 256 * 256
+            flag_off = off
+            off += 3 * 256                                    # one 256-byte line of flag words per buffer
+            buf = symm.empty(off, dtype=torch.uint8, device=self.device)
+            buf.zero_()
+            handle = symm.rendezvous(buf, group)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+        except Exception as exc:                              # no fabric / unsupported build: keep NCCL
+            self.peer_gather_error = repr(exc)
+            return
+        self._symm_buf, self._symm_handle = buf, handle
+        self.peer_full, self.peer_ptrs, self.peer_flag_ptrs = [], [], []
+        for i, (w, o) in enumerate(zip(widths, offsets)):
+            self.peer_full.append(buf[o:o + B * w * 2].view(torch.float16).view(B, w))
+            self.peer_ptrs.append((ctypes.c_void_p * W)(*[p + o for p in ptrs]))
+            self.peer_flag_ptrs.append((ctypes.c_void_p * W)(*[p + flag_off + 256 * i for p in ptrs]))
+        self.peer_epochs = torch.zeros(3, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.pg)                            # every rank's buffer is zeroed before anyone stores
+        self.peer_gather = True
+
+    def _gather(self, which: int, local):
+        """All-gather of ``local`` [B, n_loc] into [B, tp * n_loc] (rank-major columns); ``which`` selects the
+        full buffer: 0 attention rows, 1 hidden rows, 2 MLP rows."""
+        if self.peer_gather:
+            st = torch.cuda.current_stream().cuda_stream
+            _cabi.check(self.lib.b200q_peer_allgather(local.data_ptr(), self.peer_ptrs[which], self.peer_flag_ptrs[which],
+                                                      self.peer_epochs[which:].data_ptr(), self.tp_rank, self.tp_size,
+                                                      self.B, local.shape[1] * 2, st), "peer_allgather")
+            return self.peer_full[which]
+        if which == 0:
+            return self._all_gather_rows(local, self.gather_attn, self.attn_full)
+        if which == 2:
+            return self._all_gather_rows(local, self.gather_act, self.act_full)
+        return self._all_gather_rows(local, self.gather_h)
+
     def _all_gather_rows(self, local, gathered, full=None):
         """[B, n_loc] on every rank -> [B, tp * n_loc] in rank-major column order."""
         import torch.distributed as dist
@@ -203,11 +260,19 @@ class DecodeStack:
         F16, ck = _cabi.F16, _cabi.check
         n = 0
         torch.index_select(self.embedding, 0, self.token_ids, out=self.h)
+        pending = None      # tensor-parallel path: gathered down-projection rows whose residual add (h2 + rows -> h)
+                            # is folded into the next kernel's prologue instead of being a launch of its own
         for w, cache in zip(self.layers, self.caches):
             qw, qs, qz = w["qkv"]
-            ck(lib.b200q_norm_qmatvec(bits, self.h.data_ptr(), None, w["input_norm"].data_ptr(), F16, cfg.eps, None, None,
-                                      qw.data_ptr(), qs.data_ptr(), qz.data_ptr(), None, self.qkv.data_ptr(), B,
-                                      qw.shape[0], cfg.hidden, G, F16, F16, st), "norm_qmatvec")
+            if pending is None:
+                ck(lib.b200q_norm_qmatvec(bits, self.h.data_ptr(), None, w["input_norm"].data_ptr(), F16, cfg.eps, None,
+                                          None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(), None, self.qkv.data_ptr(), B,
+                                          qw.shape[0], cfg.hidden, G, F16, F16, st), "norm_qmatvec")
+            else:
+                ck(lib.b200q_norm_qmatvec(bits, pending.data_ptr(), self.h2.data_ptr(), w["input_norm"].data_ptr(), F16,
+                                          cfg.eps, self.h.data_ptr(), None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(),
+                                          None, self.qkv.data_ptr(), B, qw.shape[0], cfg.hidden, G, F16, F16, st),
+                   "norm_qmatvec")
             ck(lib.b200q_rope_kv_append(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
                                         self.positions.data_ptr(), self.block_table.data_ptr(), self.q_rot.data_ptr(),
                                         cache.k_codes.data_ptr(), cache.v_codes.data_ptr(), cache.k_scales.data_ptr(),
@@ -237,23 +302,28 @@ class DecodeStack:
                    "down_proj")
                 n += 7
             else:
-                attn_full = self._all_gather_rows(self.attn, self.gather_attn, self.attn_full)
+                attn_full = self._gather(0, self.attn)
                 ck(lib.b200q_qmatvec(bits, attn_full.data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
                                      self.o_loc.data_ptr(), B, ow.shape[0], cfg.n_heads * D, G, F16, F16, st), "o_proj")
-                o_full = self._all_gather_rows(self.o_loc, self.gather_h)
-                torch.add(self.h, o_full, out=self.h2)                       # cast(h + o), the layer's residual add
-                ck(lib.b200q_gate_up_swiglu(bits, self.h2.data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
+                o_full = self._gather(1, self.o_loc)
+                # h2 = cast(h + o) (the layer's residual add) is formed in the prologue of the gate/up launch
+                ck(lib.b200q_gate_up_swiglu(bits, o_full.data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
                                             us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, self.act.data_ptr(),
-                                            None, w["post_norm"].data_ptr(), F16, cfg.eps, None, None, B, gw.shape[0],
-                                            cfg.hidden, G, F16, F16, st), "gate_up")
-                act_full = self._all_gather_rows(self.act, self.gather_act, self.act_full)
+                                            self.h.data_ptr(), w["post_norm"].data_ptr(), F16, cfg.eps, self.h2.data_ptr(),
+                                            None, B, gw.shape[0], cfg.hidden, G, F16, F16, st), "gate_up")
+                act_full = self._gather(2, self.act)
                 ck(lib.b200q_qmatvec(bits, act_full.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(), None,
                                      self.o_loc.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
-                d_full = self._all_gather_rows(self.o_loc, self.gather_h)
-                torch.add(self.h2, d_full, out=self.h)
-                n += 7
-        ck(lib.b200q_rmsnorm_residual(self.h.data_ptr(), None, self.final_norm.data_ptr(), self.out.data_ptr(), None, B,
-                                      cfg.hidden, cfg.eps, F16, _cabi.dtype_code(self.final_norm.dtype), st), "final_norm")
+                pending = self._gather(1, self.o_loc)      # h = cast(h2 + down) happens in the next prologue
+                n += 7 + (4 if self.peer_gather else 0)
+        if pending is None:
+            ck(lib.b200q_rmsnorm_residual(self.h.data_ptr(), None, self.final_norm.data_ptr(), self.out.data_ptr(), None,
+                                          B, cfg.hidden, cfg.eps, F16, _cabi.dtype_code(self.final_norm.dtype), st),
+               "final_norm")
+        else:
+            ck(lib.b200q_rmsnorm_residual(pending.data_ptr(), self.h2.data_ptr(), self.final_norm.data_ptr(),
+                                          self.out.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.eps, F16,
+                                          _cabi.dtype_code(self.final_norm.dtype), st), "final_norm")
         self.positions.add_(1)
         self.lengths.add_(1)
         self.launches_per_step = n + 1
