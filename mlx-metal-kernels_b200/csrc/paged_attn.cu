@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
 }
 
 // Merges the partials of every (sequence, query head): one warp each, lanes over d.
-constexpr int kMergeWarps = 8;
+constexpr int kMergeWarps = 32;     // one pass over up to 128 candidates with four loads in flight per warp
 
 // One CTA per (sequence, query head).  The partials of a sequence may sit in every CTA slot of the
 // main kernel (a single long sequence is cut over the whole grid), so the slots are spread over the
