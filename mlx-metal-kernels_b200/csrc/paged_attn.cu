@@ -459,11 +459,13 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
 }
 
 // Merges the partials of every (sequence, query head): one warp each, lanes over d.
-constexpr int kMergeWarps = 32;     // one pass over up to 128 candidates with four loads in flight per warp
 
 // One CTA per (sequence, query head).  The partials of a sequence may sit in every CTA slot of the
 // main kernel (a single long sequence is cut over the whole grid), so the slots are spread over the
 // CTA's warps and their loads are independent of one another; lanes cover the head dimension.
+// kMergeWarps: 32 for short batches (few CTAs, up to ~300 candidates each: four loads in flight per warp cover
+// them in one or two rounds), 8 for long batches (many CTAs with a dozen candidates each).
+template <int kMergeWarps>
 __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
     __shared__ float red[kMergeWarps][128];
     __shared__ float red_s[2][kMergeWarps];
@@ -745,12 +747,14 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(B * Hq);
-        cfg.blockDim = dim3(kMergeWarps * 32);
+        const bool wide = B * Hq < 2 * sm_count();
+        cfg.blockDim = dim3((wide ? 32 : 8) * 32);
         cfg.dynamicSmemBytes = 0;
         cfg.stream = stream;
         cfg.attrs = attr;
         cfg.numAttrs = tuning_get("no_pdl") ? 0 : 1;
-        if (cudaLaunchKernelEx(&cfg, paged_attn_merge_kernel, p) != cudaSuccess) return B200Q_ERR_LAUNCH;
+        if (cudaLaunchKernelEx(&cfg, wide ? paged_attn_merge_kernel<32> : paged_attn_merge_kernel<8>, p) != cudaSuccess)
+            return B200Q_ERR_LAUNCH;
     }
     return finish_launch();
 }
