@@ -562,14 +562,35 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         auto present = [&](int e) { return FULL || ((e % GS) * NP + e / GS) < ng; };
         Operands ops[PIPE ? 2 : 1];
         if (PIPE) fetch(0, ops[0]);       // group 0 always exists
+        // with 4 or 8 batch columns per group a lane meets NB consecutive groups of its two rows, one per pass:
+        // their scales / zero points are fetched once per unit as vectors
+        uint32_t mvec_s[2][NB >= 4 ? NB / 2 : 1], mvec_z[2][NB >= 4 ? NB / 2 : 1];
+        if constexpr (NB >= 4) {
+            if (p.meta_vec) {
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const uint32_t ma = mb_u + meta_lane + rr * meta_row8 + (uint32_t)gabs * 2;
+                    lds_words<NB / 2>(ma, mvec_s[rr]);
+                    if (has_z) {
+                        lds_words<NB / 2>(ma + mbuf_half, mvec_z[rr]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < NB / 2; ++i) mvec_z[rr][i] = 0u;
+                    }
+                }
+            }
+        }
 
 #pragma unroll
         for (int pass = 0; pass < NP; ++pass) {
-            float acc[NT][2][4];
+            // two accumulators shorten the dependent MMA chain of a pass; with one group per pass (NB == 8) the chain
+            // is four instructions anyway and one accumulator saves its zeroing and the final add
+            constexpr int NACC = NB == 8 ? 1 : 2;
+            float acc[NT][NACC][4];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int a = 0; a < 2; ++a)
+                for (int a = 0; a < NACC; ++a)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[nt][a][i] = 0.0f;
             // This lane's column belongs to one group of the pass (slot my_js): only that group's activations
@@ -603,7 +624,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                                 const uint4 xq = xr[nt][wd];
                                 const uint4 xv = make_uint4(mine ? xq.x : 0u, mine ? xq.y : 0u, mine ? xq.z : 0u, mine ? xq.w : 0u);
                                 mma_m16n8k16(acc[nt][0], aL0, bL0, aH0, bH0, xv.x, xv.y);
-                                mma_m16n8k16(acc[nt][1], aL1, bL1, aH1, bH1, xv.z, xv.w);
+                                mma_m16n8k16(acc[nt][NACC - 1], aL1, bL1, aH1, bH1, xv.z, xv.w);
                             }
                         }
                     } else {
@@ -618,7 +639,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                                 const uint4 xq = xr[nt][wp];
                                 const uint4 xv = make_uint4(mine ? xq.x : 0u, mine ? xq.y : 0u, mine ? xq.z : 0u, mine ? xq.w : 0u);
                                 mma_m16n8k16(acc[nt][0], a0, c0, a1, c1, xv.x, xv.y);
-                                mma_m16n8k16(acc[nt][1], a2, c2, a3, c3, xv.z, xv.w);
+                                mma_m16n8k16(acc[nt][NACC - 1], a2, c2, a3, c3, xv.z, xv.w);
                             }
                         }
                     }
@@ -640,6 +661,10 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                             } else {
                                 z0[rr] = z1[rr] = 0.0f;
                             }
+                        } else if constexpr (NB >= 4) {
+                            const uint32_t sw = mvec_s[rr][pass >> 1], zw = mvec_z[rr][pass >> 1];
+                            s0[rr] = s1[rr] = half_bits_to_float((pass & 1) ? sw >> 16 : sw & 0xFFFFu);
+                            z0[rr] = z1[rr] = half_bits_to_float((pass & 1) ? zw >> 16 : zw & 0xFFFFu);
                         } else {
                             s0[rr] = s1[rr] = half_bits_to_float(lds_u16(ma + pass * 2));
                             z0[rr] = z1[rr] = has_z ? half_bits_to_float(lds_u16(ma + mbuf_half + pass * 2)) : 0.0f;
@@ -668,8 +693,8 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                     const float4 mx = lds_f128(xmx_u + (uint32_t)e * 8);   // {M, X} of column 2t, {M, X} of 2t+1
 #pragma unroll
                     for (int rr = 0; rr < 2; ++rr) {
-                        float v0 = acc[nt][0][2 * rr] + acc[nt][1][2 * rr];
-                        float v1 = acc[nt][0][2 * rr + 1] + acc[nt][1][2 * rr + 1];
+                        float v0 = acc[nt][0][2 * rr], v1 = acc[nt][0][2 * rr + 1];
+                        if constexpr (NACC == 2) { v0 += acc[nt][1][2 * rr]; v1 += acc[nt][1][2 * rr + 1]; }
                         v0 = fmaf(-z0[rr], mx.y, v0 - mx.x);
                         v1 = fmaf(-z1[rr], mx.w, v1 - mx.z);
                         y[nt][2 * rr] = fmaf(s0[rr], v0, y[nt][2 * rr]);
