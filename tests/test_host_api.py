@@ -274,3 +274,24 @@ def test_synth_generators_are_seeded_and_affine_formula_holds():
     used = case["block_table"][case["block_table"] >= 0]
     assert used.numel() == used.unique().numel()          # pages are not shared between sequences
     assert int(((case["lengths"] + 15) // 16).sum()) == used.numel()
+
+
+def test_c_abi_rejects_bad_arguments_before_touching_a_device():
+    """Argument checks of the C entry points run on the host: null pointers and impossible sizes come back as
+    error codes (never a crash), also on a machine without a GPU."""
+    import ctypes
+    lib = cabi.load()
+    bad = -1            # B200Q_ERR_BAD_ARG
+    unsupported = -2    # B200Q_ERR_UNSUPPORTED
+    assert lib.b200q_qmatvec(4, None, None, None, None, None, None, 1, 16, 64, 32, 0, 0, None) == bad
+    assert lib.b200q_qmatvec(5, 1, 1, 1, None, None, 1, 1, 16, 64, 32, 0, 0, None) == bad          # bits
+    assert lib.b200q_dequant(4, None, None, None, None, 4, 64, 32, 0, 0, None) == bad
+    assert lib.b200q_paged_gqa_decode_static(4, None, None, None, None, None, None, None, None, 0, 32, 8, 128, 16, 1, 1, 32,
+                                             1.0, 0, 0, None) == bad
+    # tensor-parallel exchange: world size, rank and row size are validated
+    ptrs = (ctypes.c_void_p * 2)(16, 32)
+    assert lib.b200q_peer_allgather(None, ptrs, ptrs, 16, 0, 2, 1, 32, None) == bad
+    assert lib.b200q_peer_allgather(16, ptrs, ptrs, 16, 2, 2, 1, 32, None) == bad                 # rank >= world
+    assert lib.b200q_peer_allgather(16, ptrs, ptrs, 16, 0, 9, 1, 32, None) == bad                 # world > 8
+    assert lib.b200q_peer_allgather(16, ptrs, ptrs, 16, 0, 2, 1, 24, None) == unsupported         # rows of 24 bytes
+    assert b"scratch" in lib.b200q_strerror(-6)
