@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int n_tiles = interleave ? (total_tiles - cta + (int)gridDim.x - 1) / (int)gridDim.x : (r_cnt + kTileRows - 1) / kTileRows;
     const int n_xc = p.n_xc;
     const int cpx = p.xk / p.kc;                   // stages per (matrix, tile, activation chunk)
+    const int units_per_visit = cpx * p.nu;        // units (incl. absent ones of a short last chunk) per such visit
     const int nslot = p.nslot;
     const int B = p.B;
     const int Gn = p.Gn;
@@ -307,6 +308,9 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 #pragma unroll
                 for (int m = 0; m < MATS; ++m) {
                     float* src = slot_base + ((size_t)m * kConsumerWarps * kTileRows + r) * BC + b;
+                    // Slot j holds k-spans j, j + 16, ... of the (tile, matrix) visit (the consumers index their slots by
+                    // span, not by warp): summing the slots in order adds a row's spans in k order, whatever CTA or
+                    // GPU holds the row.
                     float s = 0.0f;
 #pragma unroll
                     for (int w = 0; w < kConsumerWarps; ++w) {
@@ -375,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     const int b0 = NB == 1 ? 0 : (2 * t) % NB;  // their first batch row
     const uint32_t meta_lane = (uint32_t)(g * Gn + (NB == 1 ? 2 * t : jc * NP)) * 2;   // byte offset inside a scales array
     const uint32_t meta_row8 = (uint32_t)8 * Gn * 2;
-    float* part_lane = part + ((size_t)cw * kTileRows) * BC;
+    float* part_lane = part;
 
 
     pdl_wait();   // activations belong to the previous kernel until here
@@ -531,7 +535,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     bool ok = true;
     int c_slot = 0;
     uint32_t c_phase = 0;
-    int first_unit = cw;                        // index of this warp's first unit in the current stage (units are dealt round-robin)
     int mb_idx = 0;                             // scale / zero-point buffer of the current (tile, matrix) visit
     int trace_c = 0; (void)trace_c;
 
@@ -749,6 +752,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         const int c_end = min(p.n_kc, c_begin + cpx);
         // All counters below are advanced incrementally: a consumer warp touches every stage, most of them
         // without finding a unit of its own, so the per-stage bookkeeping has to stay a handful of instructions.
+        int visit_rot = 0;                         // ((tile * MATS + matrix) * units_per_visit) mod consumer warps
         int ps = 0;                                // result slot of the tile and the parity of its slot_free barrier
         uint32_t sf_parity = 0;                    // (tile / nslot - 1) & 1, meaningful from tile nslot on
         int row0 = r_lo;
@@ -763,9 +767,15 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                                        ok ? kWaitLimit : 64u) && ok;
 #pragma unroll 1
             for (int m = 0; m < MATS; ++m) {
+                // units of a visit are dealt to the warps starting at warp visit_rot
+                int first_unit = cw - visit_rot;
+                if (first_unit < 0) first_unit += kConsumerWarps;
+                visit_rot += units_per_visit % kConsumerWarps;
+                if (visit_rot >= kConsumerWarps) visit_rot -= kConsumerWarps;
                 const uint32_t mb_u = mbuf_u + (uint32_t)mb_idx * 2 * mbuf_half;
                 const bool has_z = ((MATS == 2 && m != 0) ? p.z[1] : p.z[0]) != nullptr;
-                float* dst = dst_tile + (MATS == 2 && m != 0 ? part_mat_stride : 0u);
+                // this warp's slot of the visit = the position of its first k-span
+                float* dst = dst_tile + (MATS == 2 && m != 0 ? part_mat_stride : 0u) + (uint32_t)first_unit * (kTileRows * BC);
                 int k0 = c_begin * p.kc;
 #pragma unroll 1
                 for (int c = c_begin; c < c_end; ++c, k0 += p.kc) {

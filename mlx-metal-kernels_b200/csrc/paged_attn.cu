@@ -51,7 +51,7 @@ struct AttnParams {
     const __half* v_scales;
     const int32_t* block_table; // [B, max_blocks]
     const int32_t* lengths;     // [B]
-    float* partial;             // [(grid + B) * subs][Hq][D + 2]  (acc[D], max, sum)
+    float* partial;             // [grid + B][Hq][D + 2]  (acc[D], max, sum); slot = range + sequence
     void* out;                  // [B, Hq, D]
     int B, Hq, Hkv, D, P, max_blocks, G, Gd, group;
     int64_t num_pages;
@@ -59,7 +59,7 @@ struct AttnParams {
     int q_dtype;
     int bits;
     int stages;                 // pages in flight per warp
-    int subs;                   // warps per kv head inside a CTA (8 / Hkv)
+    int subs;                   // ranges per CTA (8 / Hkv)
     int row_bytes;              // bytes of one token row of codes, all kv heads
     int scale_row_halves;       // halves of one token row of scales, all kv heads
     uint32_t off_prefix, off_ring, slot_bytes;
@@ -141,14 +141,19 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
     pdl_launch_dependents();
     pdl_wait();   // lengths / block table / q / the cache itself may be produced by the previous kernel
 
+    // The flattened page list is cut into p.grid equal ranges.  A CTA has 8 warps = 8 (range, kv head) pairs:
+    // with 8 kv heads one range, with fewer heads several consecutive ranges (subs of them).  The cut depends
+    // only on the batch and the device, not on the number of heads, so a head's partial results (and the
+    // merged output) are the same bits whether all heads or a tensor-parallel shard of them are computed.
     const int total = build_prefix(p, prefix);
-    const int ppc = (total + p.grid - 1) / p.grid;               // pages per CTA
-    const int lo = min(total, (int)blockIdx.x * ppc);
-    const int hi = min(total, lo + ppc);
+    const int ppc = (total + p.grid - 1) / p.grid;               // pages per range
     const int subs = p.subs;
     const int h = warp % p.Hkv;                                  // kv head of this warp
     const int sub = warp / p.Hkv;
-    if (lo >= hi || sub >= subs) return;
+    const int vc = (int)blockIdx.x * subs + sub;                 // range of this warp
+    const int lo = min(total, vc * ppc);
+    const int hi = min(total, lo + ppc);
+    if (lo >= hi || sub >= subs || vc >= p.grid) return;
 
     const int g = lane >> 2;
     const int t = lane & 3;
@@ -157,8 +162,7 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
     constexpr int NS = ring_depth(BITS, TWO);                     // pages in flight per warp
     constexpr int SLOT = K_BYTES + V_BYTES + 256;                // bytes of one ring slot
     uint8_t* my_ring = smem + p.off_ring + (size_t)warp * NS * SLOT;
-    // number of pages this warp walks: f = lo + sub + j * subs < hi
-    const int n_my = (hi - lo - sub + subs - 1) / subs;
+    const int n_my = hi - lo;                                     // pages this warp walks: f = lo + j
 
     uint32_t qa[8][2];          // Q as A operand: [mma][a0a1 (row g), a4a5 (row g)]; rows 8..15 are zero
     float o[8][4];              // O^T tiles: rows d, cols heads
@@ -173,7 +177,7 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
         const int j = base + lane;
         Desc d = {-1, 0, 0};
         if (j < n_my) {
-            const int f = lo + sub + j * subs;
+            const int f = lo + j;
             const int b = find_sequence(prefix, p.B, f);
             const int pg = f - prefix[b];
             int page = p.block_table[(int64_t)b * p.max_blocks + pg];
@@ -244,7 +248,7 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
     };
 
     auto flush = [&](int b) {
-        float* dst = p.partial + ((size_t)((blockIdx.x + b) * subs + sub) * p.Hq) * (D + 2);
+        float* dst = p.partial + ((size_t)(vc + b) * p.Hq) * (D + 2);
         float l0 = l_run;
         l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
         l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -470,8 +474,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
     __shared__ float red[kMergeWarps][128];
     __shared__ float red_s[2][kMergeWarps];
     __shared__ int red_i[2][kMergeWarps];
-    __shared__ int cand_off[kMaxGrid * 8];        // candidates: (CTA of the main kernel, sub-warp) pairs of this sequence
-    __shared__ float cand_m[kMaxGrid * 8];
+    __shared__ int cand_off[kMaxGrid];            // candidates: page ranges of the main kernel that touch this sequence
+    __shared__ float cand_m[kMaxGrid];
     const int D = p.D;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -506,25 +510,14 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
     float l_part = 0.0f;
     if (s_hi > s_lo) {
         const int c_first = s_lo / ppc, c_last = (s_hi - 1) / ppc;
-        const int n_cand = (c_last - c_first + 1) * p.subs;
-        // (cta c, sub) wrote a partial for b iff it walked at least one page of b:
-        // pages f = lo_c + sub + j*subs inside [max(lo_c, s_lo), min(hi_c, s_hi)).
-        // Pass 1 (one candidate per thread): resolve the candidate to the offset of its partial (or -1) and
-        // its running maximum, kept in shared memory so that pass 2 is free of index arithmetic.
+        const int n_cand = c_last - c_first + 1;
+        // Every range c_first..c_last holds at least one page of b, i.e. wrote a partial into slot c + b.
+        // Pass 1 (one candidate per thread): the offset of the partial and its running maximum, kept in shared
+        // memory so that pass 2 is free of index arithmetic.
         float m_tot = -INFINITY;
         for (int i = threadIdx.x; i < n_cand; i += kMergeWarps * 32) {
-            const int c = c_first + i / p.subs;
-            const int sub = i - (i / p.subs) * p.subs;
-            const int lo_c = c * ppc, hi_c = min(total, lo_c + ppc);
-            const int a = max(lo_c, s_lo), e = min(hi_c, s_hi);
-            const int rel = a - lo_c - sub;
-            const int first = lo_c + sub + (rel <= 0 ? 0 : (rel + p.subs - 1) / p.subs) * p.subs;
-            int off = -1;
-            float m = -INFINITY;
-            if (first < e) {
-                off = (((c + b) * p.subs + sub) * p.Hq + hq) * (D + 2);
-                m = p.partial[(size_t)off + D];
-            }
+            const int off = ((c_first + i + b) * p.Hq + hq) * (D + 2);
+            const float m = p.partial[(size_t)off + D];
             cand_off[i] = off;
             cand_m[i] = m;
             m_tot = fmaxf(m_tot, m);
@@ -652,7 +645,8 @@ inline int subs_for(int Hkv) { return (Hkv <= kAttnWarps && kAttnWarps % Hkv == 
 
 size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int Hkv, int D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return 0;
-    return (size_t)(kMaxGrid + B) * subs_for(Hkv) * Hq * (D + 2) * sizeof(float);
+    (void)Hkv;
+    return (size_t)(kMaxGrid + B) * Hq * (D + 2) * sizeof(float);
 }
 
 int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes, const void* k_scales,
@@ -702,7 +696,8 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     // batches otherwise pay for partial results and their merge more than for the KV bytes.
     const int64_t pages_cap = (int64_t)B * max_blocks;
     p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(kMaxGrid, sm_count() * ctas_per_sm), (pages_cap + 1) / 2));
-    const bool two = p.grid > sm_count();
+    const int launch_grid = (p.grid + p.subs - 1) / p.subs;   // CTAs: each covers `subs` ranges
+    const bool two = launch_grid > sm_count();
     const int stages = ring_depth(bits, two);
 
     uint32_t off = 0;
@@ -736,7 +731,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(p.grid);
+        cfg.gridDim = dim3(launch_grid);
         cfg.blockDim = dim3(kAttnThreads);
         cfg.dynamicSmemBytes = total_smem;
         cfg.stream = stream;

@@ -10,8 +10,8 @@ advanced inside the graph).
 Tensor parallelism over ``tp_size`` GPUs of one node: every matrix is sharded by OUTPUT rows (QKV by
 heads, so the KV cache is sharded by kv head) and the activations are re-assembled with an NCCL
 all-gather after attention, O, SwiGLU and down (small kernels storing into NVLink peer memory, or NCCL
-when symmetric memory is unavailable).  Row sharding keeps every output element's products; only the order
-in which partial sums are combined changes, so the sharded stack equals the single-GPU stack to rounding.
+when symmetric memory is unavailable).  The kernels combine partial sums in an order that does not depend
+on the sharding, so the sharded stack is bitwise identical to the single-GPU stack.
 """
 from __future__ import annotations
 

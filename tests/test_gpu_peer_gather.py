@@ -1,8 +1,8 @@
 """Two-GPU checks of the NVLink peer all-gather and of the tensor-parallel stack built on it (skipped on a
 single GPU): the gathered rows equal torch's all_gather, repeated calls and CUDA-graph replays keep working,
-the stack over peer gathers equals the stack over NCCL gathers bit for bit (same arithmetic, different transport),
-and the sharded stack reproduces the unsharded one within rounding (sharding changes the order in which
-partial sums are combined, in the matvec as in the split-KV attention)."""
+and the sharded stack, over peer gathers as over NCCL gathers, reproduces the unsharded one bit for bit (the
+matvec sums a row's k-spans in k order whatever CTA holds the row, and the attention cuts the page list
+independently of the number of heads)."""
 import importlib
 import os
 import socket
@@ -76,10 +76,8 @@ def _rank_main(rank, world, port, result_path):
             st.capture()
             outs[name] = [st.step(toks[i]).clone() for i in range(4)]
         torch.cuda.synchronize()
-        def rel(a, b):
-            return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
-        ok["nccl_vs_single"] = max(rel(a, b) for a, b in zip(outs["nccl"], outs["single"]))
-        ok["peer_equals_nccl"] = all(torch.equal(a, b) for a, b in zip(outs["peer"], outs["nccl"]))
+        ok["nccl_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["nccl"], outs["single"]))
+        ok["peer_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["peer"], outs["single"]))
         ok["status"] = int(cabi.device_status())
         gathered = [None] * world
         dist.all_gather_object(gathered, ok)
@@ -108,8 +106,8 @@ def test_peer_gather_and_sharded_stack(tmp_path):
     rows = torch.load(result)
     for ok in rows:
         assert ok["status"] == 0, ok
-        assert ok["nccl_vs_single"] <= 2e-3, ok
+        assert ok["nccl_equals_single"], ok
         if ok["peer_enabled"]:
-            assert ok["peer_equals_nccl"], ok
+            assert ok["peer_equals_single"], ok
             assert all(v for k, v in ok.items() if k.startswith("gather_")), ok
     print("peer gather enabled:", rows[0]["peer_enabled"], rows[0]["peer_error"])
