@@ -190,6 +190,22 @@ int b200q_rope_kv_append(const void* qkv, const float* cos_table, const float* s
 int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch,
                          int rank, int world, int rows, int64_t row_bytes_local, void* stream);
 
+/* The same exchange fused into the kernels (no stand-alone launch): an exchange buffer is registered once
+ * under a slot number (0..15) - pointers as for b200q_peer_allgather, plus `counter`, a device uint32 owned by
+ * this rank and zero-initialised once.  b200q_tp_next(in_slot, out_slot) then applies to the NEXT call of
+ * b200q_qmatvec / b200q_norm_qmatvec / b200q_gate_up_swiglu / b200q_paged_gqa_decode made by this thread
+ * (-1 = none):
+ *   out_slot: the kernel stores its result rows (for gate/up: the SwiGLU rows) into column block `rank` of
+ *             every rank's full buffer instead of (y / act_out / out may then be NULL) or besides the local
+ *             output, and its last CTA publishes the sequence number;
+ *   in_slot:  the kernel's input `x` is this rank's view of that slot's full buffer; the kernel waits (bounded)
+ *             for all source ranks before reading it.
+ * Only the tensor-core matvec kernels and the split-KV attention kernels support this (B200Q_ERR_UNSUPPORTED
+ * otherwise); batch rows <= 16.  The sharded result equals the unsharded one bit for bit. */
+int b200q_tp_register(int slot, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* counter,
+                      int rank, int world);
+int b200q_tp_next(int in_slot, int out_slot);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,6 +36,19 @@ const DevProps& props() {
 }
 }  // namespace
 
+namespace {
+TpSlot g_tp_slots[16];
+bool g_tp_valid[16] = {};
+thread_local int g_tp_next_in = -1, g_tp_next_out = -1;
+}  // namespace
+
+const TpSlot* tp_slot(int slot) { return (slot >= 0 && slot < 16 && g_tp_valid[slot]) ? &g_tp_slots[slot] : nullptr; }
+void tp_take(int* in_slot, int* out_slot) {
+    *in_slot = g_tp_next_in;
+    *out_slot = g_tp_next_out;
+    g_tp_next_in = g_tp_next_out = -1;
+}
+
 int tuning_get(const char* key) {
     std::lock_guard<std::mutex> lock(g_mu);
     auto it = g_tuning.find(key);
@@ -257,6 +270,35 @@ int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* co
                          int rank, int world, int rows, int64_t row_bytes_local, void* stream) {
     return peer_allgather_impl(local, peer_full, peer_flags, epoch, rank, world, rows, row_bytes_local,
                                (cudaStream_t)stream);
+}
+
+int b200q_tp_register(int slot, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* counter,
+                      int rank, int world) {
+    if (slot < 0 || slot >= 16 || peer_full == nullptr || peer_flags == nullptr || epoch == nullptr || counter == nullptr)
+        return B200Q_ERR_BAD_ARG;
+    if (world < 2 || world > kTpMaxRanks || rank < 0 || rank >= world) return B200Q_ERR_BAD_ARG;
+    TpSlot t = {};
+    for (int r = 0; r < world; ++r) {
+        if (peer_full[r] == nullptr || peer_flags[r] == nullptr) return B200Q_ERR_BAD_ARG;
+        t.out.full[r] = peer_full[r];
+        t.out.flags[r] = peer_flags[r];
+    }
+    t.out.epoch = epoch;
+    t.out.counter = counter;
+    t.out.rank = rank;
+    t.out.world = world;
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_tp_slots[slot] = t;
+    g_tp_valid[slot] = true;
+    return B200Q_OK;
+}
+
+int b200q_tp_next(int in_slot, int out_slot) {
+    if ((in_slot >= 0 && tp_slot(in_slot) == nullptr) || (out_slot >= 0 && tp_slot(out_slot) == nullptr))
+        return B200Q_ERR_BAD_ARG;
+    g_tp_next_in = in_slot;
+    g_tp_next_out = out_slot;
+    return B200Q_OK;
 }
 
 int b200q_set_tuning(const char* key, int value) {

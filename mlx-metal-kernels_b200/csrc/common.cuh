@@ -42,6 +42,29 @@ enum DeviceEvent : int {
 };
 
 // ---------------------------------------------------------------------------------------------
+// Tensor-parallel exchange fused into kernels (see b200q_tp_register / b200q_tp_next).  The writer kernel
+// stores its output rows into column block `rank` of every rank's full buffer [rows, world * n] (peer stores)
+// and its last CTA publishes a sequence number in every rank's flag word; the reader kernel waits, bounded,
+// until the flag words of all source ranks carry the sequence number of its own rank's latest publication.
+// ---------------------------------------------------------------------------------------------
+constexpr int kTpMaxRanks = 8;
+struct TpOut {
+    void* full[kTpMaxRanks];        // full buffer of rank r as mapped on this GPU
+    uint32_t* flags[kTpMaxRanks];   // flag words [world] of rank r as mapped on this GPU
+    uint32_t* epoch;                // this rank's publication counter for the buffer (device memory)
+    uint32_t* counter;              // CTAs of the writer kernel that have finished (device memory, zero between uses)
+    int rank, world;                // world == 0: no exchange
+};
+struct TpIn {
+    const uint32_t* flags;          // this rank's flag words [world]
+    const uint32_t* epoch;          // this rank's publication counter (already advanced by the local writer)
+    int world;                      // world == 0: nothing to wait for
+};
+struct TpSlot { TpOut out; };       // host table entry
+const TpSlot* tp_slot(int slot);    // nullptr if the slot was never registered
+void tp_take(int* in_slot, int* out_slot);   // exchange slots set by b200q_tp_next for the next call (then cleared)
+
+// ---------------------------------------------------------------------------------------------
 // Tuning table (host side; see b200q_set_tuning)
 // ---------------------------------------------------------------------------------------------
 int tuning_get(const char* key);
@@ -108,6 +131,41 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
 // Programmatic dependent launch.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+constexpr uint32_t kTpSpinLimit = 1u << 22;   // acquire loads; each takes a fraction of a microsecond
+// Called by one whole warp of every CTA of the writer kernel after its stores: the last CTA publishes.
+__device__ __forceinline__ void tp_finish_writer(const TpOut& out, int lane) {
+    __threadfence_system();                      // this CTA's peer stores are visible before it is counted
+    __syncwarp();
+    unsigned last = 0;
+    if (lane == 0) last = (atomicAdd(out.counter, 1u) == gridDim.x * gridDim.y - 1u) ? 1u : 0u;
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+        __threadfence_system();
+        const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(out.epoch) + 1u;
+        if (lane < out.world) st_release_sys(out.flags[lane] + out.rank, seq);
+        __syncwarp();
+        if (lane == 0) {
+            *out.epoch = seq;
+            *out.counter = 0u;
+        }
+    }
+}
+// Called by threads 0 .. world-1 of the reader; returns false when the bounded wait ran out.
+__device__ __forceinline__ bool tp_wait_source(const TpIn& in, int src) {
+    const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(in.epoch);
+    for (uint32_t it = 0; it < kTpSpinLimit; ++it)
+        if ((int32_t)(ld_acquire_sys(in.flags + src) - seq) >= 0) return true;
+    return false;
+}
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

@@ -130,8 +130,12 @@ int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scal
                  const void* residual, void* y, int B, int64_t N, int64_t K, int group_size, int act_dtype,
                  int scale_dtype, const void* residual_in, const void* norm_weight, int norm_w_dtype, float eps,
                  void* z_out, void* normed_out, cudaStream_t stream) {
-    if ((bits != 4 && bits != 8) || x == nullptr || codes == nullptr || scales == nullptr || y == nullptr)
+    int tp_in_slot = -1, tp_out_slot = -1;
+    tp_take(&tp_in_slot, &tp_out_slot);
+    if ((bits != 4 && bits != 8) || x == nullptr || codes == nullptr || scales == nullptr ||
+        (y == nullptr && tp_out_slot < 0))
         return B200Q_ERR_BAD_ARG;
+    if ((tp_in_slot >= 0 || tp_out_slot >= 0) && B > 16) return B200Q_ERR_UNSUPPORTED;
     if (B <= 0 || N <= 0 || K <= 0 || group_size <= 0 || !is_act_dtype(act_dtype) || !is_scale_dtype(scale_dtype))
         return B200Q_ERR_BAD_ARG;
     if (norm_weight != nullptr && !is_scale_dtype(norm_w_dtype)) return B200Q_ERR_BAD_ARG;
@@ -160,7 +164,16 @@ int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scal
         p.B = bn; p.N = (int)N; p.K = (int)K; p.G = group_size; p.Gn = (int)((K + group_size - 1) / group_size);
         p.act_dtype = act_dtype; p.scale_dtype = scale_dtype;
         p.row_bytes = bits == 4 ? (int)((K + 1) / 2) : (int)K;
+        if (tp_out_slot >= 0) p.tp_out = tp_slot(tp_out_slot)->out;
+        if (tp_in_slot >= 0) {
+            const TpOut& src = tp_slot(tp_in_slot)->out;
+            p.tp_in.flags = src.flags[src.rank];
+            p.tp_in.epoch = src.epoch;
+            p.tp_in.world = src.world;
+        }
+        const bool tp_used = tp_in_slot >= 0 || tp_out_slot >= 0;
         int rc = fast_path_ok(p) ? dispatch_fast(bits, p, false, stream) : B200Q_ERR_UNSUPPORTED;
+        if (rc == B200Q_ERR_UNSUPPORTED && tp_used) return rc;      // exchanges exist only in the tensor-core kernel
         if (rc == B200Q_ERR_UNSUPPORTED && bn > 1 && fast_path_ok(p)) {
             chunk = (bn + 1) / 2;
             continue;
@@ -188,9 +201,12 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
                  void* act_out, const void* residual_in, const void* norm_weight, float eps, void* z_out,
                  void* normed_out, int rows, int64_t N, int64_t K, int group_size, int act_dtype, int scale_dtype,
                  int norm_w_dtype, cudaStream_t stream) {
+    int tp_in_slot = -1, tp_out_slot = -1;
+    tp_take(&tp_in_slot, &tp_out_slot);
     if ((bits != 4 && bits != 8) || x == nullptr || gate_codes == nullptr || up_codes == nullptr ||
         gate_scales == nullptr || up_scales == nullptr)
         return B200Q_ERR_BAD_ARG;
+    if ((tp_in_slot >= 0 || tp_out_slot >= 0) && rows > 16) return B200Q_ERR_UNSUPPORTED;
     if (rows <= 0 || N <= 0 || K <= 0 || group_size <= 0 || !is_act_dtype(act_dtype) || !is_scale_dtype(scale_dtype))
         return B200Q_ERR_BAD_ARG;
     if (norm_weight != nullptr && !is_scale_dtype(norm_w_dtype)) return B200Q_ERR_BAD_ARG;
@@ -222,8 +238,17 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
         p.B = bn; p.N = (int)N; p.K = (int)K; p.G = group_size; p.Gn = (int)((K + group_size - 1) / group_size);
         p.act_dtype = act_dtype; p.scale_dtype = scale_dtype;
         p.row_bytes = bits == 4 ? (int)((K + 1) / 2) : (int)K;
+        if (tp_out_slot >= 0) p.tp_out = tp_slot(tp_out_slot)->out;
+        if (tp_in_slot >= 0) {
+            const TpOut& src = tp_slot(tp_in_slot)->out;
+            p.tp_in.flags = src.flags[src.rank];
+            p.tp_in.epoch = src.epoch;
+            p.tp_in.world = src.world;
+        }
+        const bool tp_used = tp_in_slot >= 0 || tp_out_slot >= 0;
         int rc;
         rc = fast_path_ok(p) ? dispatch_fast(bits, p, true, stream) : B200Q_ERR_UNSUPPORTED;
+        if (rc == B200Q_ERR_UNSUPPORTED && tp_used) return rc;      // exchanges exist only in the tensor-core kernel
         if (rc == B200Q_ERR_UNSUPPORTED && bn > 1 && fast_path_ok(p)) {
             chunk = (bn + 1) / 2;
             continue;

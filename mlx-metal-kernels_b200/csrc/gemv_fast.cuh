@@ -326,24 +326,36 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         if (p.act_dtype == B200Q_F16) reinterpret_cast<__half*>(basep)[o] = __float2half_rn(v);
                         else reinterpret_cast<__nv_bfloat16*>(basep)[o] = __float2bfloat16_rn(v);
                     };
+                    // tensor-parallel exchange: the value goes to column block `rank` of every rank's full rows
+                    auto store_peers = [&](float v) {
+                        const int64_t of = (int64_t)b * p.N * p.tp_out.world + (int64_t)p.tp_out.rank * p.N + row0 + r;
+                        const unsigned short bits16 = p.act_dtype == B200Q_F16 ? __half_as_ushort(__float2half_rn(v))
+                                                                               : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+#pragma unroll 1
+                        for (int peer = 0; peer < p.tp_out.world; ++peer)
+                            reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
+                    };
                     if (GATE_UP) {
                         if (p.gate_out != nullptr) store(p.gate_out, val[0]);
                         if (p.up_out != nullptr) store(p.up_out, val[MATS - 1]);
-                        if (p.act_out != nullptr) {
+                        if (p.act_out != nullptr || p.tp_out.world > 0) {
                             const float gte = val[0];
                             const float silu = gte / (1.0f + expf(-gte));
-                            store(p.act_out, silu * val[MATS - 1]);
+                            if (p.act_out != nullptr) store(p.act_out, silu * val[MATS - 1]);
+                            if (p.tp_out.world > 0) store_peers(silu * val[MATS - 1]);
                         }
                     } else {
                         float v = val[0];
                         if (p.residual != nullptr) v = load_as_f32(p.residual, p.act_dtype, o) + v;
-                        store(p.y, v);
+                        if (p.y != nullptr) store(p.y, v);
+                        if (p.tp_out.world > 0) store_peers(v);
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&slot_free[ps]);
         }
+        if (p.tp_out.world > 0) tp_finish_writer(p.tp_out, lane);
         EVENT(9);
         return;
     }
@@ -384,6 +396,11 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
     pdl_wait();   // activations belong to the previous kernel until here
     if (warp == 0) EVENT(2);
+    if (p.tp_in.world > 0) {
+        // the activations are an exchange buffer filled by all ranks: wait for every source rank's flag
+        if (ctid < p.tp_in.world && !tp_wait_source(p.tp_in, ctid)) atomicMax(&g_device_status, (int)EV_PEER_WAIT);
+        named_bar_sync(1, kConsumerThreads);
+    }
 
     // per batch row: inv_rms (norm prologue) and the power of two that maps bf16 rows into fp16 range
     if (need_row_pass) {

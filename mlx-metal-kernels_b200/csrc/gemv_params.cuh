@@ -57,6 +57,8 @@ struct GemvParams {
     int meta_vec;           // scales / zeros are fp16, 16-byte aligned, Gn % 8 == 0: vector loads
     int interleave;         // 1: CTA c takes tiles c, c + grid, ... instead of a contiguous row range
     int rows_lo, rem;       // CTA c owns rows_lo (+1 if c < rem) rows
+    TpOut tp_out;           // tensor-parallel exchange: outputs go to every rank's full buffer (world == 0: off)
+    TpIn tp_in;             // ... the activations are another exchange's full buffer: wait for its flags first
     uint32_t off_xs, off_xzero, off_xmx, off_xscale, off_part, off_meta, off_ring;
     uint32_t xstride, stage_bytes, row_stride;
 };

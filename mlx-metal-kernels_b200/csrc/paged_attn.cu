@@ -64,6 +64,7 @@ struct AttnParams {
     int scale_row_halves;       // halves of one token row of scales, all kv heads
     uint32_t off_prefix, off_ring, slot_bytes;
     int grid;
+    TpOut tp_out;               // tensor-parallel exchange of the merged rows (world == 0: off)
 };
 
 __device__ __forceinline__ int clamp_len(int len, int cap) { return max(0, min(len, cap)); }
@@ -556,8 +557,20 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
         for (int w = 0; w < kMergeWarps; ++w) { sum += red[w][threadIdx.x]; l_tot += red_s[1][w]; }
         const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
         const size_t o = ((size_t)b * p.Hq + hq) * D + threadIdx.x;
-        if (p.q_dtype == B200Q_F16) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(sum * inv);
-        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(sum * inv);
+        const unsigned short bits16 = p.q_dtype == B200Q_F16 ? __half_as_ushort(__float2half_rn(sum * inv))
+                                                             : __bfloat16_as_ushort(__float2bfloat16_rn(sum * inv));
+        if (p.out != nullptr) reinterpret_cast<unsigned short*>(p.out)[o] = bits16;
+        if (p.tp_out.world > 0) {
+            // tensor-parallel exchange: this head's row goes to column block `rank` of every rank's full rows
+            const size_t of = ((size_t)b * p.tp_out.world + p.tp_out.rank) * p.Hq * D + (size_t)hq * D + threadIdx.x;
+#pragma unroll 1
+            for (int peer = 0; peer < p.tp_out.world; ++peer)
+                reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
+        }
+    }
+    if (p.tp_out.world > 0) {
+        __syncthreads();                         // all of this CTA's peer stores are issued
+        if (warp == 0) tp_finish_writer(p.tp_out, lane);
     }
 }
 
@@ -654,8 +667,10 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
                           void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size,
                           int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
                           int scale_dtype, cudaStream_t stream) {
+    int tp_in_slot = -1, tp_out_slot = -1;
+    tp_take(&tp_in_slot, &tp_out_slot);
     if ((bits != 4 && bits != 8) || q == nullptr || k_codes == nullptr || v_codes == nullptr || k_scales == nullptr ||
-        v_scales == nullptr || block_table == nullptr || lengths == nullptr || out == nullptr)
+        v_scales == nullptr || block_table == nullptr || lengths == nullptr || (out == nullptr && tp_out_slot < 0))
         return B200Q_ERR_BAD_ARG;
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
         group_size <= 0 || Hq % Hkv != 0 || !is_act_dtype(q_dtype) || !is_scale_dtype(scale_dtype))
@@ -670,6 +685,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
                          Hkv <= kAttnWarps && page_size == 16 && B <= kMaxBatchFast &&
                          ((uintptr_t)q % 16 == 0) && ((uintptr_t)k_codes % 16 == 0) && ((uintptr_t)v_codes % 16 == 0) &&
                          ((uintptr_t)k_scales % 8 == 0) && ((uintptr_t)v_scales % 8 == 0);
+    if (!fast_ok && tp_out_slot >= 0) return B200Q_ERR_UNSUPPORTED;   // the exchange exists only in the split-KV kernels
     if (!fast_ok) {
         SimpleParams sp = {q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out,
                            B, Hq, Hkv, D, page_size, max_blocks, group_size, Gd, bits, q_dtype, scale_dtype,
@@ -681,6 +697,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     if (workspace == nullptr || workspace_bytes < paged_gqa_workspace_bytes_impl(B, Hq, Hkv, D)) return B200Q_ERR_WORKSPACE;
 
     AttnParams p = {};
+    if (tp_out_slot >= 0) p.tp_out = tp_slot(tp_out_slot)->out;
     p.q = (const __half*)q; p.k_codes = k_codes; p.v_codes = v_codes;
     p.k_scales = (const __half*)k_scales; p.v_scales = (const __half*)v_scales;
     p.block_table = block_table; p.lengths = lengths; p.partial = (float*)workspace; p.out = out;

@@ -27,15 +27,6 @@ struct PeerGatherParams {
     int rank, world, rows, vec_loc;     // vec_loc = 16-byte vectors per row of the local shard
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 __global__ void __launch_bounds__(512) peer_allgather_kernel(const __grid_constant__ PeerGatherParams p) {
     const uint32_t seq = *p.epoch + 1u;             // identical on all ranks: every rank counts its own calls
     const int total = p.rows * p.vec_loc;

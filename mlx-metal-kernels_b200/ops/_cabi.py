@@ -36,6 +36,8 @@ SIGNATURES = {
     "b200q_gate_up_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _vp, _vp,
                                   _i, _i64, _i64, _i, _i, _i, _vp]),
     "b200q_peer_allgather": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp]),
+    "b200q_tp_register": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),
+    "b200q_tp_next": (_i, [_i, _i]),
     "b200q_swiglu": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _vp]),
     "b200q_residual_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "b200q_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f, _i, _i, _vp]),

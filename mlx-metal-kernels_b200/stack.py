@@ -137,8 +137,11 @@ class PagedKV:
 class DecodeStack:
     """Runs decode steps of ``cfg.n_layers`` layers on one GPU (or one tensor-parallel rank)."""
 
+    _next_slot = 0      # exchange slots of the library handed out so far (process-wide)
+
     def __init__(self, cfg: StackConfig, layers, final_norm, embedding, batch: int, max_context: int, device,
-                 tp_rank: int = 0, tp_size: int = 1, process_group=None, use_peer_gather: bool = True):
+                 tp_rank: int = 0, tp_size: int = 1, process_group=None, use_peer_gather: bool = True,
+                 fuse_exchange: bool = True):
         self.cfg, self.B, self.device = cfg, batch, device
         self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
         self.lib = _cabi.load()
@@ -166,6 +169,8 @@ class DecodeStack:
         self.act = torch.zeros((batch, cfg.intermediate // tp_size), **f16)
         self.out = torch.zeros((batch, cfg.hidden), **f16)
         self.peer_gather = False
+        self.peer_fused = False
+        self.fuse_exchange = fuse_exchange
         if tp_size > 1:
             self.o_loc = torch.zeros((batch, cfg.hidden // tp_size), **f16)
             self.gather_attn = torch.zeros((tp_size, batch, self.hq * D), **f16)
@@ -224,9 +229,21 @@ class DecodeStack:
             self.peer_ptrs.append((ctypes.c_void_p * W)(*[p + o for p in ptrs]))
             self.peer_flag_ptrs.append((ctypes.c_void_p * W)(*[p + flag_off + 256 * i for p in ptrs]))
         self.peer_epochs = torch.zeros(3, dtype=torch.int32, device=self.device)
+        self.peer_counters = torch.zeros(3, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize()
         dist.barrier(group=self.pg)                            # every rank's buffer is zeroed before anyone stores
         self.peer_gather = True
+        # the same buffers as exchange slots of the kernels themselves (stores from the epilogue, waits in the
+        # next prologue): three slots per stack instance
+        base = DecodeStack._next_slot
+        if self.fuse_exchange and base + 3 <= 16:
+            DecodeStack._next_slot += 3
+            self.slots = (base, base + 1, base + 2)
+            for i, slot in enumerate(self.slots):
+                _cabi.check(self.lib.b200q_tp_register(slot, self.peer_ptrs[i], self.peer_flag_ptrs[i],
+                                                       self.peer_epochs[i:].data_ptr(), self.peer_counters[i:].data_ptr(),
+                                                       self.tp_rank, W), "tp_register")
+            self.peer_fused = True
 
     def _gather(self, which: int, local):
         """All-gather of ``local`` [B, n_loc] into [B, tp * n_loc] (rank-major columns); ``which`` selects the
@@ -260,6 +277,7 @@ class DecodeStack:
         F16, ck = _cabi.F16, _cabi.check
         n = 0
         torch.index_select(self.embedding, 0, self.token_ids, out=self.h)
+        pending_slot = -1
         pending = None      # tensor-parallel path: gathered down-projection rows whose residual add (h2 + rows -> h)
                             # is folded into the next kernel's prologue instead of being a launch of its own
         for w, cache in zip(self.layers, self.caches):
@@ -269,6 +287,8 @@ class DecodeStack:
                                           None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(), None, self.qkv.data_ptr(), B,
                                           qw.shape[0], cfg.hidden, G, F16, F16, st), "norm_qmatvec")
             else:
+                if pending_slot >= 0:
+                    ck(lib.b200q_tp_next(pending_slot, -1), "tp_next")
                 ck(lib.b200q_norm_qmatvec(bits, pending.data_ptr(), self.h2.data_ptr(), w["input_norm"].data_ptr(), F16,
                                           cfg.eps, self.h.data_ptr(), None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(),
                                           None, self.qkv.data_ptr(), B, qw.shape[0], cfg.hidden, G, F16, F16, st),
@@ -279,9 +299,12 @@ class DecodeStack:
                                         cache.v_scales.data_ptr(), cfg.kv_bits, B, self.hq, self.hkv, D, cfg.page_size,
                                         self.num_pages, self.max_blocks, cfg.kv_group_size, self.cos.shape[0], st),
                "rope_kv_append")
+            if self.peer_fused:
+                ck(lib.b200q_tp_next(-1, self.slots[0]), "tp_next")
             ck(lib.b200q_paged_gqa_decode(cfg.kv_bits, self.q_rot.data_ptr(), cache.k_codes.data_ptr(),
                                           cache.v_codes.data_ptr(), cache.k_scales.data_ptr(), cache.v_scales.data_ptr(),
-                                          self.block_table.data_ptr(), self.lengths.data_ptr(), self.attn.data_ptr(),
+                                          self.block_table.data_ptr(), self.lengths.data_ptr(),
+                                          None if self.peer_fused else self.attn.data_ptr(),
                                           self.workspace.data_ptr(), self.workspace.numel(), B, self.hq, self.hkv, D,
                                           cfg.page_size, self.num_pages, self.max_blocks, cfg.kv_group_size,
                                           1.0 / math.sqrt(D), F16, F16, st), "paged_gqa_decode")
@@ -301,7 +324,7 @@ class DecodeStack:
                                      self.h2.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.intermediate, G, F16, F16, st),
                    "down_proj")
                 n += 7
-            else:
+            elif not self.peer_fused:
                 attn_full = self._gather(0, self.attn)
                 ck(lib.b200q_qmatvec(bits, attn_full.data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
                                      self.o_loc.data_ptr(), B, ow.shape[0], cfg.n_heads * D, G, F16, F16, st), "o_proj")
@@ -316,6 +339,36 @@ class DecodeStack:
                                      self.o_loc.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
                 pending = self._gather(1, self.o_loc)      # h = cast(h2 + down) happens in the next prologue
                 n += 7 + (4 if self.peer_gather else 0)
+            else:
+                # exchanges fused into the kernels: the O, gate/up and down launches wait for the rows they read and
+                # store the rows they produce straight into every rank's buffers (the attention rows were stored by
+                # the merge kernel above)
+                sa, sh, sm = self.slots
+                last = w is self.layers[-1]
+                ck(lib.b200q_tp_next(sa, sh), "tp_next")
+                ck(lib.b200q_qmatvec(bits, self.peer_full[0].data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
+                                     None, B, ow.shape[0], cfg.n_heads * D, G, F16, F16, st), "o_proj")
+                ck(lib.b200q_tp_next(sh, sm), "tp_next")
+                ck(lib.b200q_gate_up_swiglu(bits, self.peer_full[1].data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
+                                            us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, None,
+                                            self.h.data_ptr(), w["post_norm"].data_ptr(), F16, cfg.eps, self.h2.data_ptr(),
+                                            None, B, gw.shape[0], cfg.hidden, G, F16, F16, st), "gate_up")
+                if last:
+                    # the final norm is not a kernel that can wait: close the step with the stand-alone exchange
+                    ck(lib.b200q_tp_next(sm, -1), "tp_next")
+                    ck(lib.b200q_qmatvec(bits, self.peer_full[2].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
+                                         None, self.o_loc.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st),
+                       "down_proj")
+                    pending = self._gather(1, self.o_loc)
+                    pending_slot = -1
+                    n += 8
+                else:
+                    ck(lib.b200q_tp_next(sm, sh), "tp_next")
+                    ck(lib.b200q_qmatvec(bits, self.peer_full[2].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
+                                         None, None, B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
+                    pending = self.peer_full[1]
+                    pending_slot = sh
+                    n += 7
         if pending is None:
             ck(lib.b200q_rmsnorm_residual(self.h.data_ptr(), None, self.final_norm.data_ptr(), self.out.data_ptr(), None,
                                           B, cfg.hidden, cfg.eps, F16, _cabi.dtype_code(self.final_norm.dtype), st),

@@ -43,9 +43,9 @@ def _rank_main(rank, world, port, result_path):
         fnorm = torch.ones(cfg.hidden, dtype=torch.float16, device=device)
         B = 3
 
-        def make(tp_rank, tp_size, peer):
+        def make(tp_rank, tp_size, peer, fused=False):
             st = stack_mod.DecodeStack(cfg, layers, fnorm, emb, B, 96, device, tp_rank=tp_rank, tp_size=tp_size,
-                                       process_group=None, use_peer_gather=peer)
+                                       process_group=None, use_peer_gather=peer, fuse_exchange=fused)
             for i, c in enumerate(st.caches):          # same context on every rank: fill the full cache, keep own heads
                 full = stack_mod.PagedKV(cfg, cfg.n_kv_heads, st.num_pages, device)
                 full.fill_random(cfg, 900 + i)
@@ -59,7 +59,9 @@ def _rank_main(rank, world, port, result_path):
         single = make(0, 1, False)
         nccl = make(rank, world, False)
         peer = make(rank, world, True)
+        fused = make(rank, world, True, fused=True)
         ok["peer_enabled"] = bool(peer.peer_gather)
+        ok["fused_enabled"] = bool(fused.peer_fused)
         ok["peer_error"] = getattr(peer, "peer_gather_error", "")
         # the gather by itself, several calls in a row
         if peer.peer_gather:
@@ -72,12 +74,13 @@ def _rank_main(rank, world, port, result_path):
         toks = torch.randint(0, cfg.vocab, (4, B), device=device)
         dist.broadcast(toks, 0)
         outs = {}
-        for name, st in (("single", single), ("nccl", nccl), ("peer", peer)):
+        for name, st in (("single", single), ("nccl", nccl), ("peer", peer), ("fused", fused)):
             st.capture()
             outs[name] = [st.step(toks[i]).clone() for i in range(4)]
         torch.cuda.synchronize()
         ok["nccl_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["nccl"], outs["single"]))
         ok["peer_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["peer"], outs["single"]))
+        ok["fused_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["fused"], outs["single"]))
         ok["status"] = int(cabi.device_status())
         gathered = [None] * world
         dist.all_gather_object(gathered, ok)
@@ -109,5 +112,8 @@ def test_peer_gather_and_sharded_stack(tmp_path):
         assert ok["nccl_equals_single"], ok
         if ok["peer_enabled"]:
             assert ok["peer_equals_single"], ok
+        if ok["fused_enabled"]:
+            assert ok["fused_equals_single"], ok
             assert all(v for k, v in ok.items() if k.startswith("gather_")), ok
-    print("peer gather enabled:", rows[0]["peer_enabled"], rows[0]["peer_error"])
+    print("peer gather enabled:", rows[0]["peer_enabled"], "fused exchange enabled:", rows[0]["fused_enabled"],
+          rows[0]["peer_error"])
