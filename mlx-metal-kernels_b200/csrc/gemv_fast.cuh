@@ -571,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         // The unit's 8 groups in execution order e = pass * GS + slot; the operands of group e + 1 are
         // fetched from shared memory before the tensor-core work of group e is issued.
         constexpr int NXV = BITS == 4 ? NW : NW / 2;          // 16-byte activation loads per group and column tile
-        constexpr bool PIPE = LOGG <= 6 && NT == 1;           // (wider groups / two column tiles: not enough registers)
+        constexpr bool PIPE = LOGG <= 6 && NT == 1 && !(BITS == 8 && NB >= 4);   // (elsewhere: not enough registers)
         struct Operands { uint32_t wa[NW], wb[NW]; };
         auto fetch = [&](int e, Operands& o) {
             const int pass = e / GS, js = e % GS;
