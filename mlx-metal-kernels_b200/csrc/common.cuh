@@ -196,6 +196,12 @@ __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
+// Transposes an 8x8 matrix of 16-bit values held one row per 4 lanes (lane l: row l/4, columns 2(l%4), 2(l%4)+1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(a));
+    return r;
+}
 __device__ __forceinline__ uint32_t half_dup(__half h) {
     uint32_t u = __half_as_ushort(h);
     return u | (u << 16);

@@ -16,12 +16,14 @@
 //     pages ahead.  No CTA-wide barrier, no bank conflicts (the ring is laid out [piece][lane]).
 //     Measured on B200: the bulk-copy (TMA) engine needs >= 2 KB per copy to reach HBM speed,
 //     and a token row of one page is 512 B, so per-lane asynchronous copies are the faster route.
-//   * scores S^T[head, token] = Q K^T on mma.sync.m16n8k16 with the query heads of the group as
-//     rows and in-register dequantised K as the B operand; online softmax in fp32; the
-//     probabilities are already in B-operand layout for O^T[d, head] += V^T P, where V^T is the A
-//     operand built from the four token rows with one byte-permute per word pair.  KV bytes are
-//     read once per kv head, not once per query head; Khat / Vhat are bit-identical to the
-//     reference's fp16 dequantised cache.
+//   * scores S[token, head] = K Q^T on mma.sync.m16n8k16 with the 16 tokens of a page as rows (in-register
+//     dequantised K is the A operand) and the up to 8 query heads of the group as columns: no padding rows and
+//     no zero operand registers.  Online softmax in fp32 (a lane holds two heads of tokens g and g + 8; the row
+//     maximum is a butterfly over the 8 token lanes, the sums stay per lane until a partial is written).  One
+//     movmatrix per 8 tokens turns the probabilities into the B operand of O^T[d, head] += V^T P, where V^T is
+//     the A operand built from the four token rows with one byte-permute per word pair.  KV bytes are read once
+//     per kv head, not once per query head; Khat / Vhat are bit-identical to the reference's fp16 dequantised
+//     cache.
 //
 // Everything else (other head dims, bf16 queries, other group sizes) runs the simple kernel: one
 // warp per (sequence, query head), the reference's streaming-softmax loop.
@@ -39,7 +41,10 @@ namespace {
 
 constexpr int kAttnWarps = 8;
 constexpr int kAttnThreads = kAttnWarps * 32;
-constexpr int kMaxGrid = 304;             // upper bound on CTAs of the fast kernel (sizes the workspace)
+#ifndef B200Q_ATTN_CTAS
+#define B200Q_ATTN_CTAS 2                    // resident CTAs per SM of the fast kernel's dense shape
+#endif
+constexpr int kMaxGrid = 152 * B200Q_ATTN_CTAS;   // upper bound on CTAs of the fast kernel (sizes the workspace)
 constexpr int kMaxBatchFast = 2048;       // prefix sums of page counts live in shared memory
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -129,7 +134,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // memory.  TWO = false: one CTA per SM with a deeper ring, for grids that do not fill the SMs twice anyway.
 constexpr int ring_depth(int bits, bool two) { return bits == 4 ? (two ? 4 : 8) : (two ? 2 : 5); }
 template <int BITS, int LOGG, bool TWO>
-__global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged_attn_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int D = 128;
     constexpr int DP = BITS == 4 ? 64 : 128;          // code bytes per head and token
@@ -165,10 +170,10 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
     uint8_t* my_ring = smem + p.off_ring + (size_t)warp * NS * SLOT;
     const int n_my = hi - lo;                                     // pages this warp walks: f = lo + j
 
-    uint32_t qa[8][2];          // Q as A operand: [mma][a0a1 (row g), a4a5 (row g)]; rows 8..15 are zero
+    uint32_t qb[8][2];          // Q^T as B operand: [mma][b0b1, b2b3], column g = query head g of the group
     float o[8][4];              // O^T tiles: rows d, cols heads
-    float m_run = -INFINITY;    // running max / sum of query head g of the group
-    float l_run = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY};    // running max of query heads 2t, 2t+1 of the group
+    float l_run[2] = {0.0f, 0.0f};              // this lane's share (tokens g, g + 8 of every page) of their running sums
     int cur_b = -1;
 
     // Page descriptors (page id, sequence, valid tokens) of 32 consecutive pages of this warp, one per
@@ -250,9 +255,12 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
 
     auto flush = [&](int b) {
         float* dst = p.partial + ((size_t)(vc + b) * p.Hq) * (D + 2);
-        float l0 = l_run;
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        float l0 = l_run[0], l1 = l_run[1];
+#pragma unroll
+        for (int o2 = 4; o2 < 32; o2 <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, o2);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, o2);
+        }
         // O^T[d][head]: thread (g,t) holds d = 16g + 2i (+1), heads 2t, 2t+1
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -263,9 +271,15 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
                 if (head < group) dst[(size_t)(h * group + head) * (D + 2) + d] = o[i][e];
             }
         }
-        if (t == 0 && g < group) {
-            dst[(size_t)(h * group + g) * (D + 2) + D] = m_run;
-            dst[(size_t)(h * group + g) * (D + 2) + D + 1] = l0;
+        if (g == 0) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int head = 2 * t + e;
+                if (head < group) {
+                    dst[(size_t)(h * group + head) * (D + 2) + D] = m_run[e];
+                    dst[(size_t)(h * group + head) * (D + 2) + D + 1] = e ? l1 : l0;
+                }
+            }
         }
     };
 
@@ -290,13 +304,13 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
         if (b != cur_b) {
             if (cur_b >= 0) flush(cur_b);
             cur_b = b;
-            m_run = -INFINITY;
-            l_run = 0.0f;
+            m_run[0] = m_run[1] = -INFINITY;
+            l_run[0] = l_run[1] = 0.0f;
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
-            // Q fragments for (b, kv head h): row r of the tile is query head h*group + r (r < group <= 8)
+            // Q fragments for (b, kv head h): column r of the tile is query head h*group + r (r < group <= 8)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint4 u = make_uint4(0, 0, 0, 0);
@@ -307,12 +321,12 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
                 const uint32_t w[4] = {u.x, u.y, u.z, u.w};   // halves d0..d0+7
                 if (BITS == 4) {
                     // mma 2c: pairs (0,4) (1,5); mma 2c+1: pairs (2,6) (3,7)
-                    qa[2 * c][0] = prmt(w[0], w[2], 0x5410);     qa[2 * c][1] = prmt(w[0], w[2], 0x7632);
-                    qa[2 * c + 1][0] = prmt(w[1], w[3], 0x5410); qa[2 * c + 1][1] = prmt(w[1], w[3], 0x7632);
+                    qb[2 * c][0] = prmt(w[0], w[2], 0x5410);     qb[2 * c][1] = prmt(w[0], w[2], 0x7632);
+                    qb[2 * c + 1][0] = prmt(w[1], w[3], 0x5410); qb[2 * c + 1][1] = prmt(w[1], w[3], 0x7632);
                 } else {
                     // mma 2c: codes 0..3 -> pairs (0,1) (2,3); mma 2c+1: codes 4..7
-                    qa[2 * c][0] = w[0];     qa[2 * c][1] = w[1];
-                    qa[2 * c + 1][0] = w[2]; qa[2 * c + 1][1] = w[3];
+                    qb[2 * c][0] = w[0];     qb[2 * c][1] = w[1];
+                    qb[2 * c + 1][0] = w[2]; qb[2 * c + 1][1] = w[3];
                 }
             }
         }
@@ -321,95 +335,87 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? 2 : 1) paged_attn_kernel(c
             const __half* ksc = reinterpret_cast<const __half*>(slot + K_BYTES + V_BYTES);         // [16][4]
             const __half* vsc = ksc + 64;                                                             // [16][4]
 
-            // ---------------- S^T = Q K^T : two n-tiles (tokens g and g + 8) ------------------
-            float s[2][4];
+            // ---------------- S = K Q^T : rows = tokens g and g + 8, columns = query heads 2t, 2t+1 ----------
+            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (BITS == 4) {
+                const uint4 ua = *reinterpret_cast<const uint4*>(slot + lane * 16);          // token g
+                const uint4 ub = *reinterpret_cast<const uint4*>(slot + 512 + lane * 16);    // token g + 8
+                const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+                const uint32_t sa = half_dup(__habs(ksc[g * 4 + ((32 * t) >> LOGG)]));
+                const uint32_t sb = half_dup(__habs(ksc[(g + 8) * 4 + ((32 * t) >> LOGG)]));
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t wa2 = wa[c] >> 8, wb2 = wb[c] >> 8;
+                    // exact (code - 8), then one rounding in the multiply: fp16((code-8)*s)
+                    const uint32_t a0 = hmul2_u32(hsub2_u32(lop3_and_or(wa[c], 0x000F000Fu, 0x64006400u), 0x64086408u), sa);
+                    const uint32_t a1 = hmul2_u32(hsub2_u32(lop3_and_or(wb[c], 0x000F000Fu, 0x64006400u), 0x64086408u), sb);
+                    const uint32_t a2 = hmul2_u32(hsub2_u32(lop3_and_or(wa[c], 0x00F000F0u, 0x54005400u), 0x54805480u), sa);
+                    const uint32_t a3 = hmul2_u32(hsub2_u32(lop3_and_or(wb[c], 0x00F000F0u, 0x54005400u), 0x54805480u), sb);
+                    mma_m16n8k16(s, a0, a1, a2, a3, qb[2 * c][0], qb[2 * c][1]);
+                    const uint32_t c0 = hmul2_u32(hsub2_u32(lop3_and_or(wa2, 0x000F000Fu, 0x64006400u), 0x64086408u), sa);
+                    const uint32_t c1 = hmul2_u32(hsub2_u32(lop3_and_or(wb2, 0x000F000Fu, 0x64006400u), 0x64086408u), sb);
+                    const uint32_t c2 = hmul2_u32(hsub2_u32(lop3_and_or(wa2, 0x00F000F0u, 0x54005400u), 0x54805480u), sa);
+                    const uint32_t c3 = hmul2_u32(hsub2_u32(lop3_and_or(wb2, 0x00F000F0u, 0x54005400u), 0x54805480u), sb);
+                    mma_m16n8k16(s, c0, c1, c2, c3, qb[2 * c + 1][0], qb[2 * c + 1][1]);
+                }
+            } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
-                const int tok = g + 8 * nt;
-                if (BITS == 4) {
-                    const uint4 u = *reinterpret_cast<const uint4*>(slot + nt * 512 + lane * 16);
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-                    const uint32_t s2 = half_dup(__habs(ksc[tok * 4 + ((32 * t) >> LOGG)]));
+                for (int hb = 0; hb < 2; ++hb) {
+                    const uint4 ua = *reinterpret_cast<const uint4*>(slot + hb * 512 + lane * 16);          // token g
+                    const uint4 ub = *reinterpret_cast<const uint4*>(slot + (2 + hb) * 512 + lane * 16);    // token g + 8
+                    const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+                    const uint32_t sa = half_dup(__habs(ksc[g * 4 + ((64 * hb + 16 * t) >> LOGG)]));
+                    const uint32_t sb = half_dup(__habs(ksc[(g + 8) * 4 + ((64 * hb + 16 * t) >> LOGG)]));
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        const uint32_t w2 = w[c] >> 8;
-                        // exact (code - 8), then one rounding in the multiply: fp16((code-8)*s)
-                        const uint32_t v0 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                        const uint32_t v1 = hmul2_u32(hsub2_u32(lop3_and_or(w[c], 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                        const uint32_t v2 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                        const uint32_t v3 = hmul2_u32(hsub2_u32(lop3_and_or(w2, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                        mma_m16n8k16(s[nt], qa[2 * c][0], 0u, qa[2 * c][1], 0u, v0, v1);
-                        mma_m16n8k16(s[nt], qa[2 * c + 1][0], 0u, qa[2 * c + 1][1], 0u, v2, v3);
-                    }
-                } else {
-#pragma unroll
-                    for (int hb = 0; hb < 2; ++hb) {
-                        const uint4 u = *reinterpret_cast<const uint4*>(slot + (2 * nt + hb) * 512 + lane * 16);
-                        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-                        const uint32_t s2 = half_dup(__habs(ksc[tok * 4 + ((64 * hb + 16 * t) >> LOGG)]));
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const uint32_t v0 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4140u), 0x64806480u), s2);
-                            const uint32_t v1 = hmul2_u32(hsub2_u32(prmt(w[c], 0x64646464u, 0x4342u), 0x64806480u), s2);
-                            const int mi = 4 * hb + c;
-                            mma_m16n8k16(s[nt], qa[mi][0], 0u, qa[mi][1], 0u, v0, v1);
-                        }
+                        const uint32_t a0 = hmul2_u32(hsub2_u32(prmt(wa[c], 0x64646464u, 0x4140u), 0x64806480u), sa);
+                        const uint32_t a1 = hmul2_u32(hsub2_u32(prmt(wb[c], 0x64646464u, 0x4140u), 0x64806480u), sb);
+                        const uint32_t a2 = hmul2_u32(hsub2_u32(prmt(wa[c], 0x64646464u, 0x4342u), 0x64806480u), sa);
+                        const uint32_t a3 = hmul2_u32(hsub2_u32(prmt(wb[c], 0x64646464u, 0x4342u), 0x64806480u), sb);
+                        const int mi = 4 * hb + c;
+                        mma_m16n8k16(s, a0, a1, a2, a3, qb[mi][0], qb[mi][1]);
                     }
                 }
             }
-            // ---------------- online softmax (row g = query head g of the group; rows 8..15 are padding) ----
-            float pr[2][2];
-            float alpha;
+            // ---------------- online softmax: this lane holds heads 2t, 2t+1 of tokens g and g + 8 ----------
+            float alpha[2];
+            uint32_t pb0, pb1;      // P[token][head] as the B operand of O^T += V^T P
             {
-                float mx = -INFINITY;
+                const bool in0 = g < valid, in1 = g + 8 < valid;   // also discards whatever stale bytes sit in unused slots
+                s[0] = in0 ? s[0] * sm_scale : -INFINITY;
+                s[1] = in0 ? s[1] * sm_scale : -INFINITY;
+                s[2] = in1 ? s[2] * sm_scale : -INFINITY;
+                s[3] = in1 ? s[3] * sm_scale : -INFINITY;
+                float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int tok = 8 * nt + 2 * t + e;
-                        float v = s[nt][e] * sm_scale;
-                        if (tok >= valid) v = -INFINITY;     // also discards whatever stale bytes sit in unused slots
-                        s[nt][e] = v;
-                        mx = fmaxf(mx, v);
-                    }
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const float m_new = fmaxf(m_run, mx);          // finite: every staged page has a valid token
-                alpha = fast_exp2((m_run - m_new) * kLog2e);   // exp(-inf) = 0 on the first page
-                float lsum = 0.0f;
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const float pv = fast_exp2((s[nt][e] - m_new) * kLog2e);
-                        pr[nt][e] = pv;
-                        lsum += pv;
-                    }
-                l_run = l_run * alpha + lsum;
-                m_run = m_new;
+                for (int o2 = 4; o2 < 32; o2 <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o2));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o2));
+                }
+                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);   // finite: every staged page has a valid token
+                alpha[0] = fast_exp2((m_run[0] - mn0) * kLog2e);                       // exp(-inf) = 0 on the first page
+                alpha[1] = fast_exp2((m_run[1] - mn1) * kLog2e);
+                const float p0 = fast_exp2((s[0] - mn0) * kLog2e), p1 = fast_exp2((s[1] - mn1) * kLog2e);
+                const float p2 = fast_exp2((s[2] - mn0) * kLog2e), p3 = fast_exp2((s[3] - mn1) * kLog2e);
+                // per-lane share of the sums (tokens g, g + 8); the 8 shares of a head are added when a partial is written
+                l_run[0] = l_run[0] * alpha[0] + (p0 + p2);
+                l_run[1] = l_run[1] * alpha[1] + (p1 + p3);
+                m_run[0] = mn0;
+                m_run[1] = mn1;
+                // transpose (token g, heads 2t, 2t+1) into (tokens 2t, 2t+1, head g): b0b1 tokens 0..7, b2b3 tokens 8..15
+                const __half2 x0 = __floats2half2_rn(p0, p1);
+                const __half2 x1 = __floats2half2_rn(p2, p3);
+                pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&x0));
+                pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&x1));
             }
-            // ---------------- rescale O^T columns (heads 2t, 2t+1); alpha of head r lives in lanes g == r ----
-            {
-                const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * t);
-                const float a1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);
-                if (__any_sync(0xffffffffu, (a0 != 1.0f) || (a1 != 1.0f))) {
+            // ---------------- rescale O^T columns (heads 2t, 2t+1) ----------------------------------------------
+            if (__any_sync(0xffffffffu, (alpha[0] != 1.0f) || (alpha[1] != 1.0f))) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        o[i][0] *= a0; o[i][1] *= a1; o[i][2] *= a0; o[i][3] *= a1;
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[1]; o[i][2] *= alpha[0]; o[i][3] *= alpha[1];
                 }
             }
             // ---------------- O^T += V^T P ---------------------------------------------------------
-            // B operand: P[token][head]: b0b1 = tokens 2t,2t+1 ; b2b3 = tokens 2t+8,2t+9 ; column = head g
-            uint32_t pb0, pb1;
-            {
-                const __half2 x0 = __floats2half2_rn(pr[0][0], pr[0][1]);   // tokens 2t, 2t+1
-                const __half2 x1 = __floats2half2_rn(pr[1][0], pr[1][1]);   // tokens 2t+8, 2t+9
-                pb0 = *reinterpret_cast<const uint32_t*>(&x0);
-                pb1 = *reinterpret_cast<const uint32_t*>(&x1);
-            }
             const int vgrp = (16 * g) >> LOGG;
             uint32_t vreg[2][16];   // [token pair][j]: (Vhat[tokA][16g + j], Vhat[tokB][16g + j])
 #pragma unroll
@@ -708,7 +714,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     p.scale_row_halves = Hkv * Gd;
     p.slot_bytes = (bits == 4 ? 2048 : 4096) + 256;
     int ctas_per_sm = tuning_get("attn.ctas_per_sm");
-    if (ctas_per_sm <= 0) ctas_per_sm = 2;
+    if (ctas_per_sm <= 0) ctas_per_sm = B200Q_ATTN_CTAS;
     // At least two pages per CTA (by the block table's capacity; the lengths live on the device): short
     // batches otherwise pay for partial results and their merge more than for the KV bytes.
     const int64_t pages_cap = (int64_t)B * max_blocks;
