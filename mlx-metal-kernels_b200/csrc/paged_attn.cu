@@ -718,7 +718,10 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     // At least two pages per CTA (by the block table's capacity; the lengths live on the device): short
     // batches otherwise pay for partial results and their merge more than for the KV bytes.
     const int64_t pages_cap = (int64_t)B * max_blocks;
-    p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(kMaxGrid, sm_count() * ctas_per_sm), (pages_cap + 1) / 2));
+    int min_pages = tuning_get("attn.min_pages");
+    if (min_pages <= 0) min_pages = 2;
+    p.grid = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(kMaxGrid, sm_count() * ctas_per_sm),
+                                                         (pages_cap + min_pages - 1) / min_pages));
     const int launch_grid = (p.grid + p.subs - 1) / p.subs;   // CTAs: each covers `subs` ranges
     const bool two = launch_grid > sm_count();
     const int stages = ring_depth(bits, two);

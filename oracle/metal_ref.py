@@ -107,6 +107,26 @@ def paged_attention(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, 
     return out
 
 
+def contiguous_attention(bits, q, k_codes, v_codes, k_scales, v_scales, lengths, cache_shape, group_size, scale):
+    """meta as in ops/quantized_kv_cache_ops.py:444-447 (q8) / :480-483 (q4); grid B*Hq."""
+    q = np.ascontiguousarray(q, dtype=np.float16)
+    B, _, Hq, D = q.shape
+    _, max_s, Hkv, _ = cache_shape
+    groups = (D + group_size - 1) // group_size
+    out = np.zeros_like(q)
+    ln = np.ascontiguousarray(lengths, dtype=np.int32)
+    sc = np.asarray([scale], dtype=np.float32)
+    args = [q, np.ascontiguousarray(k_codes, dtype=np.uint8), np.ascontiguousarray(v_codes, dtype=np.uint8),
+            _f32(k_scales), _f32(v_scales), ln]
+    if bits == 4:
+        meta = _i32(B, max_s, Hq, Hkv, D, (D + 1) // 2, group_size, groups)
+        _call(_get().ref_q4_attn_f16, *args, meta, sc, out, B * Hq)
+    else:
+        meta = _i32(B, max_s, Hq, Hkv, D, group_size, groups)
+        _call(_get().ref_q8_attn_f16, *args, meta, sc, out, B * Hq)
+    return out
+
+
 def fused_swiglu(gate, up):
     """meta as in ops/activation_ops.py:144."""
     gate = np.ascontiguousarray(gate, dtype=np.float16)

@@ -80,6 +80,21 @@ extern "C" void ref_q8_paged_attn_f16(const half* q, const uint8_t* K_pages_q, c
 #include "q8_paged_gqa_decode_attention.metal"
     GRID_END
 }
+// ---- kernels/q{4,8}_gqa_decode_attention.metal (contiguous cache) ----------------------------
+extern "C" void ref_q4_attn_f16(const half* q, const uint8_t* K_q, const uint8_t* V_q, const float* K_scales,
+                                const float* V_scales, const int* lengths, const int* meta, const float* scale,
+                                half* out, long long grid) {
+    GRID_BEGIN(grid)
+#include "q4_gqa_decode_attention.metal"
+    GRID_END
+}
+extern "C" void ref_q8_attn_f16(const half* q, const uint8_t* K_q, const uint8_t* V_q, const float* K_scales,
+                                const float* V_scales, const int* lengths, const int* meta, const float* scale,
+                                half* out, long long grid) {
+    GRID_BEGIN(grid)
+#include "q8_gqa_decode_attention.metal"
+    GRID_END
+}
 // ---- kernels/fused_swiglu.metal ------------------------------------------------------------
 extern "C" void ref_fused_swiglu_f16(const half* gate, const half* up, const int* meta, half* out,
                                      long long grid) {

@@ -120,6 +120,32 @@ def main():
     out["mtl_btl_table"], out["mtl_btl_pos"] = bt, pos
     out["mtl_btl_pages"], out["mtl_btl_offsets"] = metal_ref.block_table_lookup(bt, pos, 8)
 
+    # contiguous quantised cache attention: ragged lengths, G=32; its own generator so that the arrays above
+    # do not depend on what is added here
+    rng2 = np.random.default_rng(20240607)
+    for bits in (4, 8):
+        for tag, (B, Hq, Hkv, D, max_s, lengths) in {
+            "gqa": (3, 8, 2, 64, 24, [24, 7, 1]),
+            "mqa": (2, 4, 1, 128, 48, [33, 48]),
+            "d16": (1, 4, 4, 16, 13, [13]),
+        }.items():
+            G = 32
+            groups = (D + G - 1) // G
+            cols = (D + 1) // 2 if bits == 4 else D
+            kq = rng2.integers(0, 256, size=(B, max_s, Hkv, cols), dtype=np.uint8)
+            vq = rng2.integers(0, 256, size=(B, max_s, Hkv, cols), dtype=np.uint8)
+            smax = 7 if bits == 4 else 127
+            ks = (np.abs(rng2.standard_normal((B, max_s, Hkv, groups))) * 2.5 / smax + 1e-3).astype(np.float16)
+            vs = (np.abs(rng2.standard_normal((B, max_s, Hkv, groups))) * 2.5 / smax + 1e-3).astype(np.float16)
+            q = rng2.standard_normal((B, 1, Hq, D)).astype(np.float16)
+            scale = np.float32(1.0 / np.sqrt(D))
+            o = metal_ref.contiguous_attention(bits, q, kq, vq, ks, vs, np.asarray(lengths, np.int32),
+                                               (B, max_s, Hkv, D), G, float(scale))
+            key = f"mtl_cattn_q{bits}_{tag}"
+            for name, val in dict(q=q, kq=kq, vq=vq, ks=ks, vs=vs, lengths=np.asarray(lengths, np.int32),
+                                  shape=np.asarray((B, max_s, Hkv, D), np.int32), out=o).items():
+                out[f"{key}_{name}"] = val
+
     dest = Path(__file__).resolve().parent / "hotpath_golden.npz"
     np.savez_compressed(dest, **out)
     print(f"wrote {dest} ({dest.stat().st_size} bytes, {len(out)} arrays)")

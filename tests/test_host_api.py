@@ -6,8 +6,8 @@ import re
 import pytest
 import torch
 
-from helpers import act_ops, cabi, fused_ops, mlp_ops, norm_ops, pkv_ops, pq_ops, quant_ops, random_quant_case, synth
-from oracle import paged_quantized_kv_ops as opq, quant_ops as oq
+from helpers import act_ops, cabi, fused_ops, mlp_ops, norm_ops, pkv_ops, pq_ops, qkv_ops, quant_ops, random_quant_case, synth
+from oracle import paged_quantized_kv_ops as opq, quant_ops as oq, quantized_kv_cache_ops as ocq
 
 
 def test_library_exports_every_declared_symbol():
@@ -244,6 +244,71 @@ def test_paged_attention_validation_errors():
     no_shape = dataclasses.replace(cache, original_page_shape=None)
     with pytest.raises(ValueError, match="original_page_shape is required"):
         fn(q, no_shape, backend="metal_q8")
+
+
+def test_contiguous_quantized_cache_host_logic():
+    C = qkv_ops.QuantizedKVCacheConfig
+    assert dataclasses.asdict(C()) == dict(bits=8, group_size=32, symmetric=True, with_zeros=False,
+                                           scale_dtype="float16", layout="contiguous")
+    with pytest.raises(ValueError):
+        C(bits=5).validate()
+    with pytest.raises(ValueError):
+        C(group_size=0).validate()
+    with pytest.raises(NotImplementedError):
+        C(symmetric=False).validate()
+    with pytest.raises(NotImplementedError):
+        C(with_zeros=True).validate()
+    with pytest.raises(NotImplementedError):
+        C(layout="paged").validate()
+    # the quantiser is plain tensor code: it matches the oracle on CPU tensors, lengths mask included
+    torch.manual_seed(3)
+    K = torch.randn(2, 6, 2, 40).to(torch.float16)
+    V = torch.randn(2, 6, 2, 40).to(torch.float16)
+    for bits in (8, 4):
+        cache = qkv_ops.quantize_kv_cache(K, V, C(bits=bits, group_size=32), lengths=[6, 2])
+        ref = ocq.quantize_kv_cache(K, V, bits=bits, group_size=32, lengths=[6, 2])
+        assert torch.equal(cache.k_q, ref.k_q) and torch.equal(cache.v_scales, ref.v_scales)
+        dp = 20 if bits == 4 else 40
+        assert cache.shapes() == {"k_q": (2, 6, 2, dp), "v_q": (2, 6, 2, dp), "k_scales": (2, 6, 2, 2),
+                                  "v_scales": (2, 6, 2, 2), "original": (2, 6, 2, 40)}
+        assert cache.memory_bytes() == 2 * 2 * 6 * 2 * dp + 2 * 2 * 6 * 2 * 2 * 2
+        assert cache.compression_ratio() == (2 * 2 * 6 * 2 * 40 * 2) / cache.memory_bytes()
+        cache.validate()
+    with pytest.raises(ValueError, match="must match"):
+        qkv_ops.quantize_kv_cache(K, V[:1], C())
+    with pytest.raises(ValueError, match="4-D"):
+        qkv_ops.quantize_kv_cache(K[0], V[0], C())
+    with pytest.raises(ValueError, match="positions must be in"):
+        qkv_ops.quantize_kv_cache(K, V, C(), lengths=[7, 1])
+
+    q = torch.randn(2, 1, 4, 40).to(torch.float16)
+    fn = qkv_ops.quantized_kv_gqa_decode_attention
+    with pytest.raises(cabi.ReferenceBackendUnavailable):
+        fn(q, cache)                       # default backend is "reference", as in the reference
+    with pytest.raises(ValueError, match="requires bits=8"):
+        fn(q, cache, backend="metal_q8")
+    with pytest.raises(ValueError, match="backend must be one of"):
+        fn(q, cache, backend="metal")
+    with pytest.raises(ValueError, match=r"\[B,1,Hq,D\]"):
+        fn(q[:, 0], cache, backend="metal_q4")
+    with pytest.raises(ValueError, match="batch mismatch"):
+        fn(q[:1], cache, backend="metal_q4")
+    with pytest.raises(ValueError, match="head_dim mismatch"):
+        fn(q[..., :8], cache, backend="metal_q4")
+    with pytest.raises(ValueError, match="positions must be in"):
+        fn(q, cache, [7, 1], backend="metal_q4")
+    with pytest.raises(cabi.B200QError, match="no CPU route"):
+        fn(q, cache, backend="metal_q4")
+    with pytest.raises(cabi.ReferenceBackendUnavailable):
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, None)
+    with pytest.raises(NotImplementedError):
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, None, backend="metal_q4")
+    # the paged view shares the buffers: 16-token pages when MAX_S allows it, else one page per sequence
+    view = qkv_ops.as_paged_view(cache, torch.tensor([6, 2], dtype=torch.int32))
+    assert view.page_size == 6 and view.block_table.tolist() == [[0], [1]] and view.k_pages_q.data_ptr() == cache.k_q.data_ptr()
+    big = qkv_ops.quantize_kv_cache(torch.zeros(2, 32, 1, 16), torch.zeros(2, 32, 1, 16), C())
+    view = qkv_ops.as_paged_view(big, torch.tensor([32, 32], dtype=torch.int32))
+    assert view.page_size == 16 and view.block_table.tolist() == [[0, 1], [2, 3]] and view.original_page_shape == (4, 16, 1, 16)
 
 
 def test_block_table_lookup_host_checks():

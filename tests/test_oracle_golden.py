@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from oracle import elementwise_ops, paged_kv_ops, paged_quantized_kv_ops as pq, quant_ops as oq
+from oracle import quantized_kv_cache_ops as oc
 
 
 def t(a):
@@ -90,6 +91,37 @@ def test_paged_attention_matches_metal_kernel_body(golden, bits, tag):
     zero_rows = np.nonzero(g["lengths"] == 0)[0]
     for b in zero_rows:
         assert float(got[b].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("tag", ["gqa", "mqa", "d16"])
+def test_contiguous_attention_matches_metal_kernel_body(golden, bits, tag):
+    key = f"mtl_cattn_q{bits}_{tag}"
+    g = {n: golden[f"{key}_{n}"] for n in ("q", "kq", "vq", "ks", "vs", "lengths", "shape", "out")}
+    cache = oc.OracleQuantizedKV(k_q=t(g["kq"]), v_q=t(g["vq"]), k_scales=t(g["ks"]), v_scales=t(g["vs"]), bits=bits,
+                                 group_size=32, original_shape=tuple(int(v) for v in g["shape"]))
+    got = oc.reference_quantized_kv_gqa_decode_attention(t(g["q"]), cache, t(g["lengths"]))
+    # same bound as the paged pin: Metal keeps dequantised K/V in fp32, the MLX path rounds them to fp16
+    want = t(g["out"]).float()
+    assert bool(((got.float() - want).abs() <= 2e-3 + want.abs() * 2.0 ** -10).all())
+
+
+def test_contiguous_cache_quantiser_masks_past_the_length_and_round_trips():
+    gen = torch.Generator().manual_seed(5)
+    K = torch.randn((2, 9, 2, 48), generator=gen).to(torch.float16)
+    V = torch.randn((2, 9, 2, 48), generator=gen).to(torch.float16)
+    for bits, step in ((8, 127.0), (4, 7.0)):
+        cache = oc.quantize_kv_cache(K, V, bits=bits, group_size=32, lengths=[9, 4])
+        assert cache.k_q.shape == (2, 9, 2, 48 if bits == 8 else 24) and cache.k_scales.shape == (2, 9, 2, 2)
+        assert int(cache.k_q[1, 4:].max()) == 0 and float(cache.v_scales[1, 4:].abs().max()) == 0.0
+        Kd, Vd = oc.dequantize_kv_cache(cache)
+        # half a quantisation step of the group's scale, plus the fp16 roundings of scale and result
+        bound = K[0].float().abs().amax() / step * 0.5 * 1.01 + 2e-3
+        assert float((Kd[0].float() - K[0].float()).abs().max()) <= float(bound)
+        assert float(Kd[1, 4:].abs().max()) == 0.0      # code 0 with scale 0 dequantises to 0
+        # the same cache through the paged quantiser (one page per sequence) gives the same codes where valid
+        paged = pq.quantize_kv_pages(K, V, None, None, bits=bits, page_size=9, group_size=32)
+        assert torch.equal(paged.k_pages_q[0], cache.k_q[0]) and torch.equal(paged.v_scales[0], cache.v_scales[0])
 
 
 def test_swiglu_matches_metal_kernel_body(golden):
