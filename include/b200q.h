@@ -139,6 +139,22 @@ int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, cons
                            int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages, int max_blocks,
                            int group_size, float scale, int q_dtype, int scale_dtype, void* stream);
 
+/* The same attention restricted to a sliding window with optional attention sinks: of the valid tokens
+ * j < L = min(lengths[b], max_blocks*page_size) only j < sink_tokens and j >= L - window_size take part
+ * (the decode row of the reference's "sliding_window" / "sliding_window_sink" masks,
+ * build_sparse_attention_mask, ops/sparse_attention_ops.py:85-105, with the query at position L - 1).
+ * The reference has this over a quantized cache only as a pure-MLX scaffold
+ * (reference_sparse_paged_quantized_kv_gqa_decode_attention, ops/paged_quantized_kv_ops.py:669-714, and
+ * ops/quantized_kv_cache_ops.py:544-603, whose Metal backend raises NotImplementedError); here the split-KV
+ * kernel skips the pages that hold no attended position, so the cost follows sink_tokens + window_size, not
+ * the context length.  window_size must be > 0; sink_tokens >= 0.  Other arguments as above. */
+int b200q_paged_gqa_decode_window(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                  const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                  const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
+                                  int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages, int max_blocks,
+                                  int group_size, float scale, int q_dtype, int scale_dtype, int sink_tokens,
+                                  int window_size, void* stream);
+
 /* The same attention for callers that cannot allocate device memory at all.  (No counterpart in the
  * reference: its runtime allocates every kernel output itself.)  Some hosts of this library may not
  * call cudaMalloc: a plugin running inside another runtime's memory budget, a worker that must not

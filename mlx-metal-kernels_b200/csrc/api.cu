@@ -87,7 +87,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
                           const void* v_scales, const int32_t* block_table, const int32_t* lengths, void* out,
                           void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size,
                           int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
-                          int scale_dtype, cudaStream_t stream);
+                          int scale_dtype, int sink_tokens, int window_size, cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
 // dequant: out = cast(fp32(code - zero) * scale).  __fsub_rn / __fmul_rn keep the two roundings
@@ -413,7 +413,19 @@ int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, cons
                            int q_dtype, int scale_dtype, void* stream) {
     return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, workspace,
                                  workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
-                                 q_dtype, scale_dtype, (cudaStream_t)stream);
+                                 q_dtype, scale_dtype, 0, 0, (cudaStream_t)stream);
+}
+
+int b200q_paged_gqa_decode_window(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                  const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                  const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes, int B,
+                                  int Hq, int Hkv, int D, int page_size, int64_t num_pages, int max_blocks,
+                                  int group_size, float scale, int q_dtype, int scale_dtype, int sink_tokens,
+                                  int window_size, void* stream) {
+    if (window_size <= 0) return B200Q_ERR_BAD_ARG;
+    return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, workspace,
+                                 workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
+                                 q_dtype, scale_dtype, sink_tokens, window_size, (cudaStream_t)stream);
 }
 
 size_t b200q_paged_gqa_static_scratch_bytes(void) { return paged_gqa_static_scratch_bytes_impl(); }

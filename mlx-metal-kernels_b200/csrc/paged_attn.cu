@@ -69,10 +69,37 @@ struct AttnParams {
     int scale_row_halves;       // halves of one token row of scales, all kv heads
     uint32_t off_prefix, off_ring, slot_bytes;
     int grid;
+    int sink, window;           // window > 0: only positions < sink or >= length - window are attended
     TpOut tp_out;               // tensor-parallel exchange of the merged rows (world == 0: off)
 };
 
 __device__ __forceinline__ int clamp_len(int len, int cap) { return max(0, min(len, cap)); }
+
+// Pages of one sequence that hold at least one attended position.  Dense: all of them.  With a window: the
+// pages of the sink tokens that lie below the window, then the pages from the window's first position on.
+struct SeqPages { int n, sink_pages, first_recent, L; };
+__device__ __forceinline__ SeqPages seq_pages(int len, int cap, int P, int sink, int window) {
+    const int L = clamp_len(len, cap);
+    const int n_all = (L + P - 1) / P;
+    if (window <= 0 || L <= 0) return {n_all, n_all, n_all, L};
+    const int lo = max(0, L - window);
+    const int sink_pages = (min(sink, lo) + P - 1) / P;
+    const int first_recent = max(sink_pages, lo / P);
+    return {sink_pages + n_all - first_recent, sink_pages, first_recent, L};
+}
+// bit t set: slot t of page pg (16 slots) is an attended position of a sequence of L tokens
+__device__ __forceinline__ uint32_t page_mask16(int pg, int L, int sink, int window) {
+    const int valid = min(16, L - pg * 16);
+    uint32_t m = valid >= 16 ? 0xFFFFu : ((1u << max(valid, 0)) - 1u);
+    if (window > 0) {
+        const int lo_t = max(0, L - window) - pg * 16;      // first slot of the window in this page
+        const int sink_t = sink - pg * 16;                    // slots below this are sink tokens
+        const uint32_t recent = lo_t <= 0 ? 0xFFFFu : (lo_t >= 16 ? 0u : (0xFFFFu << lo_t) & 0xFFFFu);
+        const uint32_t sinks = sink_t <= 0 ? 0u : (sink_t >= 16 ? 0xFFFFu : (1u << sink_t) - 1u);
+        m &= recent | sinks;
+    }
+    return m;
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
@@ -97,7 +124,7 @@ __device__ int build_prefix(const AttnParams& p, int* prefix) {
         for (int b0 = 0; b0 < p.B; b0 += 32) {
             const int b = b0 + lane;
             int n = 0;
-            if (b < p.B) n = (clamp_len(p.lengths[b], p.max_blocks * p.P) + p.P - 1) / p.P;
+            if (b < p.B) n = seq_pages(p.lengths[b], p.max_blocks * p.P, p.P, p.sink, p.window).n;
             int incl = n;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -178,19 +205,22 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
 
     // Page descriptors (page id, sequence, valid tokens) of 32 consecutive pages of this warp, one per
     // lane.  Two windows: one for the page being consumed, one for the page being issued ahead.
-    struct Desc { int page, b, valid; };
+    struct Desc { int page, b, valid; };      // valid: token count | attended-slot mask << 16
     auto lookup = [&](int base) -> Desc {
         const int j = base + lane;
         Desc d = {-1, 0, 0};
         if (j < n_my) {
             const int f = lo + j;
             const int b = find_sequence(prefix, p.B, f);
-            const int pg = f - prefix[b];
+            const SeqPages sp = seq_pages(p.lengths[b], p.max_blocks * p.P, p.P, p.sink, p.window);
+            const int idx = f - prefix[b];
+            const int pg = idx < sp.sink_pages ? idx : sp.first_recent + (idx - sp.sink_pages);
             int page = p.block_table[(int64_t)b * p.max_blocks + pg];
             if (page < 0 || page >= p.num_pages) page = -1;
             d.page = page;
             d.b = b;
-            d.valid = min(p.P, clamp_len(p.lengths[b], p.max_blocks * p.P) - pg * p.P);
+            // low half: tokens of the page below the length (what is copied); high half: attended slots
+            d.valid = min(p.P, sp.L - pg * p.P) | (int)(page_mask16(pg, sp.L, p.sink, p.window) << 16);
         }
         return d;
     };
@@ -215,7 +245,7 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
         if (j > 0 && (j & 31) == 0) win_i = lookup(j);
         const int src_lane = j & 31;
         const int page = __shfl_sync(0xffffffffu, win_i.page, src_lane);
-        const int valid = __shfl_sync(0xffffffffu, win_i.valid, src_lane);
+        const int valid = __shfl_sync(0xffffffffu, win_i.valid, src_lane) & 0xFFFF;
         if (page >= 0) {
             uint8_t* slot = my_ring + slot_i * SLOT;
             const uint8_t* kbase = p.k_codes + (size_t)page * page_code_bytes;
@@ -294,7 +324,9 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
         if (j > 0 && (j & 31) == 0) win_c = lookup(j);
         const int page = __shfl_sync(0xffffffffu, win_c.page, j & 31);
         const int b = __shfl_sync(0xffffffffu, win_c.b, j & 31);
-        const int valid = __shfl_sync(0xffffffffu, win_c.valid, j & 31);
+        const uint32_t valid_mask = (uint32_t)__shfl_sync(0xffffffffu, win_c.valid, j & 31);
+        const int valid = (int)(valid_mask & 0xFFFFu);
+        const uint32_t attended = valid_mask >> 16;
         // look-ahead: copies of page j + NS - 1 (an empty group keeps the count uniform at the end)
         if (j + NS - 1 < n_my) issue(j + NS - 1);
         else cp_async_commit();
@@ -381,7 +413,8 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
             float alpha[2];
             uint32_t pb0, pb1;      // P[token][head] as the B operand of O^T += V^T P
             {
-                const bool in0 = g < valid, in1 = g + 8 < valid;   // also discards whatever stale bytes sit in unused slots
+                // also discards whatever stale bytes sit in unused slots
+                const bool in0 = (attended >> g) & 1u, in1 = (attended >> (g + 8)) & 1u;
                 s[0] = in0 ? s[0] * sm_scale : -INFINITY;
                 s[1] = in0 ? s[1] * sm_scale : -INFINITY;
                 s[2] = in1 ? s[2] * sm_scale : -INFINITY;
@@ -494,7 +527,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
     const int cap = p.max_blocks * p.P;
     int below = 0, all = 0;
     for (int i = threadIdx.x; i < p.B; i += kMergeWarps * 32) {
-        const int n = (clamp_len(p.lengths[i], cap) + p.P - 1) / p.P;
+        const int n = seq_pages(p.lengths[i], cap, p.P, p.sink, p.window).n;
         all += n;
         if (i < b) below += n;
     }
@@ -510,7 +543,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
     for (int w = 0; w < kMergeWarps; ++w) { below += red_i[0][w]; all += red_i[1][w]; }
     const int total = all;
     const int s_lo = below;
-    const int s_hi = below + (clamp_len(p.lengths[b], cap) + p.P - 1) / p.P;
+    const int s_hi = below + seq_pages(p.lengths[b], cap, p.P, p.sink, p.window).n;
     const int ppc = (total + p.grid - 1) / p.grid;
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -589,6 +622,7 @@ struct SimpleParams {
     int B, Hq, Hkv, D, P, max_blocks, G, Gd, bits, q_dtype, scale_dtype;
     int64_t num_pages;
     float scale;
+    int sink, window;
 };
 
 __global__ void __launch_bounds__(128) paged_attn_simple_kernel(const __grid_constant__ SimpleParams p) {
@@ -609,6 +643,7 @@ __global__ void __launch_bounds__(128) paged_attn_simple_kernel(const __grid_con
     float m = -INFINITY, l = 0.0f;
     const float off = p.bits == 4 ? 8.0f : 128.0f;
     for (int j = 0; j < L; ++j) {
+        if (p.window > 0 && j >= p.sink && j < L - p.window) continue;     // outside sink and window
         const int page = p.block_table[(int64_t)b * p.max_blocks + j / p.P];
         if (page < 0 || page >= p.num_pages) continue;
         const int64_t tok = ((int64_t)page * p.P + (j % p.P)) * p.Hkv + hkv;
@@ -672,14 +707,15 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
                           const void* v_scales, const int32_t* block_table, const int32_t* lengths, void* out,
                           void* workspace, size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size,
                           int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
-                          int scale_dtype, cudaStream_t stream) {
+                          int scale_dtype, int sink_tokens, int window_size, cudaStream_t stream) {
     int tp_in_slot = -1, tp_out_slot = -1;
     tp_take(&tp_in_slot, &tp_out_slot);
     if ((bits != 4 && bits != 8) || q == nullptr || k_codes == nullptr || v_codes == nullptr || k_scales == nullptr ||
         v_scales == nullptr || block_table == nullptr || lengths == nullptr || (out == nullptr && tp_out_slot < 0))
         return B200Q_ERR_BAD_ARG;
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
-        group_size <= 0 || Hq % Hkv != 0 || !is_act_dtype(q_dtype) || !is_scale_dtype(scale_dtype))
+        group_size <= 0 || Hq % Hkv != 0 || !is_act_dtype(q_dtype) || !is_scale_dtype(scale_dtype) ||
+        sink_tokens < 0 || window_size < 0)
         return B200Q_ERR_BAD_ARG;
     if (D > 128) return B200Q_ERR_UNSUPPORTED;
     const int Gd = (D + group_size - 1) / group_size;
@@ -695,7 +731,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     if (!fast_ok) {
         SimpleParams sp = {q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out,
                            B, Hq, Hkv, D, page_size, max_blocks, group_size, Gd, bits, q_dtype, scale_dtype,
-                           num_pages, scale};
+                           num_pages, scale, sink_tokens, window_size};
         const int warps = 4;
         paged_attn_simple_kernel<<<(B * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(sp);
         return finish_launch();
@@ -710,6 +746,8 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.P = page_size; p.max_blocks = max_blocks; p.G = group_size; p.Gd = Gd;
     p.group = group; p.num_pages = num_pages; p.scale = scale; p.q_dtype = q_dtype; p.bits = bits;
     p.subs = subs_for(Hkv);
+    p.sink = sink_tokens;
+    p.window = window_size;
     p.row_bytes = Hkv * dp;
     p.scale_row_halves = Hkv * Gd;
     p.slot_bytes = (bits == 4 ? 2048 : 4096) + 256;
@@ -814,7 +852,7 @@ int paged_gqa_decode_static_impl(int bits, const void* q, const uint8_t* k_codes
     }
     return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, ptr,
                                  kStaticScratchBytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
-                                 q_dtype, scale_dtype, stream);
+                                 q_dtype, scale_dtype, 0, 0, stream);
 }
 
 }  // namespace b200q

@@ -48,6 +48,8 @@ SIGNATURES = {
                                            _f, _i, _i, _vp]),
     "b200q_paged_gqa_decode": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64,
                                     _i, _i, _f, _i, _i, _vp]),
+    "b200q_paged_gqa_decode_window": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64,
+                                           _i, _i, _f, _i, _i, _i, _i, _vp]),
 }
 
 _lib = None

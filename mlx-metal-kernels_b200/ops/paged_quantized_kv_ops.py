@@ -17,6 +17,7 @@ import torch
 from . import _cabi
 from .gqa_ops import validate_gqa_heads
 from .quant_ops import dequant_codes, pack_q4
+from .sparse_attention_ops import decode_window
 
 _MAX_HEAD_DIM = 128
 
@@ -130,7 +131,10 @@ def _quantize_groups(values: torch.Tensor, bits: int, group_size: int):
     if pad:
         v = torch.nn.functional.pad(v, (0, pad))
     v = v.reshape(*values.shape[:-1], groups, group_size)
-    scale = v.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8) / float(limit)
+    max_abs = v.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8)
+    # a tensor divisor: dividing by a Python scalar multiplies by its reciprocal on CUDA, which is not the
+    # reference's correctly rounded max_abs / limit in the last bit
+    scale = max_abs / torch.full_like(max_abs, float(limit))
     codes = (torch.round(v / scale).clamp(-limit, limit) + offset).to(torch.uint8)
     codes = codes.reshape(*values.shape[:-1], groups * group_size)[..., :D]
     return codes, scale.squeeze(-1).to(torch.float16)
@@ -276,8 +280,9 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
-def paged_attention_launch(q3d, paged_qkv, scale, out=None, workspace=None):
-    """q3d [B,Hq,D] -> [B,Hq,D]; all tensors already on one CUDA device."""
+def paged_attention_launch(q3d, paged_qkv, scale, out=None, workspace=None, *, sink_tokens: int = 0, window_size: int = 0):
+    """q3d [B,Hq,D] -> [B,Hq,D]; all tensors already on one CUDA device.  ``window_size > 0`` restricts the
+    attention to positions ``< sink_tokens`` or ``>= length - window_size``."""
     B, Hq, D = q3d.shape
     NUM_PAGES, PAGE_SIZE, Hkv, _ = paged_qkv.original_page_shape
     MAX_BLOCKS = paged_qkv.block_table.shape[1]
@@ -295,14 +300,14 @@ def paged_attention_launch(q3d, paged_qkv, scale, out=None, workspace=None):
     nbytes = lib.b200q_paged_gqa_workspace_bytes(B, Hq, Hkv, D)
     if workspace is None:
         workspace = _workspace(q3d.device, nbytes)
-    _cabi.check(
-        lib.b200q_paged_gqa_decode(paged_qkv.bits, q3d.data_ptr(), kq.data_ptr(), vq.data_ptr(), ks.data_ptr(),
-                                   vs.data_ptr(), bt.data_ptr(), ln.data_ptr(), out.data_ptr(), workspace.data_ptr(),
-                                   workspace.numel(), B, Hq, Hkv, D, PAGE_SIZE, NUM_PAGES, MAX_BLOCKS,
-                                   paged_qkv.group_size, float(scale), _cabi.dtype_code(q3d.dtype),
-                                   _cabi.dtype_code(ks.dtype), _cabi.stream()),
-        "b200q_paged_gqa_decode",
-    )
+    args = (paged_qkv.bits, q3d.data_ptr(), kq.data_ptr(), vq.data_ptr(), ks.data_ptr(), vs.data_ptr(), bt.data_ptr(),
+            ln.data_ptr(), out.data_ptr(), workspace.data_ptr(), workspace.numel(), B, Hq, Hkv, D, PAGE_SIZE, NUM_PAGES,
+            MAX_BLOCKS, paged_qkv.group_size, float(scale), _cabi.dtype_code(q3d.dtype), _cabi.dtype_code(ks.dtype))
+    if window_size > 0:
+        _cabi.check(lib.b200q_paged_gqa_decode_window(*args, int(sink_tokens), int(window_size), _cabi.stream()),
+                    "b200q_paged_gqa_decode_window")
+    else:
+        _cabi.check(lib.b200q_paged_gqa_decode(*args, _cabi.stream()), "b200q_paged_gqa_decode")
     return out
 
 
@@ -341,4 +346,30 @@ def paged_quantized_kv_gqa_decode_attention(q, paged_qkv: PagedQuantizedKVCache,
     _cabi.require_cuda(q, paged_qkv.k_pages_q, paged_qkv.v_pages_q, paged_qkv.k_scales, paged_qkv.v_scales,
                        paged_qkv.block_table, paged_qkv.lengths)
     out = paged_attention_launch(q.reshape(B, Hq, D), paged_qkv, scale)
+    return out.reshape(B, 1, Hq, D)
+
+
+def sparse_paged_quantized_kv_gqa_decode_attention(q, paged_qkv: PagedQuantizedKVCache, pattern, *,
+                                                   scale: float | None = None, backend: str = "cuda"):
+    """Sliding-window (+ attention sink) decode over the paged quantized cache: q [B,1,Hq,D] -> [B,1,Hq,D].
+    The reference has this as a pure-MLX scaffold only (reference_sparse_paged_quantized_kv_gqa_decode_attention,
+    ops/paged_quantized_kv_ops.py:669-714); ``backend="reference"`` raises here like every reference path.
+    ``pattern`` is a ``SparseAttentionPattern`` (dense, sliding_window, sliding_window_sink); every sequence
+    needs at least one token, as in the reference."""
+    sink_tokens, window_size = decode_window(pattern)
+    B, MAX_S, PAGE_SIZE, MAX_BLOCKS, Hq, Hkv, D, NUM_PAGES = _validate_paged_quantized_decode_inputs(q, paged_qkv)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    name = backend.lower()
+    if name == "reference":
+        _cabi.reference_unavailable("sparse_paged_quantized_kv_gqa_decode_attention")
+    if name not in ("cuda", "auto"):
+        raise ValueError(f"backend must be one of 'reference', 'cuda', got {name!r}")
+    if D > _MAX_HEAD_DIM:
+        raise ValueError(f"{name} backend supports D <= {_MAX_HEAD_DIM}, got D={D}")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"q dtype must be float16 or bfloat16, got {q.dtype}")
+    _cabi.require_cuda(q, paged_qkv.k_pages_q, paged_qkv.v_pages_q, paged_qkv.k_scales, paged_qkv.v_scales,
+                       paged_qkv.block_table, paged_qkv.lengths)
+    out = paged_attention_launch(q.reshape(B, Hq, D), paged_qkv, scale, sink_tokens=sink_tokens, window_size=window_size)
     return out.reshape(B, 1, Hq, D)

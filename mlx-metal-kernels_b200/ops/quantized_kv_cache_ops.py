@@ -23,6 +23,7 @@ from .gqa_ops import validate_gqa_heads
 from .paged_kv_ops import normalize_positions
 from .paged_quantized_kv_ops import PagedQuantizedKVCache, _quantize_groups, paged_attention_launch
 from .quant_ops import dequant_codes, pack_q4
+from .sparse_attention_ops import SparseAttentionPattern, decode_window
 
 _MAX_HEAD_DIM = 128
 _FAST_PAGE = 16
@@ -264,17 +265,36 @@ def quantized_kv_gqa_decode_attention(q, qkv_cache: QuantizedKVCache, lengths=No
 
 
 # ---------------------------------------------------------------------------------------------
-# sparse decode over a quantised cache: reference-only scaffold in the reference, not built here
+# sliding-window (+ sink) decode over a quantised cache
 # ---------------------------------------------------------------------------------------------
 def reference_quantized_kv_sparse_gqa_decode_attention(q, qkv_cache, lengths, pattern, *, scale=None):
     _cabi.reference_unavailable("reference_quantized_kv_sparse_gqa_decode_attention")
 
 
 def quantized_kv_sparse_gqa_decode_attention(q, qkv_cache, lengths, pattern, *, scale=None, backend: str = "reference"):
-    """The reference offers this with ``backend="reference"`` only (ops/quantized_kv_cache_ops.py:586-603)."""
-    if backend.lower() == "reference":
+    """The reference offers this with ``backend="reference"`` only; its Metal backends raise NotImplementedError
+    (ops/quantized_kv_cache_ops.py:586-603), and so do the Metal names here.  ``backend="cuda"`` runs the dense,
+    sliding_window and sliding_window_sink patterns on the split-KV kernels, which skip the pages outside the
+    window."""
+    if not isinstance(pattern, SparseAttentionPattern):
+        raise TypeError("pattern must be a SparseAttentionPattern")
+    name = backend.lower()
+    if name == "reference":
         _cabi.reference_unavailable("quantized_kv_sparse_gqa_decode_attention")
-    raise NotImplementedError(
-        "Metal sparse+quantized backend is not implemented yet. "
-        "Use backend='reference' or see sparse+gqa decode attention for fp16."
-    )
+    if name not in ("cuda", "auto"):
+        raise NotImplementedError(
+            "Metal sparse+quantized backend is not implemented yet. "
+            "Use backend='reference' or see sparse+gqa decode attention for fp16."
+        )
+    sink_tokens, window_size = decode_window(pattern)
+    lengths_arr, B, MAX_S, Hq, Hkv, D = _validate_quantized_decode_inputs(q, qkv_cache, lengths)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if D > _MAX_HEAD_DIM:
+        raise ValueError(f"{name} backend supports D <= {_MAX_HEAD_DIM}, got D={D}")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"q dtype must be float16 or bfloat16, got {q.dtype}")
+    _cabi.require_cuda(q, qkv_cache.k_q, qkv_cache.v_q, qkv_cache.k_scales, qkv_cache.v_scales)
+    out = paged_attention_launch(q.reshape(B, Hq, D), as_paged_view(qkv_cache, lengths_arr), scale,
+                                 sink_tokens=sink_tokens, window_size=window_size)
+    return out.reshape(B, 1, Hq, D)

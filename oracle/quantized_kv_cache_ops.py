@@ -91,11 +91,15 @@ def dequantize_kv_cache(cache):
             _dequant(cache.v_q, cache.v_scales, cache.bits, cache.group_size, shape))
 
 
-def reference_quantized_kv_gqa_decode_attention(q, cache, lengths=None, *, scale=None):
+def reference_quantized_kv_gqa_decode_attention(q, cache, lengths=None, *, scale=None, window=None):
     """ops/quantized_kv_cache_ops.py:348-406: K and V dequantised and rounded to fp16, scores in
     fp32, positions at or past the length get -1e9 before the softmax over all MAX_S positions,
     result cast to q.dtype.  (With one valid token or more the masked terms are exactly 0 in fp32,
-    so this is the softmax over the valid tokens; a length of 0 averages all MAX_S positions.)"""
+    so this is the softmax over the valid tokens; a length of 0 averages all MAX_S positions.)
+
+    ``window=(sink, recent)`` keeps only the first ``sink`` and the last ``recent`` valid positions: the decode
+    row of the sliding_window(_sink) masks that reference_quantized_kv_sparse_gqa_decode_attention applies
+    (ops/quantized_kv_cache_ops.py:544-583); ``None`` means dense."""
     if q.ndim != 4:
         raise ValueError(f"q must be 4-D [B,1,Hq,D], got {tuple(q.shape)}")
     if q.shape[1] != 1:
@@ -117,6 +121,10 @@ def reference_quantized_kv_gqa_decode_attention(q, cache, lengths=None, *, scale
     qg = qf[:, 0].reshape(B, Hkv, group, D)
     scores = torch.einsum("bhgd,bshd->bhgs", qg, Kf) * float(scale)
     valid = (torch.arange(MAX_S).reshape(1, 1, 1, MAX_S) < lengths_arr.reshape(B, 1, 1, 1))
+    if window is not None:
+        sink, recent = window
+        pos = torch.arange(MAX_S).reshape(1, 1, 1, MAX_S)
+        valid = valid & ((pos < sink) | (pos >= (lengths_arr - recent).reshape(B, 1, 1, 1)))
     scores = torch.where(valid, scores, torch.full_like(scores, -1.0e9))
     probs = torch.softmax(scores, dim=-1)
     out = torch.einsum("bhgs,bshd->bhgd", probs, Vf).reshape(B, 1, Hq, D)

@@ -15,6 +15,7 @@ mlp_ops = importlib.import_module("mlx_metal_kernels_b200.ops.mlp_block_ops")
 pq_ops = importlib.import_module("mlx_metal_kernels_b200.ops.paged_quantized_kv_ops")
 qkv_ops = importlib.import_module("mlx_metal_kernels_b200.ops.quantized_kv_cache_ops")
 pkv_ops = importlib.import_module("mlx_metal_kernels_b200.ops.paged_kv_ops")
+sparse_ops = importlib.import_module("mlx_metal_kernels_b200.ops.sparse_attention_ops")
 act_ops = importlib.import_module("mlx_metal_kernels_b200.ops.activation_ops")
 norm_ops = importlib.import_module("mlx_metal_kernels_b200.ops.norm_ops")
 fused_ops = importlib.import_module("mlx_metal_kernels_b200.ops.fused_ops")

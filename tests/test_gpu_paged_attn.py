@@ -1,6 +1,7 @@
 """GPU parity: q4/q8 paged-KV GQA decode attention and the block-table gather against the CPU
 oracle.  Bound: max |out - oracle| <= 2e-3 in fp16 (K/V ~ N(0,1))."""
 import dataclasses
+import importlib
 
 import numpy as np
 import pytest
@@ -160,3 +161,27 @@ def test_block_table_lookup_exact(cuda, golden, B, MAX_S, P, pos):
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
     fp, fo = pkv_ops.block_table_lookup(t(golden["mtl_btl_table"]).to(cuda), t(golden["mtl_btl_pos"]).to(cuda), 8)
     assert torch.equal(fp.cpu(), t(golden["mtl_btl_pages"])) and torch.equal(fo.cpu(), t(golden["mtl_btl_offsets"]))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("sink,window", [(0, 16), (4, 32), (20, 5), (3, 1), (40, 100), (0, 4096), (16, 16)])
+@pytest.mark.parametrize("Hq,Hkv,D,P", [(8, 2, 128, 16), (32, 8, 128, 16), (6, 3, 64, 8)])
+def test_sliding_window_and_sinks_match_oracle(cuda, bits, sink, window, Hq, Hkv, D, P):
+    """The split-KV kernel walks only the pages that hold an attended position (first shapes); other shapes run
+    the general kernel with the same position filter.  Lengths straddle the window, the sink count and page
+    boundaries."""
+    sparse_ops = importlib.import_module("mlx_metal_kernels_b200.ops.sparse_attention_ops")
+    lengths = [1, 15, 16, 17, 37, 200, 333]
+    case = _case_with_lengths(lengths, Hkv, D, P, bits, 32, seed=300 + sink + window)
+    q = synth.activations((len(lengths), 1, Hq, D), 71)
+    want = opq.reference_paged_quantized_kv_gqa_decode_attention(q, _oracle_cache(case), window=(sink, window))
+    name = "sliding_window_sink" if sink else "sliding_window"
+    pattern = sparse_ops.SparseAttentionPattern(name, window_size=window, sink_tokens=sink)
+    got = pq_ops.sparse_paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), pattern)
+    err = float((got.cpu().float() - want.float()).abs().max())
+    assert err <= ATOL, err
+    # a window that covers everything is the dense result, bit for bit (same kernel, same page walk)
+    if window >= max(lengths):
+        dense = pq_ops.paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), backend="cuda")
+        assert torch.equal(got, dense)
+    assert cabi.device_status() == 0

@@ -98,3 +98,18 @@ def test_zero_length_sequence_gives_zeros(cuda):
     assert float(got[0].abs().max()) == 0.0
     want = oc.reference_quantized_kv_gqa_decode_attention(q, cache, [0, 32])
     assert float((got[1].cpu().float() - want[1].float()).abs().max()) <= ATOL
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("MAX_S,lengths,sink,window", [(128, [128, 45], 4, 32), (128, [77, 128], 0, 16), (50, [50, 9], 2, 8)])
+def test_sliding_window_decode_matches_oracle(cuda, bits, MAX_S, lengths, sink, window):
+    from helpers import sparse_ops
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    cache = oc.quantize_kv_cache(_randn((B, MAX_S, Hkv, D), 51), _randn((B, MAX_S, Hkv, D), 52), bits=bits, group_size=32)
+    q = _randn((B, 1, Hq, D), 53)
+    want = oc.reference_quantized_kv_gqa_decode_attention(q, cache, lengths, window=(sink, window))
+    pattern = sparse_ops.SparseAttentionPattern("sliding_window_sink" if sink else "sliding_window", window_size=window,
+                                                sink_tokens=sink)
+    got = qkv_ops.quantized_kv_sparse_gqa_decode_attention(q.to(cuda), _to_device(cache, cuda), lengths, pattern,
+                                                           backend="cuda")
+    assert float((got.cpu().float() - want.float()).abs().max()) <= ATOL

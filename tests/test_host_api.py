@@ -6,8 +6,10 @@ import re
 import pytest
 import torch
 
-from helpers import act_ops, cabi, fused_ops, mlp_ops, norm_ops, pkv_ops, pq_ops, qkv_ops, quant_ops, random_quant_case, synth
+from helpers import (act_ops, cabi, fused_ops, mlp_ops, norm_ops, pkv_ops, pq_ops, qkv_ops, quant_ops, random_quant_case,
+                     sparse_ops, synth)
 from oracle import paged_quantized_kv_ops as opq, quant_ops as oq, quantized_kv_cache_ops as ocq
+from oracle import sparse_attention_ops as osparse
 
 
 def test_library_exports_every_declared_symbol():
@@ -299,10 +301,36 @@ def test_contiguous_quantized_cache_host_logic():
         fn(q, cache, [7, 1], backend="metal_q4")
     with pytest.raises(cabi.B200QError, match="no CPU route"):
         fn(q, cache, backend="metal_q4")
-    with pytest.raises(cabi.ReferenceBackendUnavailable):
+    P = sparse_ops.SparseAttentionPattern
+    with pytest.raises(TypeError, match="SparseAttentionPattern"):
         qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, None)
+    with pytest.raises(cabi.ReferenceBackendUnavailable):
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("dense"))
     with pytest.raises(NotImplementedError):
-        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, None, backend="metal_q4")
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("dense"), backend="metal_q4")
+    with pytest.raises(NotImplementedError, match="block_sparse"):
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("block_sparse", block_size=4, block_mask=[[1]]),
+                                                         backend="cuda")
+    with pytest.raises(ValueError, match="window_size > 0"):
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("sliding_window"), backend="cuda")
+    with pytest.raises(cabi.B200QError, match="no CPU route"):
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("sliding_window", window_size=3), backend="cuda")
+    assert sparse_ops.decode_window(P("dense")) == (0, 0)
+    assert sparse_ops.decode_window(P("sliding_window", window_size=5, sink_tokens=2)) == (0, 5)
+    assert sparse_ops.decode_window(P("sliding_window_sink", window_size=5, sink_tokens=2)) == (2, 5)
+    with pytest.raises(ValueError, match="sink_tokens"):
+        P("sliding_window_sink", window_size=5, sink_tokens=-1).validate()
+    with pytest.raises(ValueError, match="pattern must be one of"):
+        P("strided").validate()
+    # the (sink, window) pair is the decode row of the reference's mask builder
+    for L in (1, 2, 7, 16, 33):
+        for W in (1, 3, 16, 40):
+            for S in (0, 1, 5):
+                pos = torch.arange(L)
+                assert torch.equal(osparse.decode_row(L, "sliding_window_sink", window_size=W, sink_tokens=S),
+                                   (pos < S) | (pos >= L - W))
+                assert torch.equal(osparse.decode_row(L, "sliding_window", window_size=W, sink_tokens=S), pos >= L - W)
+        assert bool(osparse.decode_row(L, "dense").all())
     # the paged view shares the buffers: 16-token pages when MAX_S allows it, else one page per sequence
     view = qkv_ops.as_paged_view(cache, torch.tensor([6, 2], dtype=torch.int32))
     assert view.page_size == 6 and view.block_table.tolist() == [[0], [1]] and view.k_pages_q.data_ptr() == cache.k_q.data_ptr()
