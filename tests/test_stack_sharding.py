@@ -1,4 +1,4 @@
-"""Host-side logic of the tensor-parallel decode stack on CPU: two gloo ranks shard one layer with
+"""Host-side logic of the tensor-parallel decode stack on CPU: two (and four) gloo ranks shard one layer with
 ``shard_layer``, run the layer with the oracle's per-op functions on their shards, re-assemble the
 activations with the stack's own ``_all_gather_rows`` and must reproduce the unsharded oracle layer."""
 import importlib
@@ -13,7 +13,6 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-WORLD = 2
 
 
 def _free_port():
@@ -23,7 +22,7 @@ def _free_port():
 
 
 def _tiny(stack_mod):
-    cfg = stack_mod.StackConfig(hidden=256, intermediate=512, n_layers=1, n_heads=4, n_kv_heads=2, head_dim=64,
+    cfg = stack_mod.StackConfig(hidden=512, intermediate=1024, n_layers=1, n_heads=8, n_kv_heads=4, head_dim=64,
                                 vocab=31, bits=4, group_size=64, kv_bits=8, kv_group_size=32)
     layer = stack_mod.random_layer(cfg, 7, "cpu")
     gen = torch.Generator().manual_seed(5)
@@ -56,7 +55,7 @@ def _slice_heads(cache, lo, hi):
                              group_size=cache.group_size, original_page_shape=(n, P, hi - lo, D))
 
 
-def _rank_main(rank, port, result_path):
+def _rank_main(rank, WORLD, port, result_path):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -119,9 +118,10 @@ def _rank_main(rank, port, result_path):
         dist.destroy_process_group()
 
 
-def test_two_rank_sharded_layer_matches_unsharded(tmp_path):
+@pytest.mark.parametrize("WORLD", [2, 4])
+def test_sharded_layer_matches_unsharded(tmp_path, WORLD):
     result = str(tmp_path / "result.pt")
-    mp.spawn(_rank_main, args=(_free_port(), result), nprocs=WORLD, join=True)
+    mp.spawn(_rank_main, args=(WORLD, _free_port(), result), nprocs=WORLD, join=True)
     rows = torch.load(result)
     assert len(rows) == WORLD
     for err, ref, ok_shapes in rows:
