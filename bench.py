@@ -218,6 +218,16 @@ def kernel_microbenchmarks(device, peak, all_configs=False, cpu=False):
         qc = qq.cpu()
         cpu_fn = lambda: opq.reference_paged_quantized_kv_gqa_decode_attention(qc, ocache)
     record("c4_q4_paged_gqa_decode_b16_h32_kv8_d128_p16", sec, nbytes, R, extra={"sum_lengths": total}, cpu_fn=cpu_fn)
+    if all_configs:
+        # the same caches through the sliding-window entry point (4 sink tokens + the last 1024): the kernel walks
+        # only the pages that hold an attended position, so bytes and time follow the window, not the context
+        sparse = importlib.import_module(f"{entry.PKG_ALIAS}.ops.sparse_attention_ops")
+        pattern = sparse.SparseAttentionPattern("sliding_window_sink", window_size=1024, sink_tokens=4)
+        attended = int(torch.clamp(case["lengths"], max=1024 + 4).sum())
+        wbytes = attended * 8 * 144 + 16 * 66 * 4 + 2 * 16 * 32 * 128 * 2
+        sec = _time_graph(lambda: [pq.sparse_paged_quantized_kv_gqa_decode_attention(qq, c, pattern) for c in caches],
+                          10, stream) / R
+        record("c4_window1024_sink4_q4_paged_gqa_decode_b16", sec, wbytes, R, extra={"attended_tokens": attended})
     del caches
     torch.cuda.empty_cache()
     return out
