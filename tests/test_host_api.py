@@ -388,3 +388,48 @@ def test_c_abi_rejects_bad_arguments_before_touching_a_device():
     assert lib.b200q_peer_allgather(16, ptrs, ptrs, 16, 0, 9, 1, 32, None) == bad                 # world > 8
     assert lib.b200q_peer_allgather(16, ptrs, ptrs, 16, 0, 2, 1, 24, None) == unsupported         # rows of 24 bytes
     assert b"scratch" in lib.b200q_strerror(-6)
+
+
+def test_window_page_walk_covers_exactly_the_attended_positions():
+    """The rule by which the split-KV attention kernel lists the pages of a sequence under a sliding window
+    (csrc/paged_attn.cu: seq_pages, page_mask16), restated on the host: the listed pages are strictly increasing,
+    each holds at least one attended slot, and the union of their slot masks is the decode row of the reference's
+    mask builder."""
+    P = 16
+
+    def seq_pages(L, sink, window):
+        n_all = (L + P - 1) // P
+        if window <= 0 or L <= 0:
+            return n_all, n_all, n_all
+        lo = max(0, L - window)
+        sink_pages = (min(sink, lo) + P - 1) // P
+        first_recent = max(sink_pages, lo // P)
+        return sink_pages + n_all - first_recent, sink_pages, first_recent
+
+    def page_mask(pg, L, sink, window):
+        valid = min(16, L - pg * 16)
+        m = (1 << max(valid, 0)) - 1
+        if window > 0:
+            lo_t = max(0, L - window) - pg * 16
+            sink_t = sink - pg * 16
+            recent = 0xFFFF if lo_t <= 0 else (0 if lo_t >= 16 else (0xFFFF << lo_t) & 0xFFFF)
+            sinks = 0 if sink_t <= 0 else (0xFFFF if sink_t >= 16 else (1 << sink_t) - 1)
+            m &= recent | sinks
+        return m
+
+    for L in (1, 2, 15, 16, 17, 31, 32, 33, 100, 257):
+        for sink in (0, 1, 4, 16, 20, 300):
+            for window in (1, 5, 16, 17, 64, 1000):
+                n, sink_pages, first_recent = seq_pages(L, sink, window)
+                pages = [i if i < sink_pages else first_recent + (i - sink_pages) for i in range(n)]
+                assert pages == sorted(set(pages)) and all(0 <= pg < (L + P - 1) // P for pg in pages)
+                seen = torch.zeros(L, dtype=torch.bool)
+                for pg in pages:
+                    m = page_mask(pg, L, sink, window)
+                    assert m != 0, (L, sink, window, pg)
+                    for t in range(16):
+                        if (m >> t) & 1:
+                            seen[pg * 16 + t] = True
+                want = osparse.decode_row(L, "sliding_window_sink" if sink else "sliding_window", window_size=window,
+                                          sink_tokens=sink)
+                assert torch.equal(seen, want), (L, sink, window)
