@@ -2,12 +2,13 @@
 //
 //   y[b, n] = sum_k x[b, k] * (code[n, k] - zero[n, k/G]) * scale[n, k/G]          b < B <= 16
 //
-// Design (one CTA per SM: 16 consumer warps, one producer warp, one epilogue warp):
+// Design (one CTA per SM: 16 consumer warps, three producer warps, one epilogue warp):
 //   * output rows are dealt out evenly to the CTAs; a CTA walks its rows in tiles of 16 (one
 //     tensor-core M tile).
-//   * the producer warp streams each tile through a ring of shared-memory stages with 1-D bulk
+//   * the producer warps stream each tile through a ring of shared-memory stages with 1-D bulk
 //     copies (TMA engine) signalled on mbarriers: one copy per weight row and k-chunk, sized
-//     about 2 KB because the copy engine needs >= 2 KB per copy to saturate HBM.  It starts
+//     about 2 KB because the copy engine needs >= 2 KB per copy to saturate HBM; the copies of a
+//     stage are shared by the producer warps (issuing one costs a warp about 40 ns).  They start
 //     before griddepcontrol.wait: weights do not depend on the previous kernel.
 //   * the codes are NOT dequantised.  OR-ing a code into the mantissa of 1024.0 (or 64.0 for the
 //     high nibbles) gives the exact half 1024 + q, which goes straight into mma.sync.m16n8k16 as
@@ -37,17 +38,6 @@
 
 namespace b200q {
 namespace {
-
-#if defined(B200Q_DBG_TRACE)
-__device__ unsigned long long g_trace[4 * 1024];
-#define TRACE(kind, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 1024) g_trace[(kind) * 1024 + (idx)] = clock64(); } while (0)
-__device__ unsigned long long g_events[32];
-__device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define EVENT(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_events[(i)] = gtimer(); } while (0)
-#else
-#define EVENT(i) do { } while (0)
-#define TRACE(kind, idx) do { } while (0)
-#endif
 
 // ---- activation source: 8 consecutive values of batch row b at k, as the reference would hold them --------
 __device__ __forceinline__ void load8_raw(const void* base, int dtype, int64_t idx, float (&v)[8]) {
@@ -177,7 +167,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    if (warp == 0) EVENT(0);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
     uint64_t* tile_done = empty + kMaxStages;      // [kMaxSlots] all consumer warps have added their share
@@ -213,7 +202,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     for (int i = threadIdx.x; i < nslot * MATS * kConsumerWarps * kTileRows * BC; i += kThreads) part[i] = 0.0f;
     for (int i = threadIdx.x; i < UK * 2 / 4; i += kThreads) reinterpret_cast<uint32_t*>(xzero)[i] = 0u;
     __syncthreads();
-    if (warp == 0) EVENT(1);
     pdl_launch_dependents();
 
     uint8_t* ring = smem + p.off_ring;
@@ -228,7 +216,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         uint32_t phase = 1;
         bool first_pass = true;
         int q = 0;                                  // (tile, matrix) visits so far
-        int trace_n = 0; (void)trace_n;
         for (int xc = 0; xc < n_xc; ++xc) {
             const int c_begin = xc * cpx;
             const int c_end = min(p.n_kc, c_begin + cpx);
@@ -243,7 +230,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         if (!first_pass)
                             ok = mbar_wait_bounded(&empty[slot], phase, &g_device_status, EV_GEMV_EMPTY_WAIT,
                                                    ok ? kWaitLimit : 64u) && ok;
-                        if (pw == 0) { TRACE(2, trace_n); }
                         const int k0 = c * p.kc;
                         const int kcur = min(p.kc, p.K - k0);
                         const uint32_t bytes_row = (uint32_t)(kcur * BITS / 8);
@@ -276,7 +262,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         if (lane == 0) mbar_arrive_expect_tx(&full[slot], warp_bytes);
                         __syncwarp();
                         if (nbytes != 0) bulk_g2s(dst, src, nbytes, &full[slot]);
-                        if (pw == 0) { TRACE(0, trace_n); } ++trace_n;
                         if (++slot == p.stages) { slot = 0; phase ^= 1; first_pass = false; }
                     }
                 }
@@ -297,7 +282,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             const int ps = tl % nslot;
             ok = mbar_wait_bounded(&tile_done[ps], (uint32_t)(tl / nslot) & 1u, &g_device_status, EV_GEMV_FULL_WAIT,
                                    ok ? kWaitLimit : 64u) && ok;
-            if (tl == 0) EVENT(8);
             const int row0 = r_lo + tl * tile_step;
             const int rows = min(kTileRows, r_hi - row0);
             float* slot_base = part + (size_t)ps * MATS * kConsumerWarps * kTileRows * BC;
@@ -356,7 +340,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             if (lane == 0) mbar_arrive(&slot_free[ps]);
         }
         if (p.tp_out.world > 0) tp_finish_writer(p.tp_out, lane);
-        EVENT(9);
         return;
     }
 
@@ -395,7 +378,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 
 
     pdl_wait();   // activations belong to the previous kernel until here
-    if (warp == 0) EVENT(2);
     if (p.tp_in.world > 0) {
         // the activations are an exchange buffer filled by all ranks: wait for every source rank's flag
         if (ctid < p.tp_in.world && !tp_wait_source(p.tp_in, ctid)) atomicMax(&g_device_status, (int)EV_PEER_WAIT);
@@ -487,8 +469,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             named_bar_sync(1, kConsumerThreads);
         }
     }
-
-    if (warp == 0) EVENT(3);
     // ---- stage activations of [xk0, xk0+xkn) as fp16 in tensor-core operand order, with their per-group sums ----
     auto stage_x = [&](int xk0, int xkn, bool write_side) {
         constexpr int CPG = G / 8;                 // 8-value blocks per group: the lanes that share a group
@@ -553,7 +533,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
     int c_slot = 0;
     uint32_t c_phase = 0;
     int mb_idx = 0;                             // scale / zero-point buffer of the current (tile, matrix) visit
-    int trace_c = 0; (void)trace_c;
 
     // ---- one unit: 16 rows x 8 groups ----
     //   a_u    shared address of this lane's bytes of the unit's first group (row g)
@@ -690,17 +669,18 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                             z0[rr] = z1[rr] = has_z ? half_bits_to_float(lds_u16(ma + mbuf_half + pass * 2)) : 0.0f;
                         }
                     } else {
-                        // scales in another dtype or layout: read them where they lie (rounded to fp16 like the copy path)
+                        // scales in another dtype or layout: read them where they lie, widened to fp32 (exact), as the
+                        // reference does with scales.astype(float32)
                         const void* sp = (MATS == 2 && m != 0) ? p.s[1] : p.s[0];
                         const void* zp = (MATS == 2 && m != 0) ? p.z[1] : p.z[0];
                         const int row = min(row0 + g + 8 * rr, p.N - 1);
                         const int ga = gabs + (NB == 1 ? 2 * t : jc * NP + pass);
                         const int64_t e = (int64_t)row * Gn + ga;
-                        s0[rr] = ga < Gn ? __half2float(__float2half_rn(load_as_f32(sp, p.scale_dtype, e))) : 0.0f;
-                        z0[rr] = (ga < Gn && zp != nullptr) ? __half2float(__float2half_rn(load_as_f32(zp, p.scale_dtype, e))) : 0.0f;
+                        s0[rr] = ga < Gn ? load_as_f32(sp, p.scale_dtype, e) : 0.0f;
+                        z0[rr] = (ga < Gn && zp != nullptr) ? load_as_f32(zp, p.scale_dtype, e) : 0.0f;
                         if constexpr (NB == 1) {
-                            s1[rr] = ga + 1 < Gn ? __half2float(__float2half_rn(load_as_f32(sp, p.scale_dtype, e + 1))) : 0.0f;
-                            z1[rr] = (ga + 1 < Gn && zp != nullptr) ? __half2float(__float2half_rn(load_as_f32(zp, p.scale_dtype, e + 1))) : 0.0f;
+                            s1[rr] = ga + 1 < Gn ? load_as_f32(sp, p.scale_dtype, e + 1) : 0.0f;
+                            z1[rr] = (ga + 1 < Gn && zp != nullptr) ? load_as_f32(zp, p.scale_dtype, e + 1) : 0.0f;
                         } else {
                             s1[rr] = s0[rr];
                             z1[rr] = z0[rr];
@@ -763,7 +743,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
         const int xkn = min(p.xk, p.K - xk0);
         if (xc > 0) named_bar_sync(1, kConsumerThreads);     // everyone is done with the previous chunk
         stage_x(xk0, xkn, cta == 0);
-        if (warp == 0) EVENT(4);
 
         const int c_begin = xc * cpx;
         const int c_end = min(p.n_kc, c_begin + cpx);
@@ -797,9 +776,7 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
 #pragma unroll 1
                 for (int c = c_begin; c < c_end; ++c, k0 += p.kc) {
                     const int slot = c_slot;
-                    if (cw == 0) { TRACE(3, trace_c); }
                     ok = mbar_wait_bounded(&full[slot], c_phase, &g_device_status, EV_GEMV_FULL_WAIT, ok ? kWaitLimit : 64u) && ok;
-                    if (cw == 0) { TRACE(1, trace_c); if (trace_c == 0) EVENT(5); } ++trace_c;
                     if (++c_slot == p.stages) { c_slot = 0; c_phase ^= 1; }
                     const int groups = min(p.kc, p.K - k0) >> LOGG;          // groups in this stage
 #pragma unroll 1
@@ -813,7 +790,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
                         else
                             process_unit(std::false_type{}, a_u, (uint32_t)kl * 2, kl >> LOGG, gabs, ng, mb_u, m, row0, dst, has_z);
                     }
-                    if (cw == 0 && trace_c == 1) EVENT(6);
                     // index of this warp's first unit in the next stage: units are numbered through the stages
                     first_unit -= nu_stage;
                     while (first_unit < 0) first_unit += kConsumerWarps;
@@ -831,7 +807,6 @@ __global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constan
             if (++ps == nslot) { ps = 0; dst_tile = part_lane; if (tl >= nslot) sf_parity ^= 1; }
         }
     }
-    if (cw == 0) EVENT(7);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -28,7 +28,7 @@ def test_norm_quantized_linear(cuda, bits, K, N, B):
     want = reference_quantized_linear(normed, w, s, z, bits=bits, group_size=G).squeeze(1)
     got, gn = layer_ops.norm_quantized_linear(x.to(cuda), nw.to(cuda), w.to(cuda), s.to(cuda), z.to(cuda), bits=bits,
                                               group_size=G, return_normed=True)
-    assert rel_l2(got, want) <= 1.5e-3       # includes the fp16 rounding of the normalised rows
+    assert rel_l2(got, want) <= 1e-3
     if K % 128 == 0:
         pass                                  # the fused path does not materialise the normalised rows
     else:
