@@ -46,14 +46,22 @@ enum {
 int b200q_version(void);
 const char* b200q_strerror(int code);
 
-/* Reads (and, if reset != 0, clears) the device-side status word that kernels set when one of
- * their bounded waits on an mbarrier runs out.  Synchronises `stream`.  0 = no event. */
+/* Reads (and, if reset != 0, clears) the device-side status word.  Kernels record an event there instead of
+ * trapping: 1-5 a bounded wait (on a shared-memory barrier or on a peer's flag) ran out, 6 b200q_rope_kv_append
+ * met a position outside the rotary table (the row was left unrotated), 7 it met a position whose block-table
+ * entry is unassigned (nothing was appended).  The largest event seen is returned.  Synchronises `stream`.
+ * 0 = no event. */
 int b200q_device_status(int reset, void* stream);
 
-/* Runtime tuning knob (benchmark sweeps; defaults are chosen per shape when unset/0).
- * Known keys: "gemv.stage_k", "gemv.stages", "gemv.ctas_per_sm", "attn.stages", "attn.ctas_per_sm",
- * "attn.force_simple" (1 = always use the one-warp-per-head kernel), "no_pdl" (1 = launch without
- * programmatic dependent launch). */
+/* Runtime tuning knob (benchmark sweeps and tests; defaults are chosen per shape when unset/0).  Keys:
+ *   "gemv.ts"            1 = every matvec the tcgen05 kernel supports goes to it, -1 = none, 0 = by batch
+ *   "gemv.ts_min_batch"  smallest batch the tcgen05 kernel takes when "gemv.ts" is 0
+ *   "gemv.force_generic" 1 = always the one-warp-per-row kernel that follows the reference arithmetic literally
+ *   "gemv.stage_k", "gemv.stages", "gemv.interleave"   ring geometry / row dealing of the mma.sync kernel
+ *   "ts.stages", "ts.smem_kb", "ts.split"               ring depth, shared-memory budget, K split of the tcgen05 kernel
+ *   "attn.ctas_per_sm", "attn.min_pages"                grid sizing of the split-KV attention kernel
+ *   "attn.force_simple"  1 = always the one-warp-per-head attention kernel
+ *   "no_pdl"             1 = launch without programmatic dependent launch */
 int b200q_set_tuning(const char* key, int value);
 
 /* Group-wise dequantisation, bit-exact: out = cast(fp32(code - zero) * scale) with two
@@ -173,6 +181,9 @@ int b200q_paged_gqa_decode_window(int bits, const void* q, const uint8_t* k_code
  *     writes every partial result it later reads, so leftovers of the previous call are never seen.
  *     Two calls whose kernels overlap on the GPU (different streams, or graphs replayed
  *     concurrently) would overwrite each other's partials: keep calls on one device stream-ordered.
+ *   - Dense attention only (there is no windowed form of this entry point).  Shapes that run the
+ *     one-warp-per-head kernel (head_dim != 128, bf16 q, page sizes other than 16 ...) use no scratch and are
+ *     never refused for size.
  * Arguments and results are those of b200q_paged_gqa_decode without workspace / workspace_bytes. */
 size_t b200q_paged_gqa_static_scratch_bytes(void);
 int b200q_paged_gqa_decode_static(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
@@ -187,12 +198,22 @@ int b200q_paged_gqa_decode_static(int bits, const void* q, const uint8_t* k_code
  * ops/gqa_ops.py:148-160), write q_out [B, Hq, D], and append k / v - quantised with the cache rule
  * of ops/paged_quantized_kv_ops.py:146-175 - to page block_table[b, pos / page_size], slot
  * pos % page_size.  The reference has no quantised append (its update kernels copy the whole cache,
- * kernels/paged_kv_cache_update.metal); this is the in-place form the decode stack needs. */
+ * kernels/paged_kv_cache_update.metal); this is the in-place form the decode stack needs.
+ * A position outside [0, table_len) leaves q / k unrotated, and a position whose block-table entry is negative
+ * or >= num_pages appends nothing; both are recorded in the status word (b200q_device_status events 6 and 7). */
 int b200q_rope_kv_append(const void* qkv, const float* cos_table, const float* sin_table,
                          const int32_t* positions, const int32_t* block_table, void* q_out, uint8_t* k_codes,
                          uint8_t* v_codes, void* k_scales, void* v_scales, int bits, int B, int Hq, int Hkv,
                          int D, int page_size, int64_t num_pages, int max_blocks, int group_size, int table_len,
                          void* stream);
+
+/* Symmetric group-wise quantisation of KV rows with the rule of the reference cache
+ * (_quantize_group_symmetric_8 / _4, ops/paged_quantized_kv_ops.py:146-153, 168-175, as applied by quantize_kv_pages,
+ * :194-292): per group of `group_size` values along D, scale = max(max|v|, 1e-8) / (127 | 7) in fp32 (stored fp16),
+ * code = clip(rint(v / scale), -127|-7, 127|7) + (128 | 8).  values [rows, D] in in_dtype (fp16 / bf16);
+ * codes [rows, D] (bits=8) or [rows, ceil(D/2)] (bits=4, low nibble = even d); scales [rows, ceil(D/group)] fp16. */
+int b200q_quantize_kv(int bits, const void* values, uint8_t* codes, void* scales, int64_t rows, int D, int group_size,
+                      int in_dtype, void* stream);
 
 /* Tensor-parallel glue (no counterpart in the reference, which is single-device): all-gather of an
  * activation shard over NVLink peer memory.  `local` [rows, row_bytes_local] is this rank's shard;

@@ -2,6 +2,7 @@
 // RMSNorm(+residual), block-table lookup).
 #include "common.cuh"
 
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -48,6 +49,7 @@ void tp_take(int* in_slot, int* out_slot) {
     *out_slot = g_tp_next_out;
     g_tp_next_in = g_tp_next_out = -1;
 }
+void tp_discard() { g_tp_next_in = g_tp_next_out = -1; }
 
 int tuning_get(const char* key) {
     std::lock_guard<std::mutex> lock(g_mu);
@@ -61,6 +63,9 @@ int max_smem_optin() { return props().smem_optin; }
 int gemv_read_status(int reset, cudaStream_t stream);
 int attn_read_status(int reset, cudaStream_t stream);
 int peer_read_status(int reset, cudaStream_t stream);
+int stack_read_status(int reset, cudaStream_t stream);
+int quantize_kv_impl(int bits, const void* values, uint8_t* codes, void* scales, int64_t rows, int D, int group_size,
+                     int in_dtype, cudaStream_t stream);
 int peer_allgather_impl(const void* local, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch,
                         int rank, int world, int rows, int64_t row_bytes_local, cudaStream_t stream);
 int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scales, const void* zeros,
@@ -260,14 +265,17 @@ int b200q_device_status(int reset, void* stream) {
     const int a = gemv_read_status(reset, (cudaStream_t)stream);
     const int b = attn_read_status(reset, (cudaStream_t)stream);
     const int c = peer_read_status(reset, (cudaStream_t)stream);
+    const int d = stack_read_status(reset, (cudaStream_t)stream);
     if (a < 0) return a;
     if (b < 0) return b;
     if (c < 0) return c;
-    return a > b ? (a > c ? a : c) : (b > c ? b : c);
+    if (d < 0) return d;
+    return std::max(std::max(a, b), std::max(c, d));
 }
 
 int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch,
                          int rank, int world, int rows, int64_t row_bytes_local, void* stream) {
+    tp_discard();
     return peer_allgather_impl(local, peer_full, peer_flags, epoch, rank, world, rows, row_bytes_local,
                                (cudaStream_t)stream);
 }
@@ -310,6 +318,7 @@ int b200q_set_tuning(const char* key, int value) {
 
 int b200q_dequant(int bits, const uint8_t* codes, const void* scales, const void* zeros, void* out, int64_t M,
                   int64_t K, int group_size, int scale_dtype, int out_dtype, void* stream) {
+    tp_discard();
     if ((bits != 4 && bits != 8) || codes == nullptr || scales == nullptr || out == nullptr) return B200Q_ERR_BAD_ARG;
     if (M <= 0 || K <= 0 || group_size <= 0 || !is_scale_dtype(scale_dtype) || !is_act_dtype(out_dtype))
         return B200Q_ERR_BAD_ARG;
@@ -337,7 +346,10 @@ int b200q_norm_qmatvec(int bits, const void* x, const void* residual_in, const v
                        float eps, void* z_out, void* normed_out, const uint8_t* codes, const void* scales,
                        const void* zeros, const void* residual, void* y, int B, int64_t N, int64_t K, int group_size,
                        int act_dtype, int scale_dtype, void* stream) {
-    if (norm_weight == nullptr) return B200Q_ERR_BAD_ARG;
+    if (norm_weight == nullptr) {
+        tp_discard();
+        return B200Q_ERR_BAD_ARG;
+    }
     return qmatvec_impl(bits, x, codes, scales, zeros, residual, y, B, N, K, group_size, act_dtype, scale_dtype,
                         residual_in, norm_weight, norm_w_dtype, eps, z_out, normed_out, (cudaStream_t)stream);
 }
@@ -346,6 +358,7 @@ int b200q_rope_kv_append(const void* qkv, const float* cos_table, const float* s
                          const int32_t* block_table, void* q_out, uint8_t* k_codes, uint8_t* v_codes, void* k_scales,
                          void* v_scales, int bits, int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages,
                          int max_blocks, int group_size, int table_len, void* stream) {
+    tp_discard();
     return rope_kv_append_impl(qkv, cos_table, sin_table, positions, block_table, q_out, k_codes, v_codes, k_scales,
                                v_scales, bits, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, table_len,
                                (cudaStream_t)stream);
@@ -362,6 +375,7 @@ int b200q_gate_up_swiglu(int bits, const void* x, const uint8_t* gate_codes, con
 }
 
 int b200q_swiglu(const void* gate, const void* up, void* out, int64_t rows, int64_t dim, int dtype, void* stream) {
+    tp_discard();
     if (gate == nullptr || up == nullptr || out == nullptr || rows <= 0 || dim <= 0 || !is_act_dtype(dtype))
         return B200Q_ERR_BAD_ARG;
     const int64_t n = rows * dim;
@@ -375,6 +389,7 @@ int b200q_swiglu(const void* gate, const void* up, void* out, int64_t rows, int6
 }
 
 int b200q_residual_add(const void* x, const void* residual, void* out, int64_t n, int dtype, void* stream) {
+    tp_discard();
     if (x == nullptr || residual == nullptr || out == nullptr || n <= 0 || !is_act_dtype(dtype)) return B200Q_ERR_BAD_ARG;
     const int grid = grid_for(n, 256);
     if (dtype == B200Q_F16)
@@ -388,6 +403,7 @@ int b200q_residual_add(const void* x, const void* residual, void* out, int64_t n
 
 int b200q_rmsnorm_residual(const void* x, const void* residual, const void* weight, void* y, void* z_out, int64_t rows,
                            int64_t D, float eps, int dtype, int w_dtype, void* stream) {
+    tp_discard();
     if (x == nullptr || weight == nullptr || y == nullptr || rows <= 0 || D <= 0 || !is_act_dtype(dtype) ||
         !is_scale_dtype(w_dtype))
         return B200Q_ERR_BAD_ARG;
@@ -396,6 +412,7 @@ int b200q_rmsnorm_residual(const void* x, const void* residual, const void* weig
 
 int b200q_block_table_lookup(const int32_t* block_table, const int32_t* positions, int32_t* page_ids, int32_t* offsets,
                              int B, int max_blocks, int page_size, void* stream) {
+    tp_discard();
     if (block_table == nullptr || positions == nullptr || page_ids == nullptr || offsets == nullptr || B <= 0 ||
         max_blocks <= 0 || page_size <= 0)
         return B200Q_ERR_BAD_ARG;
@@ -426,6 +443,12 @@ int b200q_paged_gqa_decode_window(int bits, const void* q, const uint8_t* k_code
     return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, workspace,
                                  workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
                                  q_dtype, scale_dtype, sink_tokens, window_size, (cudaStream_t)stream);
+}
+
+int b200q_quantize_kv(int bits, const void* values, uint8_t* codes, void* scales, int64_t rows, int D, int group_size,
+                      int in_dtype, void* stream) {
+    tp_discard();
+    return quantize_kv_impl(bits, values, codes, scales, rows, D, group_size, in_dtype, (cudaStream_t)stream);
 }
 
 size_t b200q_paged_gqa_static_scratch_bytes(void) { return paged_gqa_static_scratch_bytes_impl(); }

@@ -39,6 +39,8 @@ enum DeviceEvent : int {
     EV_ATTN_FULL_WAIT = 3,
     EV_ATTN_EMPTY_WAIT = 4,
     EV_PEER_WAIT = 5,         // a rank gave up waiting for a peer's shard in the peer all-gather
+    EV_ROPE_POSITION = 6,     // rope + append: a position lies outside the rotary table (row left unrotated)
+    EV_KV_PAGE_UNASSIGNED = 7,  // rope + append: the block table has no page for the position (nothing appended)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -63,6 +65,7 @@ struct TpIn {
 struct TpSlot { TpOut out; };       // host table entry
 const TpSlot* tp_slot(int slot);    // nullptr if the slot was never registered
 void tp_take(int* in_slot, int* out_slot);   // exchange slots set by b200q_tp_next for the next call (then cleared)
+void tp_discard();                           // entry points without an exchange drop a pending request
 
 // ---------------------------------------------------------------------------------------------
 // Tuning table (host side; see b200q_set_tuning)

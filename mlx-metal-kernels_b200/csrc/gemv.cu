@@ -15,7 +15,8 @@ namespace b200q {
 int gemv_read_status(int reset, cudaStream_t stream) {
     const int a = gemv_q4_read_status(reset, stream);
     const int b = gemv_q8_read_status(reset, stream);
-    return a != 0 ? a : b;
+    const int c = qgemm_ts_read_status(reset, stream);
+    return a != 0 ? a : (b != 0 ? b : c);
 }
 
 namespace {
@@ -108,7 +109,7 @@ bool fast_path_ok(const GemvParams& p) {
     if (tuning_get("gemv.force_generic")) return false;
     if (p.G != 32 && p.G != 64 && p.G != 128) return false;
     if (p.K % p.G != 0 || p.row_bytes % 16 != 0) return false;
-    if (p.B > 16) return false;
+    if (p.B > 64) return false;
     if (!aligned16(p.x) || !aligned16(p.w[0]) || (p.w[1] != nullptr && !aligned16(p.w[1]))) return false;
     if (p.res_in != nullptr && !aligned16(p.res_in)) return false;
     if (p.z_out != nullptr && !aligned16(p.z_out)) return false;
@@ -116,7 +117,23 @@ bool fast_path_ok(const GemvParams& p) {
     return true;
 }
 
+// Which kernel takes a launch: "gemv.ts" = 1 sends everything the tcgen05 kernel supports to it, -1 nothing,
+// 0 (default) the batches above gemv.ts_min_batch - 1.
+bool prefer_ts(const GemvParams& p) {
+    const int mode = tuning_get("gemv.ts");
+    if (mode < 0) return false;
+    if (mode > 0) return true;
+    int min_b = tuning_get("gemv.ts_min_batch");
+    if (min_b <= 0) min_b = 17;
+    return p.B >= min_b;
+}
+
 int dispatch_fast(int bits, GemvParams& p, bool gate_up, cudaStream_t stream) {
+    if (prefer_ts(p)) {
+        const int rc = qgemm_ts(bits, p, gate_up, stream);
+        if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+    }
+    if (p.B > 16) return B200Q_ERR_UNSUPPORTED;
     return bits == 4 ? gemv_fast_q4(p, gate_up, stream) : gemv_fast_q8(p, gate_up, stream);
 }
 
@@ -149,7 +166,7 @@ int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scal
     auto offw = [&](void* base, size_t elems) -> uint8_t* {
         return base ? reinterpret_cast<uint8_t*>(base) + elems * esz : nullptr;
     };
-    int chunk = 16;      // batch rows per launch; halved when the kernel's shared-memory plan does not fit
+    int chunk = 64;      // batch rows per launch; halved when the kernels' shared-memory plans do not fit
     for (int b0 = 0; b0 < B;) {
         GemvParams p = {};
         const int bn = std::min(chunk, B - b0);
@@ -220,7 +237,7 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
     auto offw = [&](void* base, size_t elems) -> uint8_t* {
         return base ? reinterpret_cast<uint8_t*>(base) + elems * esz : nullptr;
     };
-    int chunk = 16;      // batch rows per launch; halved when the kernel's shared-memory plan does not fit
+    int chunk = 64;      // batch rows per launch; halved when the kernels' shared-memory plans do not fit
     for (int b0 = 0; b0 < rows;) {
         GemvParams p = {};
         const int bn = std::min(chunk, rows - b0);

@@ -70,4 +70,9 @@ int gemv_fast_q8(GemvParams& p, bool gate_up, cudaStream_t stream);
 int gemv_q4_read_status(int reset, cudaStream_t stream);
 int gemv_q8_read_status(int reset, cudaStream_t stream);
 
+// tcgen05 kernel (qgemm_ts.cu): weights through tensor memory, any batch up to 64 rows per launch.  Returns
+// B200Q_ERR_UNSUPPORTED when the problem is outside its plan.
+int qgemm_ts(int bits, const GemvParams& p, bool gate_up, cudaStream_t stream);
+int qgemm_ts_read_status(int reset, cudaStream_t stream);
+
 }  // namespace b200q

@@ -833,27 +833,38 @@ int paged_gqa_decode_static_impl(int bits, const void* q, const uint8_t* k_codes
                                  const int32_t* lengths, void* out, int B, int Hq, int Hkv, int D, int page_size,
                                  int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
                                  int scale_dtype, cudaStream_t stream) {
-    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return B200Q_ERR_BAD_ARG;
-    if (paged_gqa_workspace_bytes_impl(B, Hq, Hkv, D) > kStaticScratchBytes) return B200Q_ERR_STATIC_SCRATCH;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) {
+        tp_discard();
+        return B200Q_ERR_BAD_ARG;
+    }
     // In host code the array's name is only a handle; the device address has to be asked for, once per
     // device, with that device current.
     static void* scratch_ptr[64] = {};
     static std::mutex mu;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_LAUNCH;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        tp_discard();
+        return B200Q_ERR_LAUNCH;
+    }
     void* ptr;
     {
         std::lock_guard<std::mutex> lock(mu);
         if (scratch_ptr[dev] == nullptr) {
             void* p = nullptr;
-            if (cudaGetSymbolAddress(&p, g_attn_static_scratch) != cudaSuccess || p == nullptr) return B200Q_ERR_LAUNCH;
+            if (cudaGetSymbolAddress(&p, g_attn_static_scratch) != cudaSuccess || p == nullptr) {
+                tp_discard();
+                return B200Q_ERR_LAUNCH;
+            }
             scratch_ptr[dev] = p;
         }
         ptr = scratch_ptr[dev];
     }
-    return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, ptr,
-                                 kStaticScratchBytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
-                                 q_dtype, scale_dtype, 0, 0, stream);
+    // Only the split-KV kernels use the scratch: the size check is theirs (problems that take the one-warp-per-head
+    // kernel need none), reported here under this entry point's own code.
+    const int rc = paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, ptr,
+                                         kStaticScratchBytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size,
+                                         scale, q_dtype, scale_dtype, 0, 0, stream);
+    return rc == B200Q_ERR_WORKSPACE ? B200Q_ERR_STATIC_SCRATCH : rc;
 }
 
 }  // namespace b200q

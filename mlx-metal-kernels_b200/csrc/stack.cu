@@ -17,7 +17,12 @@
 // One warp per (sequence, head); head_dim <= 128 and even; lanes own 4 consecutive elements.
 #include "common.cuh"
 
+#include <algorithm>
+
 namespace b200q {
+
+B200Q_DEFINE_STATUS_WORD(stack_read_status)
+
 namespace {
 
 struct RopeAppendParams {
@@ -52,6 +57,8 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const __grid_consta
         v[0] = __low2float(h0); v[1] = __high2float(h0); v[2] = __low2float(h1); v[3] = __high2float(h1);
     }
     const bool is_v = hh >= p.Hq + p.Hkv;
+    // a position outside the rotary table: the row passes through unrotated and the event is recorded
+    if (!is_v && lane == 0 && (pos < 0 || pos >= p.table_len)) atomicMax(&g_device_status, (int)EV_ROPE_POSITION);
     if (!is_v && live && pos >= 0 && pos < p.table_len) {
         const int half_d = p.D / 2;
 #pragma unroll
@@ -82,7 +89,10 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const __grid_consta
     const int hkv = is_v ? hh - p.Hq - p.Hkv : hh - p.Hq;
     const int blk = pos / p.P;
     int page = (pos >= 0 && blk < p.max_blocks) ? p.block_table[(size_t)b * p.max_blocks + blk] : -1;
-    if (page < 0 || page >= p.num_pages) return;          // unassigned page: nothing to write (uniform per warp)
+    if (page < 0 || page >= p.num_pages) {                // unassigned page: nothing is written, the event is recorded
+        if (lane == 0) atomicMax(&g_device_status, (int)EV_KV_PAGE_UNASSIGNED);
+        return;
+    }
     const int slot = pos % p.P;
     // group max over G elements = G/4 consecutive lanes (G a multiple of 4, power of two <= 128)
     float mx = live ? fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))) : 0.0f;
@@ -112,7 +122,61 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const __grid_consta
     }
 }
 
+// Symmetric group-wise quantisation of [rows, D] values with the cache rule above: one thread per (row, group)
+// (per row when the group size is odd, so that a packed byte never straddles two threads).
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_kv_kernel(const T* __restrict__ values, uint8_t* __restrict__ codes,
+                                                          __half* __restrict__ scales, int64_t rows, int D, int G, int Gd,
+                                                          int bits, bool per_row) {
+    const int64_t items = per_row ? rows : rows * Gd;
+    const float limit = bits == 8 ? 127.0f : 7.0f;
+    const float offset = bits == 8 ? 128.0f : 8.0f;
+    const int dp = bits == 4 ? (D + 1) / 2 : D;
+    for (int64_t it = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = per_row ? it : it / Gd;
+        const int g_lo = per_row ? 0 : (int)(it - row * Gd);
+        const int g_hi = per_row ? Gd : g_lo + 1;
+        const T* src = values + row * D;
+        uint8_t* dst = codes + row * dp;
+        for (int g = g_lo; g < g_hi; ++g) {
+            const int d_lo = g * G, d_hi = min(D, d_lo + G);
+            float mx = 0.0f;
+            for (int d = d_lo; d < d_hi; ++d) mx = fmaxf(mx, fabsf(to_f32(src[d])));
+            const float scale = __fdiv_rn(fmaxf(mx, 1e-8f), limit);
+            scales[row * Gd + g] = __float2half_rn(scale);
+            for (int d = d_lo; d < d_hi; ++d) {
+                const float qv = fminf(fmaxf(rintf(__fdiv_rn(to_f32(src[d]), scale)), -limit), limit) + offset;
+                const uint32_t c = (uint32_t)(int)qv;
+                if (bits == 8) {
+                    dst[d] = (uint8_t)c;
+                } else if (d & 1) {
+                    dst[d >> 1] = (uint8_t)(dst[d >> 1] | (c << 4));     // the low nibble was written just before by this thread
+                } else {
+                    dst[d >> 1] = (uint8_t)c;                            // high nibble zero (stays zero for an odd D)
+                }
+            }
+        }
+    }
+}
+
 }  // namespace
+
+int quantize_kv_impl(int bits, const void* values, uint8_t* codes, void* scales, int64_t rows, int D, int group_size,
+                     int in_dtype, cudaStream_t stream) {
+    if ((bits != 4 && bits != 8) || values == nullptr || codes == nullptr || scales == nullptr) return B200Q_ERR_BAD_ARG;
+    if (rows <= 0 || D <= 0 || group_size <= 0 || !is_act_dtype(in_dtype)) return B200Q_ERR_BAD_ARG;
+    const int Gd = (D + group_size - 1) / group_size;
+    const bool per_row = bits == 4 && (group_size & 1);
+    const int64_t items = per_row ? rows : rows * Gd;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((items + 255) / 256, (int64_t)sm_count() * 16));
+    if (in_dtype == B200Q_F16)
+        quantize_kv_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)values, codes, (__half*)scales, rows, D, group_size,
+                                                            Gd, bits, per_row);
+    else
+        quantize_kv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)values, codes, (__half*)scales, rows,
+                                                                   D, group_size, Gd, bits, per_row);
+    return finish_launch();
+}
 
 int rope_kv_append_impl(const void* qkv, const float* cos_table, const float* sin_table, const int32_t* positions,
                         const int32_t* block_table, void* q_out, uint8_t* k_codes, uint8_t* v_codes, void* k_scales,

@@ -35,6 +35,7 @@ SIGNATURES = {
                                   _i, _vp]),
     "b200q_gate_up_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _vp, _vp,
                                   _i, _i64, _i64, _i, _i, _i, _vp]),
+    "b200q_quantize_kv": (_i, [_i, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "b200q_peer_allgather": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp]),
     "b200q_tp_register": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),
     "b200q_tp_next": (_i, [_i, _i]),

@@ -16,7 +16,7 @@ import torch
 
 from . import _cabi
 from .gqa_ops import validate_gqa_heads
-from .quant_ops import dequant_codes, pack_q4
+from .quant_ops import dequant_codes
 from .sparse_attention_ops import decode_window
 
 _MAX_HEAD_DIM = 128
@@ -122,27 +122,26 @@ class PagedQuantizedKVCache:
 # ---------------------------------------------------------------------------------------------
 def _quantize_groups(values: torch.Tensor, bits: int, group_size: int):
     """Per group of the last axis: scale = max(max|v|, 1e-8) / (127|7) in fp32, code =
-    clip(rint(v / scale)) + (128|8), scale stored fp16 (ops/paged_quantized_kv_ops.py:146-175)."""
-    limit, offset = (127, 128) if bits == 8 else (7, 8)
+    clip(rint(v / scale)) + (128|8), scale stored fp16 (ops/paged_quantized_kv_ops.py:146-175).
+    Returns (codes [..., D] or packed [..., ceil(D/2)], scales [..., ceil(D/group)]) from the CUDA kernel."""
+    _cabi.require_cuda(values)
+    if values.dtype not in (torch.float16, torch.bfloat16):
+        values = values.to(torch.float16)
+    values = _cabi.contiguous(values)
     D = values.shape[-1]
+    rows = values.numel() // D
     groups = (D + group_size - 1) // group_size
-    pad = groups * group_size - D
-    v = values.to(torch.float32)
-    if pad:
-        v = torch.nn.functional.pad(v, (0, pad))
-    v = v.reshape(*values.shape[:-1], groups, group_size)
-    max_abs = v.abs().amax(dim=-1, keepdim=True).clamp_min(1e-8)
-    # a tensor divisor: dividing by a Python scalar multiplies by its reciprocal on CUDA, which is not the
-    # reference's correctly rounded max_abs / limit in the last bit
-    scale = max_abs / torch.full_like(max_abs, float(limit))
-    codes = (torch.round(v / scale).clamp(-limit, limit) + offset).to(torch.uint8)
-    codes = codes.reshape(*values.shape[:-1], groups * group_size)[..., :D]
-    return codes, scale.squeeze(-1).to(torch.float16)
+    dp = (D + 1) // 2 if bits == 4 else D
+    codes = torch.empty((*values.shape[:-1], dp), dtype=torch.uint8, device=values.device)
+    scales = torch.empty((*values.shape[:-1], groups), dtype=torch.float16, device=values.device)
+    _cabi.check(_cabi.load().b200q_quantize_kv(bits, values.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, D,
+                                               group_size, _cabi.dtype_code(values.dtype), _cabi.stream()),
+                "b200q_quantize_kv")
+    return codes, scales
 
 
 def quantize_kv_pages(K_pages, V_pages, block_table, lengths, config: PagedQuantizedKVConfig) -> PagedQuantizedKVCache:
-    """fp16/bf16 pages [NUM_PAGES,PAGE_SIZE,Hkv,D] -> quantized cache (ops/paged_quantized_kv_ops.py:194-292).
-    A data-preparation helper: plain tensor ops on the pages' device."""
+    """fp16/bf16 pages [NUM_PAGES,PAGE_SIZE,Hkv,D] -> quantized cache (ops/paged_quantized_kv_ops.py:194-292)."""
     config = config.validate()
     if K_pages.shape != V_pages.shape:
         raise ValueError(f"K_pages and V_pages must match, got {tuple(K_pages.shape)} != {tuple(V_pages.shape)}")
@@ -151,10 +150,7 @@ def quantize_kv_pages(K_pages, V_pages, block_table, lengths, config: PagedQuant
     NUM_PAGES, PAGE_SIZE, Hkv, D = K_pages.shape
     out = []
     for pages in (K_pages, V_pages):
-        codes, scales = _quantize_groups(pages, config.bits, config.group_size)
-        if config.bits == 4:
-            codes = pack_q4(codes.reshape(-1, D)).reshape(NUM_PAGES, PAGE_SIZE, Hkv, (D + 1) // 2)
-        out.append((codes.contiguous(), scales.contiguous()))
+        out.append(_quantize_groups(pages, config.bits, config.group_size))
     return PagedQuantizedKVCache(
         k_pages_q=out[0][0], v_pages_q=out[1][0], k_scales=out[0][1], v_scales=out[1][1],
         block_table=block_table, lengths=lengths, bits=config.bits, page_size=config.page_size,

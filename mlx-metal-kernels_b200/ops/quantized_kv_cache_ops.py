@@ -22,7 +22,7 @@ from . import _cabi
 from .gqa_ops import validate_gqa_heads
 from .paged_kv_ops import normalize_positions
 from .paged_quantized_kv_ops import PagedQuantizedKVCache, _quantize_groups, paged_attention_launch
-from .quant_ops import dequant_codes, pack_q4
+from .quant_ops import dequant_codes
 from .sparse_attention_ops import SparseAttentionPattern, decode_window
 
 _MAX_HEAD_DIM = 128
@@ -121,8 +121,8 @@ def _cache_dims(qkv_cache: QuantizedKVCache) -> tuple[int, int, int, int]:
 # ---------------------------------------------------------------------------------------------
 def quantize_kv_cache(K_cache, V_cache, config: QuantizedKVCacheConfig, *, lengths=None) -> QuantizedKVCache:
     """fp16/bf16 caches [B,MAX_S,Hkv,D] -> quantized cache (ops/quantized_kv_cache_ops.py:173-277).
-    Tokens at or past ``lengths[b]`` keep code 0 and scale 0, as in the reference.  A data-preparation
-    helper: plain tensor ops on the caches' device."""
+    Tokens at or past ``lengths[b]`` keep code 0 and scale 0, as in the reference.  The group
+    quantisation runs in the CUDA kernel behind b200q_quantize_kv; the length mask is a tensor op."""
     config = config.validate()
     if K_cache.shape != V_cache.shape:
         raise ValueError(f"K_cache and V_cache must match, got {tuple(K_cache.shape)} != {tuple(V_cache.shape)}")
@@ -140,9 +140,7 @@ def quantize_kv_cache(K_cache, V_cache, config: QuantizedKVCacheConfig, *, lengt
         if valid is not None:
             codes = torch.where(valid, codes, torch.zeros_like(codes))
             scales = torch.where(valid, scales, torch.zeros_like(scales))
-        if config.bits == 4:
-            codes = pack_q4(codes.reshape(-1, D)).reshape(B, MAX_S, Hkv, (D + 1) // 2)
-        out.append((codes.contiguous(), scales.contiguous()))
+        out.append((codes.contiguous(), scales.contiguous()))      # q4 codes come packed from the kernel
     return QuantizedKVCache(k_q=out[0][0], v_q=out[1][0], k_scales=out[0][1], v_scales=out[1][1],
                             bits=config.bits, group_size=config.group_size, original_shape=tuple(K_cache.shape),
                             layout=config.layout)

@@ -39,7 +39,7 @@ def _load_reference_quantizer(ref_root: Path):
 
 
 def main():
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("MLX_METAL_KERNELS_REF", "/root/reference"))
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["MLX_METAL_KERNELS_REF"])
     qw = _load_reference_quantizer(ref_root)
     rng = np.random.default_rng(20240607)
     out = {}

@@ -26,7 +26,7 @@ ROLES = ("qkv", "o_proj", "gate_proj", "up_proj", "down_proj")
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MLX_METAL_KERNELS_REF", "/root/reference"))
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["MLX_METAL_KERNELS_REF"])
     sys.path.insert(0, str(ref_root))
     from models.llama_config import LlamaLikeConfig
     from models.quantize_weights import QuantizationConfig, dequantize_quantized_weight, quantize_weight_groupwise

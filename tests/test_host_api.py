@@ -180,15 +180,18 @@ def test_paged_config_and_cache_validation():
 
 
 @pytest.mark.parametrize("bits,D,G", [(8, 32, 32), (4, 32, 32), (4, 17, 16), (8, 16, 32)])
-def test_quantize_kv_pages_matches_oracle_and_accounts_bytes(bits, D, G):
+def test_paged_cache_container_accounts_bytes(bits, D, G):
+    """The container's shape / byte accounting on a cache quantised by the oracle; the quantiser itself is a CUDA
+    kernel (compared with the oracle in the GPU tests) and refuses CPU tensors."""
     torch.manual_seed(bits * 100 + D)
     K = torch.randn(6, 4, 2, D).to(torch.float16)
     V = torch.randn(6, 4, 2, D).to(torch.float16)
     bt = torch.arange(6, dtype=torch.int32).reshape(2, 3)
     ln = torch.tensor([12, 9], dtype=torch.int32)
-    cache = pq_ops.quantize_kv_pages(K, V, bt, ln, pq_ops.PagedQuantizedKVConfig(bits=bits, page_size=4, group_size=G))
+    with pytest.raises(cabi.B200QError, match="no CPU route"):
+        pq_ops.quantize_kv_pages(K, V, bt, ln, pq_ops.PagedQuantizedKVConfig(bits=bits, page_size=4, group_size=G))
     ref = opq.quantize_kv_pages(K, V, bt, ln, bits=bits, page_size=4, group_size=G)
-    assert torch.equal(cache.k_pages_q, ref.k_pages_q) and torch.equal(cache.v_scales, ref.v_scales)
+    cache = pq_ops.PagedQuantizedKVCache(**{f.name: getattr(ref, f.name) for f in dataclasses.fields(ref)})
     dp = (D + 1) // 2 if bits == 4 else D
     groups = (D + G - 1) // G
     assert cache.shapes()["k_pages_q"] == (6, 4, 2, dp) and cache.shapes()["k_scales"] == (6, 4, 2, groups)
@@ -262,14 +265,15 @@ def test_contiguous_quantized_cache_host_logic():
         C(with_zeros=True).validate()
     with pytest.raises(NotImplementedError):
         C(layout="paged").validate()
-    # the quantiser is plain tensor code: it matches the oracle on CPU tensors, lengths mask included
+    # container checks on caches quantised by the oracle (the quantiser is a CUDA kernel: no CPU route)
     torch.manual_seed(3)
     K = torch.randn(2, 6, 2, 40).to(torch.float16)
     V = torch.randn(2, 6, 2, 40).to(torch.float16)
+    with pytest.raises(cabi.B200QError, match="no CPU route"):
+        qkv_ops.quantize_kv_cache(K, V, C(bits=8, group_size=32), lengths=[6, 2])
     for bits in (8, 4):
-        cache = qkv_ops.quantize_kv_cache(K, V, C(bits=bits, group_size=32), lengths=[6, 2])
         ref = ocq.quantize_kv_cache(K, V, bits=bits, group_size=32, lengths=[6, 2])
-        assert torch.equal(cache.k_q, ref.k_q) and torch.equal(cache.v_scales, ref.v_scales)
+        cache = qkv_ops.QuantizedKVCache(**{f.name: getattr(ref, f.name) for f in dataclasses.fields(ref)})
         dp = 20 if bits == 4 else 40
         assert cache.shapes() == {"k_q": (2, 6, 2, dp), "v_q": (2, 6, 2, dp), "k_scales": (2, 6, 2, 2),
                                   "v_scales": (2, 6, 2, 2), "original": (2, 6, 2, 40)}
@@ -334,7 +338,8 @@ def test_contiguous_quantized_cache_host_logic():
     # the paged view shares the buffers: 16-token pages when MAX_S allows it, else one page per sequence
     view = qkv_ops.as_paged_view(cache, torch.tensor([6, 2], dtype=torch.int32))
     assert view.page_size == 6 and view.block_table.tolist() == [[0], [1]] and view.k_pages_q.data_ptr() == cache.k_q.data_ptr()
-    big = qkv_ops.quantize_kv_cache(torch.zeros(2, 32, 1, 16), torch.zeros(2, 32, 1, 16), C())
+    bref = ocq.quantize_kv_cache(torch.zeros(2, 32, 1, 16), torch.zeros(2, 32, 1, 16), bits=8, group_size=32)
+    big = qkv_ops.QuantizedKVCache(**{f.name: getattr(bref, f.name) for f in dataclasses.fields(bref)})
     view = qkv_ops.as_paged_view(big, torch.tensor([32, 32], dtype=torch.int32))
     assert view.page_size == 16 and view.block_table.tolist() == [[0, 1], [2, 3]] and view.original_page_shape == (4, 16, 1, 16)
 
