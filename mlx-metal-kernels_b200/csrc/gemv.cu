@@ -118,13 +118,14 @@ bool fast_path_ok(const GemvParams& p) {
 }
 
 // Which kernel takes a launch: "gemv.ts" = 1 sends everything the tcgen05 kernel supports to it, -1 nothing,
-// 0 (default) the batches above gemv.ts_min_batch - 1.
+// 0 (default) the batches of gemv.ts_min_batch rows and more (default 5: measured crossover at the Llama-3-8B
+// shapes, where the mma.sync kernel pays its per-group affine step once per batch row tile).
 bool prefer_ts(const GemvParams& p) {
     const int mode = tuning_get("gemv.ts");
     if (mode < 0) return false;
     if (mode > 0) return true;
     int min_b = tuning_get("gemv.ts_min_batch");
-    if (min_b <= 0) min_b = 17;
+    if (min_b <= 0) min_b = 5;
     return p.B >= min_b;
 }
 
