@@ -185,3 +185,23 @@ def test_sliding_window_and_sinks_match_oracle(cuda, bits, sink, window, Hq, Hkv
         dense = pq_ops.paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), backend="cuda")
         assert torch.equal(got, dense)
     assert cabi.device_status() == 0
+
+
+@pytest.mark.parametrize("bits,D,G,dtype", [(8, 32, 32, torch.float16), (4, 32, 32, torch.float16), (4, 17, 16, torch.float16),
+                                            (8, 16, 32, torch.float16), (4, 128, 32, torch.bfloat16), (8, 128, 64, torch.float16),
+                                            (4, 24, 3, torch.float16)])
+def test_quantize_kv_pages_matches_oracle_exactly(cuda, bits, D, G, dtype):
+    """quantize_kv_pages runs the CUDA quantiser (b200q_quantize_kv): codes and scales equal the oracle's bit for bit,
+    including a short last group (D = 17, 16 < G), an odd group size and bf16 pages."""
+    g = torch.Generator().manual_seed(bits * 100 + D)
+    K = torch.randn((6, 4, 2, D), generator=g).to(dtype)
+    V = (torch.randn((6, 4, 2, D), generator=g) * 3).to(dtype)
+    K[0, 0, 0] = 0                                            # an all-zero group: scale 1e-8 / limit, codes at the offset
+    bt = torch.arange(6, dtype=torch.int32).reshape(2, 3)
+    ln = torch.tensor([12, 9], dtype=torch.int32)
+    want = opq.quantize_kv_pages(K, V, bt, ln, bits=bits, page_size=4, group_size=G)
+    got = pq_ops.quantize_kv_pages(K.to(cuda), V.to(cuda), bt.to(cuda), ln.to(cuda),
+                                   pq_ops.PagedQuantizedKVConfig(bits=bits, page_size=4, group_size=G))
+    for name in ("k_pages_q", "v_pages_q", "k_scales", "v_scales"):
+        assert torch.equal(getattr(got, name).cpu(), getattr(want, name)), name
+    assert got.k_scales.dtype == torch.float16

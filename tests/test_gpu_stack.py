@@ -53,6 +53,38 @@ def test_rope_kv_append_exact(cuda, bits, G):
         assert torch.equal(getattr(dcache, name).cpu(), getattr(ocache, name)), name
 
 
+def test_rope_kv_append_reports_bad_positions_and_unassigned_pages(cuda):
+    """A position outside the rotary table, or one whose block-table entry is -1, is recorded in the status word
+    (events 6 and 7) instead of being dropped silently; the other sequences are appended as usual."""
+    B, Hq, Hkv, D, P = 3, 4, 2, 128, 16
+    case = synth.paged_kv_case(B, Hkv, D, P, num_pages=16, min_len=48, max_len=48, bits=8, group_size=32, seed=9)
+    qkv = synth.activations((B, (Hq + 2 * Hkv) * D), 10)
+    cos, sin = ostack.rope_tables(D, 500000.0, 64)
+    assert cabi.device_status() == 0
+
+    def run(positions, block_table=None, table=64):
+        c = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in case.items()}
+        if block_table is not None:
+            c["block_table"] = block_table
+        dcache = pq_ops.PagedQuantizedKVCache(**{k: (v.to(cuda) if torch.is_tensor(v) else v) for k, v in c.items()})
+        layer_ops.rope_kv_append(qkv.to(cuda), cos[:table].to(cuda), sin[:table].to(cuda), positions.to(cuda), dcache, Hq)
+        return dcache
+
+    run(torch.tensor([0, 17, 40], dtype=torch.int32))
+    assert cabi.device_status() == 0
+    run(torch.tensor([0, 17, 40], dtype=torch.int32), table=32)   # position 40 is outside a 32-entry rotary table
+    assert cabi.device_status() == 6
+    bt = case["block_table"].clone()
+    bt[1, 1] = -1                                                  # position 17 of sequence 1 has no page
+    before = case["k_pages_q"].clone()
+    dcache = run(torch.tensor([0, 17, 40], dtype=torch.int32), bt)
+    assert cabi.device_status() == 7
+    assert cabi.device_status() == 0                               # reading with reset cleared it
+    # sequences 0 and 2 were appended, nothing else changed
+    changed = (dcache.k_pages_q.cpu() != before).flatten(1).any(dim=1).nonzero().flatten().tolist()
+    assert changed == sorted({int(case["block_table"][0, 0]), int(case["block_table"][2, 2])})
+
+
 def _tiny_stack(cuda, kv_bits, batch, positions):
     cfg = stack_mod.StackConfig(hidden=512, intermediate=1024, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128,
                                 vocab=97, bits=4, group_size=64, kv_bits=kv_bits, kv_group_size=32)
