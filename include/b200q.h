@@ -60,6 +60,7 @@ int b200q_device_status(int reset, void* stream);
  *   "gemv.stage_k", "gemv.stages", "gemv.interleave"   ring geometry / row dealing of the mma.sync kernel
  *   "ts.stages", "ts.smem_kb", "ts.split"               ring depth, shared-memory budget, K split of the tcgen05 kernel
  *   "attn.ctas_per_sm", "attn.min_pages"                grid sizing of the split-KV attention kernel
+ *   "attn.cluster"       1 = the one-kernel cluster form of the attention whenever it applies, -1 = never, 0 = small batches
  *   "attn.force_simple"  1 = always the one-warp-per-head attention kernel
  *   "no_pdl"             1 = launch without programmatic dependent launch */
 int b200q_set_tuning(const char* key, int value);
@@ -207,6 +208,27 @@ int b200q_rope_kv_append(const void* qkv, const float* cos_table, const float* s
                          int D, int page_size, int64_t num_pages, int max_blocks, int group_size, int table_len,
                          void* stream);
 
+/* b200q_rope_kv_append followed by b200q_paged_gqa_decode over the cache that now holds the new token, as one entry
+ * point: the attention stage of llama_layer_decode_step (ops/llama_layer_ops.py:262-330: reference_gqa_qkv_split_rope,
+ * cache update, GQA decode attention) on a paged quantized cache.  fp16 rows and fp16 cache scales.  For small batches
+ * (batch x kv heads up to a quarter of the SM count) the whole stage is ONE kernel: a thread-block cluster per
+ * (sequence, kv head) rotates q, appends the head's k / v to the page of positions[b], walks the sequence's pages and
+ * merges its partial results through distributed shared memory - no workspace traffic and no merge launch.  Larger
+ * batches run the two stages back to back; q_scratch [B, Hq, D] then receives the rotated queries (it may be NULL only
+ * when the one-kernel form is known to apply) and workspace is that of b200q_paged_gqa_decode.  lengths[b] must already
+ * count the new token (positions[b] + 1).  The result equals the two separate calls to within fp32 merge order. */
+int b200q_rope_append_paged_gqa_decode(const void* qkv, const float* cos_table, const float* sin_table,
+                                       const int32_t* positions, int table_len, int bits, uint8_t* k_codes, uint8_t* v_codes,
+                                       void* k_scales, void* v_scales, const int32_t* block_table, const int32_t* lengths,
+                                       void* out, void* q_scratch, void* workspace, size_t workspace_bytes, int B, int Hq,
+                                       int Hkv, int D, int page_size, int64_t num_pages, int max_blocks, int group_size,
+                                       float scale, void* stream);
+
+/* Kernel launches the attention stage takes on the current device for head_dim 128 / page size 16 caches: 1 when the
+ * cluster kernel applies (with or without the append), else 2 (split-KV + merge) plus 1 for the append.  For callers
+ * that report launch counts; no counterpart in the reference. */
+int b200q_attention_stage_launches(int B, int Hkv, int with_append);
+
 /* Symmetric group-wise quantisation of KV rows with the rule of the reference cache
  * (_quantize_group_symmetric_8 / _4, ops/paged_quantized_kv_ops.py:146-153, 168-175, as applied by quantize_kv_pages,
  * :194-292): per group of `group_size` values along D, scale = max(max|v|, 1e-8) / (127 | 7) in fp32 (stored fp16),
@@ -237,7 +259,8 @@ int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* co
  *             output, and its last CTA publishes the sequence number;
  *   in_slot:  the kernel's input `x` is this rank's view of that slot's full buffer; the kernel waits (bounded)
  *             for all source ranks before reading it.
- * Only the tensor-core matvec kernels and the split-KV attention kernels support this (B200Q_ERR_UNSUPPORTED
+ * b200q_rope_append_paged_gqa_decode honours out_slot as b200q_paged_gqa_decode does.
+ * Only the tensor-core matvec kernels and the split-KV / cluster attention kernels support this (B200Q_ERR_UNSUPPORTED
  * otherwise); batch rows <= 16.  The sharded result equals the unsharded one bit for bit. */
 int b200q_tp_register(int slot, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* counter,
                       int rank, int world);

@@ -81,7 +81,13 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
                  void* act_out, const void* residual_in, const void* norm_weight, float eps, void* z_out,
                  void* normed_out, int rows, int64_t N, int64_t K, int group_size, int act_dtype, int scale_dtype,
                  int norm_w_dtype, cudaStream_t stream);
+int rope_append_attention_impl(const void* qkv, const float* cos_table, const float* sin_table, const int32_t* positions,
+                               int table_len, int bits, uint8_t* k_codes, uint8_t* v_codes, void* k_scales, void* v_scales,
+                               const int32_t* block_table, const int32_t* lengths, void* out, void* q_scratch, void* workspace,
+                               size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages,
+                               int max_blocks, int group_size, float scale, cudaStream_t stream);
 size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int Hkv, int D);
+int attention_stage_launches_impl(int B, int Hkv, int with_append);
 size_t paged_gqa_static_scratch_bytes_impl();
 int paged_gqa_decode_static_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
                                  const void* k_scales, const void* v_scales, const int32_t* block_table,
@@ -421,6 +427,8 @@ int b200q_block_table_lookup(const int32_t* block_table, const int32_t* position
     return finish_launch();
 }
 
+int b200q_attention_stage_launches(int B, int Hkv, int with_append) { return attention_stage_launches_impl(B, Hkv, with_append); }
+
 size_t b200q_paged_gqa_workspace_bytes(int B, int Hq, int Hkv, int D) { return paged_gqa_workspace_bytes_impl(B, Hq, Hkv, D); }
 
 int b200q_paged_gqa_decode(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
@@ -449,6 +457,17 @@ int b200q_quantize_kv(int bits, const void* values, uint8_t* codes, void* scales
                       int in_dtype, void* stream) {
     tp_discard();
     return quantize_kv_impl(bits, values, codes, scales, rows, D, group_size, in_dtype, (cudaStream_t)stream);
+}
+
+int b200q_rope_append_paged_gqa_decode(const void* qkv, const float* cos_table, const float* sin_table,
+                                       const int32_t* positions, int table_len, int bits, uint8_t* k_codes, uint8_t* v_codes,
+                                       void* k_scales, void* v_scales, const int32_t* block_table, const int32_t* lengths,
+                                       void* out, void* q_scratch, void* workspace, size_t workspace_bytes, int B, int Hq,
+                                       int Hkv, int D, int page_size, int64_t num_pages, int max_blocks, int group_size,
+                                       float scale, void* stream) {
+    return rope_append_attention_impl(qkv, cos_table, sin_table, positions, table_len, bits, k_codes, v_codes, k_scales,
+                                      v_scales, block_table, lengths, out, q_scratch, workspace, workspace_bytes, B, Hq, Hkv, D,
+                                      page_size, num_pages, max_blocks, group_size, scale, (cudaStream_t)stream);
 }
 
 size_t b200q_paged_gqa_static_scratch_bytes(void) { return paged_gqa_static_scratch_bytes_impl(); }

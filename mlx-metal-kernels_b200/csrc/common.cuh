@@ -145,11 +145,12 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 constexpr uint32_t kTpSpinLimit = 1u << 22;   // acquire loads; each takes a fraction of a microsecond
 // Called by one whole warp of every CTA of the writer kernel after its stores: the last CTA publishes.
-__device__ __forceinline__ void tp_finish_writer(const TpOut& out, int lane) {
+__device__ __forceinline__ void tp_finish_writer(const TpOut& out, int lane, unsigned total_ctas = 0) {
+    if (total_ctas == 0) total_ctas = gridDim.x * gridDim.y;
     __threadfence_system();                      // this CTA's peer stores are visible before it is counted
     __syncwarp();
     unsigned last = 0;
-    if (lane == 0) last = (atomicAdd(out.counter, 1u) == gridDim.x * gridDim.y - 1u) ? 1u : 0u;
+    if (lane == 0) last = (atomicAdd(out.counter, 1u) == total_ctas - 1u) ? 1u : 0u;
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {
         __threadfence_system();

@@ -150,7 +150,7 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t h) { return __half2
 // BITS: code width.  LOGG: log2(group size) in {5, 6, 7}.  NB: tensor-core columns per quantisation group
 // (batch rows rounded up to 1, 2, 4, 8).  NT: column tiles (2 only with NB == 8: 9..16 batch rows).
 template <int BITS, int LOGG, int NB, int NT, bool GATE_UP>
-__global__ void __launch_bounds__(kThreads, 1) qgemv_kernel(const __grid_constant__ GemvParams p) {
+__global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MATS = GATE_UP ? 2 : 1;
     constexpr int G = 1 << LOGG;
@@ -820,7 +820,10 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     constexpr int LB = G * BITS / 32;
     constexpr int BC = NB * NT;
     const int sms = sm_count();
-    const uint32_t smem_cap = (uint32_t)max_smem_optin();
+    uint32_t smem_cap = (uint32_t)max_smem_optin();
+    if (kMinCtasPerSm > 1) smem_cap = std::min<uint32_t>(smem_cap, smem_cap / kMinCtasPerSm - 1024u);   // room for co-resident CTAs
+    const int cap_kb = tuning_get("gemv.smem_kb");
+    if (cap_kb > 0) smem_cap = std::min<uint32_t>(smem_cap, (uint32_t)cap_kb * 1024u);
 
     // k per stage: per-row copies of about 2 KB, a whole number of units
     int kc = tuning_get("gemv.stage_k");

@@ -19,6 +19,11 @@ constexpr int kProducerWarps = B200Q_GEMV_PRODUCERS;
 constexpr int kFirstProducerWarp = kConsumerWarps;
 constexpr int kEpilogueWarp = kConsumerWarps + kProducerWarps;
 constexpr int kThreads = (kConsumerWarps + kProducerWarps + 1) * 32;
+#ifndef B200Q_GEMV_MIN_CTAS
+#define B200Q_GEMV_MIN_CTAS 1
+#endif
+// CTAs of this kernel (or of two kernels of a dependent chain) that fit on one SM: bounds registers and shared memory.
+constexpr int kMinCtasPerSm = B200Q_GEMV_MIN_CTAS;
 constexpr int kTileRows = 16;
 constexpr int kUnitGroups = 8;
 constexpr uint32_t kWaitLimit = 1u << 21;

@@ -156,6 +156,254 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Per-warp building blocks shared by the split-KV kernel and the cluster kernel: a warp owns one kv head and
+// walks pages of it; every lane copies exactly the bytes IT will consume into a private ring slot.
+// ------------------------------------------------------------------------------------------------
+struct WarpAcc {
+    uint32_t qb[8][2];          // Q^T as B operand: [mma][b0b1, b2b3], column g = query head g of the group
+    float o[8][4];              // O^T tiles: rows d, cols heads
+    float m_run[2];             // running max of query heads 2t, 2t+1 of the group
+    float l_run[2];             // this lane's share (tokens g, g + 8 of every page) of their running sums
+};
+__device__ __forceinline__ void acc_reset(WarpAcc& a) {
+    a.m_run[0] = a.m_run[1] = -INFINITY;
+    a.l_run[0] = a.l_run[1] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a.o[i][e] = 0.0f;
+}
+// Q fragments of one kv head's group: row r of `qrows` (D halves apart) is query head r of the group (r < group <= 8).
+// qrows may point to global or shared memory.
+template <int BITS>
+__device__ __forceinline__ void load_q_frags(WarpAcc& a, const __half* qrows, int group, int g, int t) {
+    constexpr int D = 128;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint4 u = make_uint4(0, 0, 0, 0);
+        int d0;
+        if (BITS == 4) d0 = 32 * t + 8 * c;
+        else d0 = (c < 2 ? 16 * t + 8 * c : 64 + 16 * t + 8 * (c - 2));
+        if (g < group) u = *reinterpret_cast<const uint4*>(qrows + (size_t)g * D + d0);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};   // halves d0..d0+7
+        if (BITS == 4) {
+            // mma 2c: pairs (0,4) (1,5); mma 2c+1: pairs (2,6) (3,7)
+            a.qb[2 * c][0] = prmt(w[0], w[2], 0x5410);     a.qb[2 * c][1] = prmt(w[0], w[2], 0x7632);
+            a.qb[2 * c + 1][0] = prmt(w[1], w[3], 0x5410); a.qb[2 * c + 1][1] = prmt(w[1], w[3], 0x7632);
+        } else {
+            // mma 2c: codes 0..3 -> pairs (0,1) (2,3); mma 2c+1: codes 4..7
+            a.qb[2 * c][0] = w[0];     a.qb[2 * c][1] = w[1];
+            a.qb[2 * c + 1][0] = w[2]; a.qb[2 * c + 1][1] = w[3];
+        }
+    }
+}
+// Per-lane source offsets inside a page for kv head h.
+struct PageLanes {
+    uint32_t k_src0, k_src1, v_src[4], sc_src, sc_dst;
+    const __half* sc_base;      // lanes 0-15 copy K scales, lanes 16-31 V scales
+};
+template <int BITS>
+__device__ __forceinline__ PageLanes page_lanes(int lane, int h, uint32_t row_bytes, int scale_row_halves, int Gd,
+                                                const __half* k_scales, const __half* v_scales) {
+    constexpr int DP = BITS == 4 ? 64 : 128;
+    constexpr int K_BYTES = BITS == 4 ? 1024 : 2048;
+    const int g = lane >> 2, t = lane & 3;
+    PageLanes L;
+    L.k_src0 = (uint32_t)g * row_bytes + h * DP + 16 * t;            // token g
+    L.k_src1 = L.k_src0 + 8 * row_bytes;                             // token g + 8
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        L.v_src[i] = (uint32_t)(2 * t + (i & 1) + 8 * (i >> 1)) * row_bytes + h * DP + (BITS == 4 ? 8 : 16) * g;
+    L.sc_src = (uint32_t)(lane & 15) * scale_row_halves + h * Gd;    // halves
+    L.sc_dst = 2 * K_BYTES + (lane < 16 ? 0 : 128) + (lane & 15) * 8;
+    L.sc_base = lane < 16 ? k_scales : v_scales;
+    return L;
+}
+// Asynchronous copies of one page of kv head h into a ring slot (one commit group, also for a missing page).
+template <int BITS, int LOGG>
+__device__ __forceinline__ void issue_page(uint8_t* slot, const PageLanes& L, int lane, int page, int valid, const uint8_t* k_codes,
+                                           const uint8_t* v_codes, size_t page_code_bytes, size_t page_scale_halves) {
+    constexpr int K_BYTES = BITS == 4 ? 1024 : 2048;
+    const int g = lane >> 2, t = lane & 3;
+    if (page >= 0) {
+        const uint8_t* kbase = k_codes + (size_t)page * page_code_bytes;
+        const uint8_t* vbase = v_codes + (size_t)page * page_code_bytes;
+        if (BITS == 4) {
+            // K: 16 bytes of token g and of token g + 8 ; V: 8 bytes of tokens 2t, 2t+1, 2t+8, 2t+9
+            if (g < valid) cp_async_16(slot + lane * 16, kbase + L.k_src0);
+            if (g + 8 < valid) cp_async_16(slot + 512 + lane * 16, kbase + L.k_src1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
+                if (tok < valid) cp_async_8(slot + K_BYTES + i * 256 + lane * 8, vbase + L.v_src[i]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int tok = g + 8 * (i >> 1);
+                if (tok < valid)
+                    cp_async_16(slot + i * 512 + lane * 16, kbase + (i >> 1 ? L.k_src1 : L.k_src0) + 64 * (i & 1));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
+                if (tok < valid) cp_async_16(slot + K_BYTES + i * 512 + lane * 16, vbase + L.v_src[i]);
+            }
+        }
+        // scales of the 16 tokens for this head: lanes 0-15 K, lanes 16-31 V
+        if ((lane & 15) < valid) {
+            const __half* src = L.sc_base + (size_t)page * page_scale_halves + L.sc_src;
+            if (LOGG == 5) cp_async_8(slot + L.sc_dst, src);
+            else cp_async_4(slot + L.sc_dst, src);
+        }
+    }
+    cp_async_commit();
+}
+
+// One page of kv head h against the group's query heads: S = K Q^T on the tensor cores with the page's 16 tokens as
+// rows, online softmax in fp32, O^T += V^T P.  `valid` = tokens of the page below the length (what was copied),
+// `attended` = bit mask of the slots that take part.
+template <int BITS, int LOGG>
+__device__ __forceinline__ void process_page(WarpAcc& a, const uint8_t* slot, int valid, uint32_t attended, float sm_scale,
+                                             int lane) {
+    constexpr int K_BYTES = BITS == 4 ? 1024 : 2048;
+    constexpr int V_BYTES = K_BYTES;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+                const __half* ksc = reinterpret_cast<const __half*>(slot + K_BYTES + V_BYTES);         // [16][4]
+        const __half* vsc = ksc + 64;                                                             // [16][4]
+
+        // ---------------- S = K Q^T : rows = tokens g and g + 8, columns = query heads 2t, 2t+1 ----------
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (BITS == 4) {
+            const uint4 ua = *reinterpret_cast<const uint4*>(slot + lane * 16);          // token g
+            const uint4 ub = *reinterpret_cast<const uint4*>(slot + 512 + lane * 16);    // token g + 8
+            const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+            const uint32_t sa = half_dup(__habs(ksc[g * 4 + ((32 * t) >> LOGG)]));
+            const uint32_t sb = half_dup(__habs(ksc[(g + 8) * 4 + ((32 * t) >> LOGG)]));
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t wa2 = wa[c] >> 8, wb2 = wb[c] >> 8;
+                // exact (code - 8), then one rounding in the multiply: fp16((code-8)*s)
+                const uint32_t a0 = hmul2_u32(hsub2_u32(lop3_and_or(wa[c], 0x000F000Fu, 0x64006400u), 0x64086408u), sa);
+                const uint32_t a1 = hmul2_u32(hsub2_u32(lop3_and_or(wb[c], 0x000F000Fu, 0x64006400u), 0x64086408u), sb);
+                const uint32_t a2 = hmul2_u32(hsub2_u32(lop3_and_or(wa[c], 0x00F000F0u, 0x54005400u), 0x54805480u), sa);
+                const uint32_t a3 = hmul2_u32(hsub2_u32(lop3_and_or(wb[c], 0x00F000F0u, 0x54005400u), 0x54805480u), sb);
+                mma_m16n8k16(s, a0, a1, a2, a3, a.qb[2 * c][0], a.qb[2 * c][1]);
+                const uint32_t c0 = hmul2_u32(hsub2_u32(lop3_and_or(wa2, 0x000F000Fu, 0x64006400u), 0x64086408u), sa);
+                const uint32_t c1 = hmul2_u32(hsub2_u32(lop3_and_or(wb2, 0x000F000Fu, 0x64006400u), 0x64086408u), sb);
+                const uint32_t c2 = hmul2_u32(hsub2_u32(lop3_and_or(wa2, 0x00F000F0u, 0x54005400u), 0x54805480u), sa);
+                const uint32_t c3 = hmul2_u32(hsub2_u32(lop3_and_or(wb2, 0x00F000F0u, 0x54005400u), 0x54805480u), sb);
+                mma_m16n8k16(s, c0, c1, c2, c3, a.qb[2 * c + 1][0], a.qb[2 * c + 1][1]);
+            }
+        } else {
+#pragma unroll
+            for (int hb = 0; hb < 2; ++hb) {
+                const uint4 ua = *reinterpret_cast<const uint4*>(slot + hb * 512 + lane * 16);          // token g
+                const uint4 ub = *reinterpret_cast<const uint4*>(slot + (2 + hb) * 512 + lane * 16);    // token g + 8
+                const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+                const uint32_t sa = half_dup(__habs(ksc[g * 4 + ((64 * hb + 16 * t) >> LOGG)]));
+                const uint32_t sb = half_dup(__habs(ksc[(g + 8) * 4 + ((64 * hb + 16 * t) >> LOGG)]));
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t a0 = hmul2_u32(hsub2_u32(prmt(wa[c], 0x64646464u, 0x4140u), 0x64806480u), sa);
+                    const uint32_t a1 = hmul2_u32(hsub2_u32(prmt(wb[c], 0x64646464u, 0x4140u), 0x64806480u), sb);
+                    const uint32_t a2 = hmul2_u32(hsub2_u32(prmt(wa[c], 0x64646464u, 0x4342u), 0x64806480u), sa);
+                    const uint32_t a3 = hmul2_u32(hsub2_u32(prmt(wb[c], 0x64646464u, 0x4342u), 0x64806480u), sb);
+                    const int mi = 4 * hb + c;
+                    mma_m16n8k16(s, a0, a1, a2, a3, a.qb[mi][0], a.qb[mi][1]);
+                }
+            }
+        }
+        // ---------------- online softmax: this lane holds heads 2t, 2t+1 of tokens g and g + 8 ----------
+        float alpha[2];
+        uint32_t pb0, pb1;      // P[token][head] as the B operand of O^T += V^T P
+        {
+            // also discards whatever stale bytes sit in unused slots
+            const bool in0 = (attended >> g) & 1u, in1 = (attended >> (g + 8)) & 1u;
+            s[0] = in0 ? s[0] * sm_scale : -INFINITY;
+            s[1] = in0 ? s[1] * sm_scale : -INFINITY;
+            s[2] = in1 ? s[2] * sm_scale : -INFINITY;
+            s[3] = in1 ? s[3] * sm_scale : -INFINITY;
+            float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+            for (int o2 = 4; o2 < 32; o2 <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o2));
+            }
+            const float mn0 = fmaxf(a.m_run[0], mx0), mn1 = fmaxf(a.m_run[1], mx1);   // finite: every staged page has a valid token
+            alpha[0] = fast_exp2((a.m_run[0] - mn0) * kLog2e);                       // exp(-inf) = 0 on the first page
+            alpha[1] = fast_exp2((a.m_run[1] - mn1) * kLog2e);
+            const float p0 = fast_exp2((s[0] - mn0) * kLog2e), p1 = fast_exp2((s[1] - mn1) * kLog2e);
+            const float p2 = fast_exp2((s[2] - mn0) * kLog2e), p3 = fast_exp2((s[3] - mn1) * kLog2e);
+            // per-lane share of the sums (tokens g, g + 8); the 8 shares of a head are added when a partial is written
+            a.l_run[0] = a.l_run[0] * alpha[0] + (p0 + p2);
+            a.l_run[1] = a.l_run[1] * alpha[1] + (p1 + p3);
+            a.m_run[0] = mn0;
+            a.m_run[1] = mn1;
+            // transpose (token g, heads 2t, 2t+1) into (tokens 2t, 2t+1, head g): b0b1 tokens 0..7, b2b3 tokens 8..15
+            const __half2 x0 = __floats2half2_rn(p0, p1);
+            const __half2 x1 = __floats2half2_rn(p2, p3);
+            pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&x0));
+            pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&x1));
+        }
+        // ---------------- rescale O^T columns (heads 2t, 2t+1) ----------------------------------------------
+        if (__any_sync(0xffffffffu, (alpha[0] != 1.0f) || (alpha[1] != 1.0f))) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                a.o[i][0] *= alpha[0]; a.o[i][1] *= alpha[1]; a.o[i][2] *= alpha[0]; a.o[i][3] *= alpha[1];
+            }
+        }
+        // ---------------- O^T += V^T P ---------------------------------------------------------
+        const int vgrp = (16 * g) >> LOGG;
+        uint32_t vreg[2][16];   // [token pair][j]: (Vhat[tokA][16g + j], Vhat[tokB][16g + j])
+#pragma unroll
+        for (int tp = 0; tp < 2; ++tp) {
+            const int tokA = 2 * t + 8 * tp, tokB = tokA + 1;
+            // slots past the end of the sequence may hold anything: their weight is 0, make the value 0 too
+            const __half sA = tokA < valid ? __habs(vsc[tokA * 4 + vgrp]) : __ushort_as_half(0);
+            const __half sB = tokB < valid ? __habs(vsc[tokB * 4 + vgrp]) : __ushort_as_half(0);
+            const uint32_t s2 = (uint32_t)__half_as_ushort(sA) | ((uint32_t)__half_as_ushort(sB) << 16);
+            if (BITS == 4) {
+                const uint2 ua = *reinterpret_cast<const uint2*>(slot + K_BYTES + (2 * tp) * 256 + lane * 8);
+                const uint2 ub = *reinterpret_cast<const uint2*>(slot + K_BYTES + (2 * tp + 1) * 256 + lane * 8);
+                const uint32_t wa[2] = {ua.x, ua.y}, wb[2] = {ub.x, ub.y};
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    const uint32_t r0 = prmt(wa[w], wb[w], 0x5410);   // nibbles 0..3 of A | of B
+                    const uint32_t r1 = prmt(wa[w], wb[w], 0x7632);   // nibbles 4..7
+                    const uint32_t r0s = r0 >> 8, r1s = r1 >> 8;
+                    vreg[tp][8 * w + 0] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                    vreg[tp][8 * w + 1] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                    vreg[tp][8 * w + 2] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                    vreg[tp][8 * w + 3] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                    vreg[tp][8 * w + 4] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                    vreg[tp][8 * w + 5] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                    vreg[tp][8 * w + 6] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
+                    vreg[tp][8 * w + 7] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
+                }
+            } else {
+                const uint4 ua = *reinterpret_cast<const uint4*>(slot + K_BYTES + (2 * tp) * 512 + lane * 16);
+                const uint4 ub = *reinterpret_cast<const uint4*>(slot + K_BYTES + (2 * tp + 1) * 512 + lane * 16);
+                const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t e = prmt(wa[w], wb[w], 0x5140);   // A.b0 B.b0 A.b1 B.b1
+                    const uint32_t f2 = prmt(wa[w], wb[w], 0x7362);  // A.b2 B.b2 A.b3 B.b3
+                    vreg[tp][4 * w + 0] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4140u), 0x64806480u), s2);
+                    vreg[tp][4 * w + 1] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4342u), 0x64806480u), s2);
+                    vreg[tp][4 * w + 2] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4140u), 0x64806480u), s2);
+                    vreg[tp][4 * w + 3] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4342u), 0x64806480u), s2);
+                }
+            }
+        }
+        // tile i: row g <-> d = 16g + 2i, row g+8 <-> d = 16g + 2i + 1
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            mma_m16n8k16(a.o[i], vreg[0][2 * i], vreg[0][2 * i + 1], vreg[1][2 * i], vreg[1][2 * i + 1], pb0, pb1);
+}
+
 // Two shapes of the same kernel.  TWO = true: two CTAs per SM (16 warps hide more of the dequantisation
 // latency: 41 us against 45 us on the batch-16 q4 case) with the ring depth that still fits twice into shared
 // memory.  TWO = false: one CTA per SM with a deeper ring, for grids that do not fill the SMs twice anyway.
@@ -164,7 +412,6 @@ template <int BITS, int LOGG, bool TWO>
 __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged_attn_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int D = 128;
-    constexpr int DP = BITS == 4 ? 64 : 128;          // code bytes per head and token
     constexpr int K_BYTES = BITS == 4 ? 1024 : 2048;  // per page and head
     constexpr int V_BYTES = K_BYTES;
     const int warp = threadIdx.x >> 5;
@@ -197,10 +444,8 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
     uint8_t* my_ring = smem + p.off_ring + (size_t)warp * NS * SLOT;
     const int n_my = hi - lo;                                     // pages this warp walks: f = lo + j
 
-    uint32_t qb[8][2];          // Q^T as B operand: [mma][b0b1, b2b3], column g = query head g of the group
-    float o[8][4];              // O^T tiles: rows d, cols heads
-    float m_run[2] = {-INFINITY, -INFINITY};    // running max of query heads 2t, 2t+1 of the group
-    float l_run[2] = {0.0f, 0.0f};              // this lane's share (tokens g, g + 8 of every page) of their running sums
+    WarpAcc acc;
+    acc_reset(acc);
     int cur_b = -1;
 
     // Page descriptors (page id, sequence, valid tokens) of 32 consecutive pages of this warp, one per
@@ -226,18 +471,8 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
     };
     Desc win_c = lookup(0);     // consume window
     Desc win_i = win_c;         // issue window
-    // per-lane source offsets inside a page (bytes) and destination offsets inside a slot
-    const uint32_t row_bytes = (uint32_t)p.row_bytes;
-    const uint32_t k_src0 = (uint32_t)g * row_bytes + h * DP + 16 * t;            // token g
-    const uint32_t k_src1 = k_src0 + 8 * row_bytes;                               // token g + 8
-    uint32_t v_src[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-        v_src[i] = (uint32_t)(2 * t + (i & 1) + 8 * (i >> 1)) * row_bytes + h * DP + (BITS == 4 ? 8 : 16) * g;
-    const uint32_t sc_src = (uint32_t)(lane & 15) * p.scale_row_halves + h * p.Gd;  // halves
-    const uint32_t sc_dst = K_BYTES + V_BYTES + (lane < 16 ? 0 : 128) + (lane & 15) * 8;
-    const __half* sc_base = lane < 16 ? p.k_scales : p.v_scales;
-    const size_t page_code_bytes = (size_t)p.P * row_bytes;
+    const PageLanes L = page_lanes<BITS>(lane, h, (uint32_t)p.row_bytes, p.scale_row_halves, p.Gd, p.k_scales, p.v_scales);
+    const size_t page_code_bytes = (size_t)p.P * p.row_bytes;
     const size_t page_scale_halves = (size_t)p.P * p.scale_row_halves;
     int slot_i = 0;      // ring slot of the next page to issue
     // issue the asynchronous copies of page j (descriptor held by lane j % 32 of the issue window)
@@ -246,46 +481,14 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
         const int src_lane = j & 31;
         const int page = __shfl_sync(0xffffffffu, win_i.page, src_lane);
         const int valid = __shfl_sync(0xffffffffu, win_i.valid, src_lane) & 0xFFFF;
-        if (page >= 0) {
-            uint8_t* slot = my_ring + slot_i * SLOT;
-            const uint8_t* kbase = p.k_codes + (size_t)page * page_code_bytes;
-            const uint8_t* vbase = p.v_codes + (size_t)page * page_code_bytes;
-            if (BITS == 4) {
-                // K: 16 bytes of token g and of token g + 8 ; V: 8 bytes of tokens 2t, 2t+1, 2t+8, 2t+9
-                if (g < valid) cp_async_16(slot + lane * 16, kbase + k_src0);
-                if (g + 8 < valid) cp_async_16(slot + 512 + lane * 16, kbase + k_src1);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
-                    if (tok < valid) cp_async_8(slot + K_BYTES + i * 256 + lane * 8, vbase + v_src[i]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int tok = g + 8 * (i >> 1);
-                    if (tok < valid)
-                        cp_async_16(slot + i * 512 + lane * 16, kbase + (i >> 1 ? k_src1 : k_src0) + 64 * (i & 1));
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
-                    if (tok < valid) cp_async_16(slot + K_BYTES + i * 512 + lane * 16, vbase + v_src[i]);
-                }
-            }
-            // scales of the 16 tokens for this head: lanes 0-15 K, lanes 16-31 V
-            if ((lane & 15) < valid) {
-                const __half* src = sc_base + (size_t)page * page_scale_halves + sc_src;
-                if (LOGG == 5) cp_async_8(slot + sc_dst, src);
-                else cp_async_4(slot + sc_dst, src);
-            }
-        }
-        cp_async_commit();
+        issue_page<BITS, LOGG>(my_ring + slot_i * SLOT, L, lane, page, valid, p.k_codes, p.v_codes, page_code_bytes,
+                               page_scale_halves);
         slot_i = (slot_i + 1 == NS) ? 0 : slot_i + 1;
     };
 
     auto flush = [&](int b) {
         float* dst = p.partial + ((size_t)(vc + b) * p.Hq) * (D + 2);
-        float l0 = l_run[0], l1 = l_run[1];
+        float l0 = acc.l_run[0], l1 = acc.l_run[1];
 #pragma unroll
         for (int o2 = 4; o2 < 32; o2 <<= 1) {
             l0 += __shfl_xor_sync(0xffffffffu, l0, o2);
@@ -298,7 +501,7 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
             for (int e = 0; e < 4; ++e) {
                 const int head = 2 * t + (e & 1);
                 const int d = 16 * g + 2 * i + (e >> 1);
-                if (head < group) dst[(size_t)(h * group + head) * (D + 2) + d] = o[i][e];
+                if (head < group) dst[(size_t)(h * group + head) * (D + 2) + d] = acc.o[i][e];
             }
         }
         if (g == 0) {
@@ -306,7 +509,7 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
             for (int e = 0; e < 2; ++e) {
                 const int head = 2 * t + e;
                 if (head < group) {
-                    dst[(size_t)(h * group + head) * (D + 2) + D] = m_run[e];
+                    dst[(size_t)(h * group + head) * (D + 2) + D] = acc.m_run[e];
                     dst[(size_t)(h * group + head) * (D + 2) + D + 1] = e ? l1 : l0;
                 }
             }
@@ -336,170 +539,278 @@ __global__ void __launch_bounds__(kAttnThreads, TWO ? B200Q_ATTN_CTAS : 1) paged
         if (b != cur_b) {
             if (cur_b >= 0) flush(cur_b);
             cur_b = b;
-            m_run[0] = m_run[1] = -INFINITY;
-            l_run[0] = l_run[1] = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) o[i][e] = 0.0f;
-            // Q fragments for (b, kv head h): column r of the tile is query head h*group + r (r < group <= 8)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint4 u = make_uint4(0, 0, 0, 0);
-                int d0;
-                if (BITS == 4) d0 = 32 * t + 8 * c;
-                else d0 = (c < 2 ? 16 * t + 8 * c : 64 + 16 * t + 8 * (c - 2));
-                if (g < group) u = *reinterpret_cast<const uint4*>(p.q + ((size_t)b * p.Hq + h * group + g) * D + d0);
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};   // halves d0..d0+7
-                if (BITS == 4) {
-                    // mma 2c: pairs (0,4) (1,5); mma 2c+1: pairs (2,6) (3,7)
-                    qb[2 * c][0] = prmt(w[0], w[2], 0x5410);     qb[2 * c][1] = prmt(w[0], w[2], 0x7632);
-                    qb[2 * c + 1][0] = prmt(w[1], w[3], 0x5410); qb[2 * c + 1][1] = prmt(w[1], w[3], 0x7632);
-                } else {
-                    // mma 2c: codes 0..3 -> pairs (0,1) (2,3); mma 2c+1: codes 4..7
-                    qb[2 * c][0] = w[0];     qb[2 * c][1] = w[1];
-                    qb[2 * c + 1][0] = w[2]; qb[2 * c + 1][1] = w[3];
-                }
-            }
+            acc_reset(acc);
+            load_q_frags<BITS>(acc, p.q + ((size_t)b * p.Hq + h * group) * D, group, g, t);
         }
-        if (page >= 0) {
-            const uint8_t* slot = my_ring + slot_c * SLOT;
-            const __half* ksc = reinterpret_cast<const __half*>(slot + K_BYTES + V_BYTES);         // [16][4]
-            const __half* vsc = ksc + 64;                                                             // [16][4]
-
-            // ---------------- S = K Q^T : rows = tokens g and g + 8, columns = query heads 2t, 2t+1 ----------
-            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (BITS == 4) {
-                const uint4 ua = *reinterpret_cast<const uint4*>(slot + lane * 16);          // token g
-                const uint4 ub = *reinterpret_cast<const uint4*>(slot + 512 + lane * 16);    // token g + 8
-                const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
-                const uint32_t sa = half_dup(__habs(ksc[g * 4 + ((32 * t) >> LOGG)]));
-                const uint32_t sb = half_dup(__habs(ksc[(g + 8) * 4 + ((32 * t) >> LOGG)]));
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t wa2 = wa[c] >> 8, wb2 = wb[c] >> 8;
-                    // exact (code - 8), then one rounding in the multiply: fp16((code-8)*s)
-                    const uint32_t a0 = hmul2_u32(hsub2_u32(lop3_and_or(wa[c], 0x000F000Fu, 0x64006400u), 0x64086408u), sa);
-                    const uint32_t a1 = hmul2_u32(hsub2_u32(lop3_and_or(wb[c], 0x000F000Fu, 0x64006400u), 0x64086408u), sb);
-                    const uint32_t a2 = hmul2_u32(hsub2_u32(lop3_and_or(wa[c], 0x00F000F0u, 0x54005400u), 0x54805480u), sa);
-                    const uint32_t a3 = hmul2_u32(hsub2_u32(lop3_and_or(wb[c], 0x00F000F0u, 0x54005400u), 0x54805480u), sb);
-                    mma_m16n8k16(s, a0, a1, a2, a3, qb[2 * c][0], qb[2 * c][1]);
-                    const uint32_t c0 = hmul2_u32(hsub2_u32(lop3_and_or(wa2, 0x000F000Fu, 0x64006400u), 0x64086408u), sa);
-                    const uint32_t c1 = hmul2_u32(hsub2_u32(lop3_and_or(wb2, 0x000F000Fu, 0x64006400u), 0x64086408u), sb);
-                    const uint32_t c2 = hmul2_u32(hsub2_u32(lop3_and_or(wa2, 0x00F000F0u, 0x54005400u), 0x54805480u), sa);
-                    const uint32_t c3 = hmul2_u32(hsub2_u32(lop3_and_or(wb2, 0x00F000F0u, 0x54005400u), 0x54805480u), sb);
-                    mma_m16n8k16(s, c0, c1, c2, c3, qb[2 * c + 1][0], qb[2 * c + 1][1]);
-                }
-            } else {
-#pragma unroll
-                for (int hb = 0; hb < 2; ++hb) {
-                    const uint4 ua = *reinterpret_cast<const uint4*>(slot + hb * 512 + lane * 16);          // token g
-                    const uint4 ub = *reinterpret_cast<const uint4*>(slot + (2 + hb) * 512 + lane * 16);    // token g + 8
-                    const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
-                    const uint32_t sa = half_dup(__habs(ksc[g * 4 + ((64 * hb + 16 * t) >> LOGG)]));
-                    const uint32_t sb = half_dup(__habs(ksc[(g + 8) * 4 + ((64 * hb + 16 * t) >> LOGG)]));
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint32_t a0 = hmul2_u32(hsub2_u32(prmt(wa[c], 0x64646464u, 0x4140u), 0x64806480u), sa);
-                        const uint32_t a1 = hmul2_u32(hsub2_u32(prmt(wb[c], 0x64646464u, 0x4140u), 0x64806480u), sb);
-                        const uint32_t a2 = hmul2_u32(hsub2_u32(prmt(wa[c], 0x64646464u, 0x4342u), 0x64806480u), sa);
-                        const uint32_t a3 = hmul2_u32(hsub2_u32(prmt(wb[c], 0x64646464u, 0x4342u), 0x64806480u), sb);
-                        const int mi = 4 * hb + c;
-                        mma_m16n8k16(s, a0, a1, a2, a3, qb[mi][0], qb[mi][1]);
-                    }
-                }
-            }
-            // ---------------- online softmax: this lane holds heads 2t, 2t+1 of tokens g and g + 8 ----------
-            float alpha[2];
-            uint32_t pb0, pb1;      // P[token][head] as the B operand of O^T += V^T P
-            {
-                // also discards whatever stale bytes sit in unused slots
-                const bool in0 = (attended >> g) & 1u, in1 = (attended >> (g + 8)) & 1u;
-                s[0] = in0 ? s[0] * sm_scale : -INFINITY;
-                s[1] = in0 ? s[1] * sm_scale : -INFINITY;
-                s[2] = in1 ? s[2] * sm_scale : -INFINITY;
-                s[3] = in1 ? s[3] * sm_scale : -INFINITY;
-                float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
-#pragma unroll
-                for (int o2 = 4; o2 < 32; o2 <<= 1) {
-                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o2));
-                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o2));
-                }
-                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);   // finite: every staged page has a valid token
-                alpha[0] = fast_exp2((m_run[0] - mn0) * kLog2e);                       // exp(-inf) = 0 on the first page
-                alpha[1] = fast_exp2((m_run[1] - mn1) * kLog2e);
-                const float p0 = fast_exp2((s[0] - mn0) * kLog2e), p1 = fast_exp2((s[1] - mn1) * kLog2e);
-                const float p2 = fast_exp2((s[2] - mn0) * kLog2e), p3 = fast_exp2((s[3] - mn1) * kLog2e);
-                // per-lane share of the sums (tokens g, g + 8); the 8 shares of a head are added when a partial is written
-                l_run[0] = l_run[0] * alpha[0] + (p0 + p2);
-                l_run[1] = l_run[1] * alpha[1] + (p1 + p3);
-                m_run[0] = mn0;
-                m_run[1] = mn1;
-                // transpose (token g, heads 2t, 2t+1) into (tokens 2t, 2t+1, head g): b0b1 tokens 0..7, b2b3 tokens 8..15
-                const __half2 x0 = __floats2half2_rn(p0, p1);
-                const __half2 x1 = __floats2half2_rn(p2, p3);
-                pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&x0));
-                pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&x1));
-            }
-            // ---------------- rescale O^T columns (heads 2t, 2t+1) ----------------------------------------------
-            if (__any_sync(0xffffffffu, (alpha[0] != 1.0f) || (alpha[1] != 1.0f))) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    o[i][0] *= alpha[0]; o[i][1] *= alpha[1]; o[i][2] *= alpha[0]; o[i][3] *= alpha[1];
-                }
-            }
-            // ---------------- O^T += V^T P ---------------------------------------------------------
-            const int vgrp = (16 * g) >> LOGG;
-            uint32_t vreg[2][16];   // [token pair][j]: (Vhat[tokA][16g + j], Vhat[tokB][16g + j])
-#pragma unroll
-            for (int tp = 0; tp < 2; ++tp) {
-                const int tokA = 2 * t + 8 * tp, tokB = tokA + 1;
-                // slots past the end of the sequence may hold anything: their weight is 0, make the value 0 too
-                const __half sA = tokA < valid ? __habs(vsc[tokA * 4 + vgrp]) : __ushort_as_half(0);
-                const __half sB = tokB < valid ? __habs(vsc[tokB * 4 + vgrp]) : __ushort_as_half(0);
-                const uint32_t s2 = (uint32_t)__half_as_ushort(sA) | ((uint32_t)__half_as_ushort(sB) << 16);
-                if (BITS == 4) {
-                    const uint2 ua = *reinterpret_cast<const uint2*>(slot + K_BYTES + (2 * tp) * 256 + lane * 8);
-                    const uint2 ub = *reinterpret_cast<const uint2*>(slot + K_BYTES + (2 * tp + 1) * 256 + lane * 8);
-                    const uint32_t wa[2] = {ua.x, ua.y}, wb[2] = {ub.x, ub.y};
-#pragma unroll
-                    for (int w = 0; w < 2; ++w) {
-                        const uint32_t r0 = prmt(wa[w], wb[w], 0x5410);   // nibbles 0..3 of A | of B
-                        const uint32_t r1 = prmt(wa[w], wb[w], 0x7632);   // nibbles 4..7
-                        const uint32_t r0s = r0 >> 8, r1s = r1 >> 8;
-                        vreg[tp][8 * w + 0] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                        vreg[tp][8 * w + 1] = hmul2_u32(hsub2_u32(lop3_and_or(r0, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                        vreg[tp][8 * w + 2] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                        vreg[tp][8 * w + 3] = hmul2_u32(hsub2_u32(lop3_and_or(r0s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                        vreg[tp][8 * w + 4] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                        vreg[tp][8 * w + 5] = hmul2_u32(hsub2_u32(lop3_and_or(r1, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                        vreg[tp][8 * w + 6] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x000F000Fu, 0x64006400u), 0x64086408u), s2);
-                        vreg[tp][8 * w + 7] = hmul2_u32(hsub2_u32(lop3_and_or(r1s, 0x00F000F0u, 0x54005400u), 0x54805480u), s2);
-                    }
-                } else {
-                    const uint4 ua = *reinterpret_cast<const uint4*>(slot + K_BYTES + (2 * tp) * 512 + lane * 16);
-                    const uint4 ub = *reinterpret_cast<const uint4*>(slot + K_BYTES + (2 * tp + 1) * 512 + lane * 16);
-                    const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        const uint32_t e = prmt(wa[w], wb[w], 0x5140);   // A.b0 B.b0 A.b1 B.b1
-                        const uint32_t f2 = prmt(wa[w], wb[w], 0x7362);  // A.b2 B.b2 A.b3 B.b3
-                        vreg[tp][4 * w + 0] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4140u), 0x64806480u), s2);
-                        vreg[tp][4 * w + 1] = hmul2_u32(hsub2_u32(prmt(e, 0x64646464u, 0x4342u), 0x64806480u), s2);
-                        vreg[tp][4 * w + 2] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4140u), 0x64806480u), s2);
-                        vreg[tp][4 * w + 3] = hmul2_u32(hsub2_u32(prmt(f2, 0x64646464u, 0x4342u), 0x64806480u), s2);
-                    }
-                }
-            }
-            // tile i: row g <-> d = 16g + 2i, row g+8 <-> d = 16g + 2i + 1
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                mma_m16n8k16(o[i], vreg[0][2 * i], vreg[0][2 * i + 1], vreg[1][2 * i], vreg[1][2 * i + 1], pb0, pb1);
-        }
+        if (page >= 0) process_page<BITS, LOGG>(acc, my_ring + slot_c * SLOT, valid, attended, sm_scale, lane);
         __syncwarp();   // every lane is done with this slot before it is refilled
         slot_c = (slot_c + 1 == NS) ? 0 : slot_c + 1;
     }
     if (cur_b >= 0) flush(cur_b);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Cluster kernel for small batches: one thread-block cluster per (sequence, kv head), no partials in global memory
+// and no merge launch.  The CTAs of the cluster cut the sequence's pages into equal ranges, the 8 warps of a CTA cut
+// their range again; a warp walks its pages exactly as in the split-KV kernel.  The warps' partial (max, sum,
+// accumulator) triples are merged in shared memory, the CTAs' through distributed shared memory by the cluster's
+// first CTA, always in the same order (bitwise repeatable, and independent of how many kv heads a tensor-parallel
+// shard holds).  Optionally the kernel also does what precedes attention in a decode layer - split the fused QKV
+// row, rotate q and k, quantise and append the new token's k / v to its page: the CTA that walks the page of the
+// new position appends kv head h itself before it reads that page, every CTA rotates its own copy of q.
+// ------------------------------------------------------------------------------------------------
+struct ClusterAttnParams {
+    const __half* q;            // [B, Hq, D] rotated queries (fused == 0)
+    const __half* qkv;          // fused: [B, (Hq + 2 Hkv) * D]
+    const float* cos_table;     // fused: [table_len, D/2]
+    const float* sin_table;
+    const int32_t* positions;   // fused: [B]
+    uint8_t* k_codes;
+    uint8_t* v_codes;
+    __half* k_scales;
+    __half* v_scales;
+    const int32_t* block_table;
+    const int32_t* lengths;
+    void* out;                  // [B, Hq, D]
+    int B, Hq, Hkv, P, max_blocks, G, Gd, group, bits, table_len, fused, S;
+    int64_t num_pages;
+    float scale;
+    int row_bytes, scale_row_halves;
+    uint32_t off_q, off_wpart, off_cpart, off_ring;
+    TpOut tp_out;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+template <int BITS, int LOGG>
+__global__ void __launch_bounds__(kAttnThreads, 1) paged_attn_cluster_kernel(const __grid_constant__ ClusterAttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int D = 128;
+    constexpr int K_BYTES = BITS == 4 ? 1024 : 2048;
+    constexpr int V_BYTES = K_BYTES;
+    constexpr int NS = BITS == 4 ? 8 : 5;                         // pages in flight per warp
+    constexpr int SLOT = K_BYTES + V_BYTES + 256;
+    constexpr int PW = D + 2;                                     // floats of one partial: accumulator, max, sum
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t rank = cluster_rank_x();
+    const int h = blockIdx.y;
+    const int b = blockIdx.z;
+    const int group = p.group;
+    const int S = p.S;
+    __half* qs = reinterpret_cast<__half*>(smem + p.off_q);              // [group][D] rotated query rows
+    float* wpart = reinterpret_cast<float*>(smem + p.off_wpart);         // [8 warps][group][PW]
+    float* cpart = reinterpret_cast<float*>(smem + p.off_cpart);         // [S][group][PW] (used in the first CTA)
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const int L = clamp_len(p.lengths[b], p.max_blocks * p.P);
+    const int n_pages = (L + p.P - 1) / p.P;
+    const int ppc = (n_pages + S - 1) / S;                               // pages per CTA
+    const int c_lo = min(n_pages, (int)rank * ppc), c_hi = min(n_pages, c_lo + ppc);
+    const int ppw = (c_hi - c_lo + kAttnWarps - 1) / kAttnWarps;         // pages per warp
+    const int lo = min(c_hi, c_lo + warp * ppw), hi = min(c_hi, lo + ppw);
+
+    if (p.fused) {
+        const int heads = p.Hq + 2 * p.Hkv;
+        const int pos = p.positions[b];
+        const bool pos_ok = pos >= 0 && pos < p.table_len;
+        const int d0 = lane * 4;
+        const __half* row = p.qkv + (size_t)b * heads * D;
+        auto load4 = [&](int head, float (&v)[4]) {
+            const uint2 u = *reinterpret_cast<const uint2*>(row + (size_t)head * D + d0);
+            const __half2 h0 = *reinterpret_cast<const __half2*>(&u.x), h1 = *reinterpret_cast<const __half2*>(&u.y);
+            v[0] = __low2float(h0); v[1] = __high2float(h0); v[2] = __low2float(h1); v[3] = __high2float(h1);
+        };
+        auto rope4 = [&](float (&v)[4]) {
+            if (!pos_ok) return;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float c = p.cos_table[(size_t)pos * (D / 2) + d0 / 2 + i];
+                const float sn = p.sin_table[(size_t)pos * (D / 2) + d0 / 2 + i];
+                const float xe = v[2 * i], xo = v[2 * i + 1];
+                // two separately rounded products and one sum, as the reference's elementwise expression
+                v[2 * i] = __fsub_rn(__fmul_rn(xe, c), __fmul_rn(xo, sn));
+                v[2 * i + 1] = __fadd_rn(__fmul_rn(xe, sn), __fmul_rn(xo, c));
+            }
+        };
+        if (!pos_ok && threadIdx.x == 0) atomicMax(&g_device_status, (int)EV_ROPE_POSITION);
+        // rotated query rows of this kv head's group, one warp per query head
+        if (warp < group) {
+            float v[4];
+            load4(h * group + warp, v);
+            rope4(v);
+            const __half2 a0 = __floats2half2_rn(v[0], v[1]), a1 = __floats2half2_rn(v[2], v[3]);
+            uint2 o2;
+            o2.x = *reinterpret_cast<const uint32_t*>(&a0);
+            o2.y = *reinterpret_cast<const uint32_t*>(&a1);
+            *reinterpret_cast<uint2*>(qs + (size_t)warp * D + d0) = o2;
+        }
+        // append k (rotated) and v of kv head h to the page of `pos`: the CTA whose range holds that page
+        const int blk = pos >= 0 ? pos / p.P : -1;
+        const int owner = (ppc > 0 && blk >= 0) ? min(S - 1, blk / ppc) : 0;
+        if ((int)rank == owner && warp >= 6) {
+            const bool is_v = warp == 7;
+            int page = (blk >= 0 && blk < p.max_blocks) ? p.block_table[(size_t)b * p.max_blocks + blk] : -1;
+            if (page < 0 || page >= p.num_pages) {
+                if (lane == 0) atomicMax(&g_device_status, (int)EV_KV_PAGE_UNASSIGNED);
+            } else {
+                float v[4];
+                load4(p.Hq + (is_v ? p.Hkv : 0) + h, v);
+                if (!is_v) rope4(v);
+                __half hv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { hv[i] = __float2half_rn(v[i]); v[i] = __half2float(hv[i]); }
+                float mx = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+                const int lanes_per_group = p.G / 4;
+                for (int o2 = 1; o2 < lanes_per_group; o2 <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+                const float limit = BITS == 8 ? 127.0f : 7.0f;
+                const float offset = BITS == 8 ? 128.0f : 8.0f;
+                const float sc = __fdiv_rn(fmaxf(mx, 1e-8f), limit);
+                uint32_t codes[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    codes[i] = (uint32_t)(int)(fminf(fmaxf(rintf(__fdiv_rn(v[i], sc)), -limit), limit) + offset);
+                const size_t tok = ((size_t)page * p.P + (pos % p.P)) * p.Hkv + h;
+                uint8_t* cdst = is_v ? p.v_codes : p.k_codes;
+                __half* sdst = is_v ? p.v_scales : p.k_scales;
+                if (BITS == 8)
+                    *reinterpret_cast<uint32_t*>(cdst + tok * D + d0) = codes[0] | (codes[1] << 8) | (codes[2] << 16) | (codes[3] << 24);
+                else
+                    *reinterpret_cast<uint16_t*>(cdst + tok * (D / 2) + d0 / 2) =
+                        (uint16_t)(codes[0] | (codes[1] << 4) | (codes[2] << 8) | (codes[3] << 12));
+                if ((lane % lanes_per_group) == 0) sdst[tok * p.Gd + d0 / p.G] = __float2half_rn(sc);
+            }
+            __threadfence();          // the appended bytes are in global memory before this CTA's copies read the page
+        }
+        __syncthreads();
+    }
+
+    // ---- this warp's pages ----
+    WarpAcc acc;
+    acc_reset(acc);
+    const int n_my = hi - lo;
+    if (n_my > 0) {
+        const __half* qrows = p.fused ? qs : p.q + ((size_t)b * p.Hq + h * group) * D;
+        load_q_frags<BITS>(acc, qrows, group, g, t);
+        const PageLanes Lp = page_lanes<BITS>(lane, h, (uint32_t)p.row_bytes, p.scale_row_halves, p.Gd, p.k_scales, p.v_scales);
+        const size_t page_code_bytes = (size_t)p.P * p.row_bytes;
+        const size_t page_scale_halves = (size_t)p.P * p.scale_row_halves;
+        uint8_t* my_ring = smem + p.off_ring + (size_t)warp * NS * SLOT;
+        auto page_of = [&](int j) -> int {
+            int page = p.block_table[(size_t)b * p.max_blocks + lo + j];
+            return (page < 0 || page >= p.num_pages) ? -1 : page;
+        };
+        auto valid_of = [&](int j) -> int { return min(p.P, L - (lo + j) * p.P); };
+        int slot_i = 0, slot_c = 0;
+        for (int j = 0; j < NS - 1; ++j) {
+            if (j < n_my) issue_page<BITS, LOGG>(my_ring + slot_i * SLOT, Lp, lane, page_of(j), valid_of(j), p.k_codes, p.v_codes,
+                                                 page_code_bytes, page_scale_halves);
+            else cp_async_commit();
+            slot_i = (slot_i + 1 == NS) ? 0 : slot_i + 1;
+        }
+        for (int j = 0; j < n_my; ++j) {
+            if (j + NS - 1 < n_my)
+                issue_page<BITS, LOGG>(my_ring + slot_i * SLOT, Lp, lane, page_of(j + NS - 1), valid_of(j + NS - 1), p.k_codes,
+                                       p.v_codes, page_code_bytes, page_scale_halves);
+            else cp_async_commit();
+            slot_i = (slot_i + 1 == NS) ? 0 : slot_i + 1;
+            cp_async_wait<NS - 1>();
+            __syncwarp();
+            const int valid = valid_of(j);
+            const uint32_t attended = valid >= 16 ? 0xFFFFu : ((1u << max(valid, 0)) - 1u);
+            if (page_of(j) >= 0) process_page<BITS, LOGG>(acc, my_ring + slot_c * SLOT, valid, attended, p.scale, lane);
+            __syncwarp();
+            slot_c = (slot_c + 1 == NS) ? 0 : slot_c + 1;
+        }
+    }
+    // ---- the warp's partial: O^T[d][head] with thread (g,t) holding d = 16g + 2i (+1), heads 2t, 2t+1 ----
+    {
+        float l0 = acc.l_run[0], l1 = acc.l_run[1];
+#pragma unroll
+        for (int o2 = 4; o2 < 32; o2 <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, o2);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, o2);
+        }
+        float* dst = wpart + (size_t)warp * group * PW;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int head = 2 * t + (e & 1);
+                if (head < group) dst[head * PW + 16 * g + 2 * i + (e >> 1)] = acc.o[i][e];
+            }
+        if (g == 0) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int head = 2 * t + e;
+                if (head < group) {
+                    dst[head * PW + D] = acc.m_run[e];
+                    dst[head * PW + D + 1] = e ? l1 : l0;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // ---- merge the 8 warps (fixed order) into this CTA's partial; thread -> (head, d) ----
+    auto merge = [&](const float* src, int n, int head, int d, float& m_tot, float& l_tot) -> float {
+        m_tot = -INFINITY;
+        for (int i = 0; i < n; ++i) m_tot = fmaxf(m_tot, src[((size_t)i * group + head) * PW + D]);
+        float accv = 0.0f;
+        l_tot = 0.0f;
+        for (int i = 0; i < n; ++i) {
+            const float* ps = src + ((size_t)i * group + head) * PW;
+            const float m = ps[D];
+            const float w = m == -INFINITY ? 0.0f : exp2f((m - m_tot) * kLog2e);
+            accv = fmaf(w, ps[d], accv);
+            l_tot = fmaf(w, ps[D + 1], l_tot);
+        }
+        return accv;
+    };
+    const uint32_t cpart_u = smem_u32(cpart);
+    for (int idx = threadIdx.x; idx < group * D; idx += kAttnThreads) {
+        const int head = idx / D, d = idx - head * D;
+        float m_tot, l_tot;
+        const float v = merge(wpart, kAttnWarps, head, d, m_tot, l_tot);
+        // slot `rank` of the first CTA's table (its own slot for the first CTA itself)
+        const uint32_t base = cpart_u + (uint32_t)((rank * group + head) * PW) * 4u;
+        auto put = [&](uint32_t off, float val) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(base + off * 4u), "r"(0));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(val) : "memory");
+        };
+        put((uint32_t)d, v);
+        if (d == 0) { put((uint32_t)D, m_tot); put((uint32_t)D + 1, l_tot); }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank == 0) {
+        for (int idx = threadIdx.x; idx < group * D; idx += kAttnThreads) {
+            const int head = idx / D, d = idx - head * D;
+            float m_tot, l_tot;
+            const float v = merge(cpart, S, head, d, m_tot, l_tot);
+            const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+            const unsigned short bits16 = __half_as_ushort(__float2half_rn(v * inv));
+            const int hq = h * group + head;
+            if (p.out != nullptr) reinterpret_cast<unsigned short*>(p.out)[((size_t)b * p.Hq + hq) * D + d] = bits16;
+            if (p.tp_out.world > 0) {
+                const size_t of = ((size_t)b * p.tp_out.world + p.tp_out.rank) * p.Hq * D + (size_t)hq * D + d;
+#pragma unroll 1
+                for (int peer = 0; peer < p.tp_out.world; ++peer)
+                    reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
+            }
+        }
+    }
+    if (p.tp_out.world > 0) {
+        __syncthreads();                         // all of this CTA's peer stores are issued
+        if (warp == 0) tp_finish_writer(p.tp_out, lane, gridDim.x * gridDim.y * gridDim.z);
+    }
 }
 
 // Merges the partials of every (sequence, query head): one warp each, lanes over d.
@@ -695,7 +1006,75 @@ __global__ void __launch_bounds__(128) paged_attn_simple_kernel(const __grid_con
 inline uint32_t align_up_u32(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 inline int subs_for(int Hkv) { return (Hkv <= kAttnWarps && kAttnWarps % Hkv == 0) ? kAttnWarps / Hkv : 1; }
 
+// ---- cluster kernel: host side ----
+int cluster_size_for(int B, int Hkv) {
+    const int mode = tuning_get("attn.cluster");      // 1: whenever possible, -1: never, 0: small batches
+    if (mode < 0) return 0;
+    const int pairs = B * Hkv;
+    const int sms = sm_count();
+    if (mode == 0 && pairs * 8 > 2 * sms) return 0;
+    if (mode > 0 && pairs > 65535) return 0;
+    // 8 CTAs per cluster; the opt-in size 16 measured slower (placing one cluster per GPC costs more than the shorter
+    // page walk saves: 17.8 us against 12.9 us per stage at batch 1, context 4096)
+    int size = 8;
+    const int forced = tuning_get("attn.cluster_size");
+    if (forced == 8 || forced == 16 || forced == 4) size = forced;
+    return size;
+}
+
+int launch_cluster_attention(ClusterAttnParams& p, cudaStream_t stream) {
+    const bool g32 = p.G == 32;
+    const int slot = (p.bits == 4 ? 2048 : 4096) + 256;
+    const int ns = p.bits == 4 ? 8 : 5;
+    uint32_t off = 0;
+    p.off_q = off;      off += align_up_u32((uint32_t)p.group * 128 * 2, 128);
+    p.off_wpart = off;  off += align_up_u32((uint32_t)kAttnWarps * p.group * 130 * 4, 128);
+    p.off_cpart = off;  off += align_up_u32((uint32_t)p.S * p.group * 130 * 4, 128);
+    p.off_ring = off;   off += (uint32_t)kAttnWarps * ns * slot;
+    const uint32_t cap = (uint32_t)max_smem_optin();
+    if (off > cap) return B200Q_ERR_UNSUPPORTED;
+    using KernelFn = void (*)(ClusterAttnParams);
+    KernelFn kernel = p.bits == 4 ? (g32 ? paged_attn_cluster_kernel<4, 5> : paged_attn_cluster_kernel<4, 6>)
+                                  : (g32 ? paged_attn_cluster_kernel<8, 5> : paged_attn_cluster_kernel<8, 6>);
+    static bool configured[2][2][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[p.bits == 4][g32][dev & 63]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap) != cudaSuccess ||
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+            return B200Q_ERR_LAUNCH;
+        configured[p.bits == 4][g32][dev & 63] = true;
+    }
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (!tuning_get("no_pdl")) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = p.S;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.S, p.Hkv, p.B);
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = off;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return B200Q_ERR_LAUNCH;
+    return finish_launch();
+}
+
 }  // namespace
+
+int attention_stage_launches_impl(int B, int Hkv, int with_append) {
+    if (B <= 0 || Hkv <= 0) return 0;
+    if (B <= 65535 && cluster_size_for(B, Hkv) > 0) return 1;
+    return 2 + (with_append ? 1 : 0);
+}
 
 size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int Hkv, int D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return 0;
@@ -735,6 +1114,21 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
         const int warps = 4;
         paged_attn_simple_kernel<<<(B * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(sp);
         return finish_launch();
+    }
+    // small batches: one cluster per (sequence, kv head), merged on chip - no workspace, no second launch
+    const int cluster = window_size == 0 && B <= 65535 && Hkv <= 65535 ? cluster_size_for(B, Hkv) : 0;
+    if (cluster > 0) {
+        ClusterAttnParams c = {};
+        if (tp_out_slot >= 0) c.tp_out = tp_slot(tp_out_slot)->out;
+        c.q = (const __half*)q;
+        c.k_codes = const_cast<uint8_t*>(k_codes); c.v_codes = const_cast<uint8_t*>(v_codes);
+        c.k_scales = (__half*)const_cast<void*>(k_scales); c.v_scales = (__half*)const_cast<void*>(v_scales);
+        c.block_table = block_table; c.lengths = lengths; c.out = out;
+        c.B = B; c.Hq = Hq; c.Hkv = Hkv; c.P = page_size; c.max_blocks = max_blocks; c.G = group_size; c.Gd = Gd;
+        c.group = group; c.bits = bits; c.S = cluster; c.num_pages = num_pages; c.scale = scale;
+        c.row_bytes = Hkv * dp; c.scale_row_halves = Hkv * Gd;
+        const int rc = launch_cluster_attention(c, stream);
+        if (rc != B200Q_ERR_UNSUPPORTED) return rc;
     }
     if (workspace == nullptr || workspace_bytes < paged_gqa_workspace_bytes_impl(B, Hq, Hkv, D)) return B200Q_ERR_WORKSPACE;
 
@@ -817,6 +1211,77 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
             return B200Q_ERR_LAUNCH;
     }
     return finish_launch();
+}
+
+// Decode-layer attention in one call: split + rotate + append (as rope_kv_append_impl) followed by the attention over
+// the cache including the new token.  Small batches run it as ONE launch of the cluster kernel; otherwise the two
+// stages are launched one after the other (q_scratch [B, Hq, D] then holds the rotated queries).
+int rope_kv_append_impl(const void* qkv, const float* cos_table, const float* sin_table, const int32_t* positions,
+                        const int32_t* block_table, void* q_out, uint8_t* k_codes, uint8_t* v_codes, void* k_scales,
+                        void* v_scales, int bits, int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages,
+                        int max_blocks, int group_size, int table_len, cudaStream_t stream);
+
+int rope_append_attention_impl(const void* qkv, const float* cos_table, const float* sin_table, const int32_t* positions,
+                               int table_len, int bits, uint8_t* k_codes, uint8_t* v_codes, void* k_scales, void* v_scales,
+                               const int32_t* block_table, const int32_t* lengths, void* out, void* q_scratch, void* workspace,
+                               size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages,
+                               int max_blocks, int group_size, float scale, cudaStream_t stream) {
+    if (qkv == nullptr || cos_table == nullptr || sin_table == nullptr || positions == nullptr || k_codes == nullptr ||
+        v_codes == nullptr || k_scales == nullptr || v_scales == nullptr || block_table == nullptr || lengths == nullptr) {
+        tp_discard();
+        return B200Q_ERR_BAD_ARG;
+    }
+    if ((bits != 4 && bits != 8) || B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || page_size <= 0 || num_pages <= 0 ||
+        max_blocks <= 0 || group_size <= 0 || table_len <= 0 || Hq % Hkv != 0) {
+        tp_discard();
+        return B200Q_ERR_BAD_ARG;
+    }
+    const int group = Hq / Hkv;
+    const int Gd = (D + group_size - 1) / group_size;
+    const int dp = bits == 4 ? D / 2 : D;
+    const bool fast_ok = tuning_get("attn.force_simple") == 0 && D == 128 && (group_size == 32 || group_size == 64) &&
+                         group <= 8 && Hkv <= kAttnWarps && page_size == 16 && B <= 65535 && ((uintptr_t)qkv % 16 == 0) &&
+                         ((uintptr_t)k_codes % 16 == 0) && ((uintptr_t)v_codes % 16 == 0) && ((uintptr_t)k_scales % 8 == 0) &&
+                         ((uintptr_t)v_scales % 8 == 0);
+    const int cluster = fast_ok ? cluster_size_for(B, Hkv) : 0;
+    if (cluster > 0) {
+        int tp_in_slot = -1, tp_out_slot = -1;
+        tp_take(&tp_in_slot, &tp_out_slot);
+        if (out == nullptr && tp_out_slot < 0) return B200Q_ERR_BAD_ARG;
+        ClusterAttnParams c = {};
+        if (tp_out_slot >= 0) c.tp_out = tp_slot(tp_out_slot)->out;
+        c.qkv = (const __half*)qkv; c.cos_table = cos_table; c.sin_table = sin_table; c.positions = positions;
+        c.table_len = table_len; c.fused = 1;
+        c.k_codes = k_codes; c.v_codes = v_codes; c.k_scales = (__half*)k_scales; c.v_scales = (__half*)v_scales;
+        c.block_table = block_table; c.lengths = lengths; c.out = out;
+        c.B = B; c.Hq = Hq; c.Hkv = Hkv; c.P = page_size; c.max_blocks = max_blocks; c.G = group_size; c.Gd = Gd;
+        c.group = group; c.bits = bits; c.S = cluster; c.num_pages = num_pages; c.scale = scale;
+        c.row_bytes = Hkv * dp; c.scale_row_halves = Hkv * Gd;
+        const int rc = launch_cluster_attention(c, stream);
+        if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+        if (q_scratch == nullptr) return B200Q_ERR_WORKSPACE;
+        // fall through to the two-stage route with the exchange slots restored for the attention stage
+        int rc2 = rope_kv_append_impl(qkv, cos_table, sin_table, positions, block_table, q_scratch, k_codes, v_codes, k_scales,
+                                      v_scales, bits, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, table_len, stream);
+        if (rc2 != B200Q_OK) return rc2;
+        if (tp_out_slot >= 0) return B200Q_ERR_UNSUPPORTED;
+        return paged_gqa_decode_impl(bits, q_scratch, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, workspace,
+                                     workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
+                                     B200Q_F16, B200Q_F16, 0, 0, stream);
+    }
+    if (q_scratch == nullptr) {
+        tp_discard();
+        return B200Q_ERR_WORKSPACE;
+    }
+    const int rc = rope_kv_append_impl(qkv, cos_table, sin_table, positions, block_table, q_scratch, k_codes, v_codes, k_scales,
+                                       v_scales, bits, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, table_len, stream);
+    if (rc != B200Q_OK) {
+        tp_discard();
+        return rc;
+    }
+    return paged_gqa_decode_impl(bits, q_scratch, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, workspace,
+                                 workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale, B200Q_F16,
+                                 B200Q_F16, 0, 0, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

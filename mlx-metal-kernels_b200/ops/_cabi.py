@@ -35,6 +35,9 @@ SIGNATURES = {
                                   _i, _vp]),
     "b200q_gate_up_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _vp, _vp,
                                   _i, _i64, _i64, _i, _i, _i, _vp]),
+    "b200q_rope_append_paged_gqa_decode": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz,
+                                                _i, _i, _i, _i, _i, _i64, _i, _i, _f, _vp]),
+    "b200q_attention_stage_launches": (_i, [_i, _i, _i]),
     "b200q_quantize_kv": (_i, [_i, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "b200q_peer_allgather": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp]),
     "b200q_tp_register": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),

@@ -58,3 +58,39 @@ def rope_kv_append(qkv, cos, sin, positions, paged_qkv, n_heads: int):
         "b200q_rope_kv_append",
     )
     return q_out
+
+
+def rope_append_attention(qkv, cos, sin, positions, paged_qkv, n_heads: int, *, scale: float | None = None):
+    """The attention stage of a decode layer in one call: split the fused qkv rows [B, (Hq + 2 Hkv) * D], rotate q and
+    k at ``positions[b]``, append the quantised k / v of the new token to ``paged_qkv`` (modified in place; its
+    ``lengths`` must already count the new token) and attend over the cache.  Returns [B, Hq, D].  Small batches run
+    as a single kernel (one thread-block cluster per sequence and kv head); others as append + split-KV attention."""
+    import math
+    NUM_PAGES, P, Hkv, D = paged_qkv.original_page_shape
+    B = qkv.shape[0]
+    _cabi.require_cuda(qkv, cos, sin, positions, paged_qkv.k_pages_q, paged_qkv.block_table, paged_qkv.lengths)
+    if qkv.dtype != torch.float16 or paged_qkv.k_scales.dtype != torch.float16:
+        raise TypeError("rope_append_attention needs fp16 activations and fp16 cache scales")
+    qkv = _cabi.contiguous(qkv)
+    cos = _cabi.contiguous(cos.to(torch.float32))
+    sin = _cabi.contiguous(sin.to(torch.float32))
+    positions = _cabi.contiguous(positions.to(torch.int32))
+    bt = paged_qkv.block_table
+    ln = paged_qkv.lengths
+    if bt.dtype != torch.int32 or not bt.is_contiguous() or ln.dtype != torch.int32:
+        raise TypeError("block_table and lengths must be contiguous int32 tensors")
+    lib = _cabi.load()
+    out = torch.empty((B, n_heads, D), dtype=torch.float16, device=qkv.device)
+    q_scratch = torch.empty_like(out)
+    ws = torch.empty(max(16, lib.b200q_paged_gqa_workspace_bytes(B, n_heads, Hkv, D)), dtype=torch.uint8, device=qkv.device)
+    _cabi.check(
+        lib.b200q_rope_append_paged_gqa_decode(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(),
+                                               cos.shape[0], paged_qkv.bits, paged_qkv.k_pages_q.data_ptr(),
+                                               paged_qkv.v_pages_q.data_ptr(), paged_qkv.k_scales.data_ptr(),
+                                               paged_qkv.v_scales.data_ptr(), bt.data_ptr(), ln.reshape(B).data_ptr(),
+                                               out.data_ptr(), q_scratch.data_ptr(), ws.data_ptr(), ws.numel(), B, n_heads,
+                                               Hkv, D, P, NUM_PAGES, bt.shape[1], paged_qkv.group_size,
+                                               float(scale if scale is not None else 1.0 / math.sqrt(D)), _cabi.stream()),
+        "b200q_rope_append_paged_gqa_decode",
+    )
+    return out

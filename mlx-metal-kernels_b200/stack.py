@@ -1,9 +1,9 @@
 """Llama-shaped q4/q8 decode stack on the hot-path kernels: the caller side of the matvec / MLP /
 paged-attention operators for the layer-stack benchmark.
 
-One decode step per layer is six launches through the C ABI:
-  [RMSNorm + QKV matvec] -> [split + RoPE + quantised KV append] -> [paged GQA decode attention
-  (+ merge)] -> [O matvec + residual] -> [RMSNorm + gate/up + SwiGLU] -> [down matvec + residual]
+One decode step per layer is five calls through the C ABI:
+  [RMSNorm + QKV matvec] -> [split + RoPE + quantised KV append + paged GQA decode attention: one kernel at
+  small batch, three at large] -> [O matvec + residual] -> [RMSNorm + gate/up + SwiGLU] -> [down matvec + residual]
 and the whole step is captured in a CUDA graph (positions and lengths live on the device and are
 advanced inside the graph).
 
@@ -276,6 +276,7 @@ class DecodeStack:
         D, G, bits = cfg.head_dim, cfg.group_size, cfg.bits
         F16, ck = _cabi.F16, _cabi.check
         n = 0
+        attn_launches = lib.b200q_attention_stage_launches(B, self.hkv, 1)
         torch.index_select(self.embedding, 0, self.token_ids, out=self.h)
         pending_slot = -1
         pending = None      # tensor-parallel path: gathered down-projection rows whose residual add (h2 + rows -> h)
@@ -293,21 +294,19 @@ class DecodeStack:
                                           cfg.eps, self.h.data_ptr(), None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(),
                                           None, self.qkv.data_ptr(), B, qw.shape[0], cfg.hidden, G, F16, F16, st),
                    "norm_qmatvec")
-            ck(lib.b200q_rope_kv_append(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
-                                        self.positions.data_ptr(), self.block_table.data_ptr(), self.q_rot.data_ptr(),
-                                        cache.k_codes.data_ptr(), cache.v_codes.data_ptr(), cache.k_scales.data_ptr(),
-                                        cache.v_scales.data_ptr(), cfg.kv_bits, B, self.hq, self.hkv, D, cfg.page_size,
-                                        self.num_pages, self.max_blocks, cfg.kv_group_size, self.cos.shape[0], st),
-               "rope_kv_append")
             if self.peer_fused:
                 ck(lib.b200q_tp_next(-1, self.slots[0]), "tp_next")
-            ck(lib.b200q_paged_gqa_decode(cfg.kv_bits, self.q_rot.data_ptr(), cache.k_codes.data_ptr(),
-                                          cache.v_codes.data_ptr(), cache.k_scales.data_ptr(), cache.v_scales.data_ptr(),
-                                          self.block_table.data_ptr(), self.lengths.data_ptr(),
-                                          None if self.peer_fused else self.attn.data_ptr(),
-                                          self.workspace.data_ptr(), self.workspace.numel(), B, self.hq, self.hkv, D,
-                                          cfg.page_size, self.num_pages, self.max_blocks, cfg.kv_group_size,
-                                          1.0 / math.sqrt(D), F16, F16, st), "paged_gqa_decode")
+            # split + RoPE + quantised KV append + attention: one kernel at small batch (a cluster per sequence and kv head)
+            ck(lib.b200q_rope_append_paged_gqa_decode(self.qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                                      self.positions.data_ptr(), self.cos.shape[0], cfg.kv_bits,
+                                                      cache.k_codes.data_ptr(), cache.v_codes.data_ptr(),
+                                                      cache.k_scales.data_ptr(), cache.v_scales.data_ptr(),
+                                                      self.block_table.data_ptr(), self.lengths.data_ptr(),
+                                                      None if self.peer_fused else self.attn.data_ptr(),
+                                                      self.q_rot.data_ptr(), self.workspace.data_ptr(),
+                                                      self.workspace.numel(), B, self.hq, self.hkv, D, cfg.page_size,
+                                                      self.num_pages, self.max_blocks, cfg.kv_group_size,
+                                                      1.0 / math.sqrt(D), st), "rope_append_attention")
             ow, os_, oz = w["o"]
             gw, gs, gz = w["gate"]
             uw, us, uz = w["up"]
@@ -323,7 +322,7 @@ class DecodeStack:
                 ck(lib.b200q_qmatvec(bits, self.act.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
                                      self.h2.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.intermediate, G, F16, F16, st),
                    "down_proj")
-                n += 7
+                n += 4 + attn_launches
             elif not self.peer_fused:
                 attn_full = self._gather(0, self.attn)
                 ck(lib.b200q_qmatvec(bits, attn_full.data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
@@ -338,7 +337,7 @@ class DecodeStack:
                 ck(lib.b200q_qmatvec(bits, act_full.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(), None,
                                      self.o_loc.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
                 pending = self._gather(1, self.o_loc)      # h = cast(h2 + down) happens in the next prologue
-                n += 7 + (4 if self.peer_gather else 0)
+                n += 4 + attn_launches + (4 if self.peer_gather else 0)
             else:
                 # exchanges fused into the kernels: the O, gate/up and down launches wait for the rows they read and
                 # store the rows they produce straight into every rank's buffers (the attention rows were stored by
@@ -361,14 +360,14 @@ class DecodeStack:
                        "down_proj")
                     pending = self._gather(1, self.o_loc)
                     pending_slot = -1
-                    n += 8
+                    n += 5 + attn_launches
                 else:
                     ck(lib.b200q_tp_next(sm, sh), "tp_next")
                     ck(lib.b200q_qmatvec(bits, self.peer_full[2].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
                                          None, None, B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
                     pending = self.peer_full[1]
                     pending_slot = sh
-                    n += 7
+                    n += 4 + attn_launches
         if pending is None:
             ck(lib.b200q_rmsnorm_residual(self.h.data_ptr(), None, self.final_norm.data_ptr(), self.out.data_ptr(), None,
                                           B, cfg.hidden, cfg.eps, F16, _cabi.dtype_code(self.final_norm.dtype), st),

@@ -180,9 +180,13 @@ def test_sliding_window_and_sinks_match_oracle(cuda, bits, sink, window, Hq, Hkv
     got = pq_ops.sparse_paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), pattern)
     err = float((got.cpu().float() - want.float()).abs().max())
     assert err <= ATOL, err
-    # a window that covers everything is the dense result, bit for bit (same kernel, same page walk)
+    # a window that covers everything is the dense result of the same (split-KV) kernel, bit for bit: same page walk
     if window >= max(lengths):
-        dense = pq_ops.paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), backend="cuda")
+        cabi.set_tuning("attn.cluster", -1)
+        try:
+            dense = pq_ops.paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), backend="cuda")
+        finally:
+            cabi.set_tuning("attn.cluster", 0)
         assert torch.equal(got, dense)
     assert cabi.device_status() == 0
 
@@ -205,3 +209,25 @@ def test_quantize_kv_pages_matches_oracle_exactly(cuda, bits, D, G, dtype):
     for name in ("k_pages_q", "v_pages_q", "k_scales", "v_scales"):
         assert torch.equal(getattr(got, name).cpu(), getattr(want, name)), name
     assert got.k_scales.dtype == torch.float16
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("lengths,Hq,Hkv,G", [([4097], 32, 8, 32), ([100, 3], 32, 8, 32), ([17, 0, 5000], 32, 8, 32),
+                                               ([33], 32, 8, 64), ([700, 64], 8, 2, 32), ([1], 32, 8, 32), ([16] * 6, 4, 4, 32)])
+def test_cluster_kernel_matches_oracle(cuda, bits, lengths, Hq, Hkv, G):
+    """The one-kernel cluster form of the attention (forced on for every shape here) against the oracle, ragged and empty
+    sequences included; and it agrees with the split-KV kernels to within the bound."""
+    case = _case_with_lengths(lengths, Hkv, 128, 16, bits, G, seed=77)
+    q = synth.activations((len(lengths), 1, Hq, 128), 78)
+    want = opq.reference_paged_quantized_kv_gqa_decode_attention(q, _oracle_cache(case))
+    dcache = _device_cache(case, cuda)
+    cabi.set_tuning("attn.cluster", 1)
+    try:
+        got = pq_ops.paged_quantized_kv_gqa_decode_attention(q.to(cuda), dcache, backend="cuda")
+        cabi.set_tuning("attn.cluster", -1)
+        split = pq_ops.paged_quantized_kv_gqa_decode_attention(q.to(cuda), dcache, backend="cuda")
+    finally:
+        cabi.set_tuning("attn.cluster", 0)
+    assert float((got.cpu().float() - want.float()).abs().max()) <= ATOL
+    assert float((got.float() - split.float()).abs().max()) <= ATOL
+    assert cabi.device_status() == 0

@@ -130,3 +130,37 @@ def test_decode_stack_matches_oracle(cuda, kv_bits):
     again = stack.step(tokens.to(cuda)).clone()
     assert torch.equal(again, got)
     assert cabi.device_status() == 0
+
+
+@pytest.mark.parametrize("bits,B,Hq,Hkv,poss", [(8, 1, 32, 8, [4096]), (4, 2, 32, 8, [16, 700]), (8, 3, 8, 2, [0, 31, 95]),
+                                               (8, 1, 4, 4, [47]), (4, 5, 16, 8, [3, 200, 15, 16, 1023])])
+@pytest.mark.parametrize("cluster", [1, -1])
+def test_rope_append_attention_one_call(cuda, bits, B, Hq, Hkv, poss, cluster):
+    """b200q_rope_append_paged_gqa_decode (one cluster kernel at small batch, else append + split-KV attention) against
+    the oracle's RoPE, append and attention: appended codes / scales exact, attention rows within 2e-3."""
+    P, D = 16, 128
+    maxpos = max(poss) + 1
+    case = synth.paged_kv_case(B, Hkv, D, P, num_pages=B * ((maxpos + 15) // 16) + 5, min_len=maxpos, max_len=maxpos,
+                               bits=bits, group_size=32, seed=9)
+    case["lengths"] = torch.tensor([p + 1 for p in poss], dtype=torch.int32)
+    qkv = synth.activations((B, (Hq + 2 * Hkv) * D), 10)
+    cos, sin = ostack.rope_tables(D, 500000.0, maxpos + 1)
+    positions = torch.tensor(poss, dtype=torch.int32)
+    ocache = opq.OraclePagedKV(**{k: (v.clone() if torch.is_tensor(v) else v) for k, v in case.items()})
+    x3 = qkv.reshape(B, Hq + 2 * Hkv, D)
+    want_q = ostack.apply_rope_rows(x3[:, :Hq], cos, sin, positions)
+    ostack.append_kv(ocache, ostack.apply_rope_rows(x3[:, Hq:Hq + Hkv], cos, sin, positions), x3[:, Hq + Hkv:], positions)
+    want = opq.reference_paged_quantized_kv_gqa_decode_attention(want_q.reshape(B, 1, Hq, D), ocache).reshape(B, Hq, D)
+    dcache = pq_ops.PagedQuantizedKVCache(**{k: (v.to(cuda) if torch.is_tensor(v) else v) for k, v in case.items()})
+    cabi.set_tuning("attn.cluster", cluster)
+    try:
+        got = layer_ops.rope_append_attention(qkv.to(cuda), cos.to(cuda), sin.to(cuda), positions.to(cuda), dcache, Hq)
+        again_cache = pq_ops.PagedQuantizedKVCache(**{k: (v.to(cuda) if torch.is_tensor(v) else v) for k, v in case.items()})
+        again = layer_ops.rope_append_attention(qkv.to(cuda), cos.to(cuda), sin.to(cuda), positions.to(cuda), again_cache, Hq)
+    finally:
+        cabi.set_tuning("attn.cluster", 0)
+    for name in ("k_pages_q", "v_pages_q", "k_scales", "v_scales"):
+        assert torch.equal(getattr(dcache, name).cpu(), getattr(ocache, name)), name
+    assert float((got.cpu().float() - want.float()).abs().max()) <= 2e-3
+    assert torch.equal(again, got)                 # fixed merge order: bitwise repeatable
+    assert cabi.device_status() == 0
