@@ -58,7 +58,10 @@ int b200q_device_status(int reset, void* stream);
  *   "gemv.ts_min_batch"  smallest batch the tcgen05 kernel takes when "gemv.ts" is 0
  *   "gemv.force_generic" 1 = always the one-warp-per-row kernel that follows the reference arithmetic literally
  *   "gemv.stage_k", "gemv.stages", "gemv.interleave"   ring geometry / row dealing of the mma.sync kernel
- *   "ts.stages", "ts.smem_kb", "ts.split"               ring depth, shared-memory budget, K split of the tcgen05 kernel
+ *   "ts.stages", "ts.smem_kb", "ts.split", "ts.big"     ring depth, shared-memory budget, K split, shape of the tcgen05 kernel
+ *   "ts.tp_world"        number of equal row shards the matrices of this process are split into (tensor parallelism):
+ *                        the tcgen05 kernel then splits K as the unsharded launch would, which keeps a shard's rows
+ *                        bit-identical to the unsharded result
  *   "attn.ctas_per_sm", "attn.min_pages"                grid sizing of the split-KV attention kernel
  *   "attn.cluster"       1 = the one-kernel cluster form of the attention whenever it applies, -1 = never, 0 = small batches
  *   "attn.force_simple"  1 = always the one-warp-per-head attention kernel

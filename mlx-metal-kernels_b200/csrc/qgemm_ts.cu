@@ -795,10 +795,17 @@ int launch_ts(TsParams& p, cudaStream_t stream) {
     p.tmem_cols = WHOLE ? 512 : 256;
     p.a_slots = std::min(kMaxASlots, (p.tmem_cols - p.a_col0) / kChunkCols);
     if (p.a_slots < 2) return B200Q_ERR_UNSUPPORTED;
-    // K split over a cluster when the tiles do not fill the SMs
+    // K split over a cluster when the tiles do not fill the SMs.  The split (and with it the order in which a row's
+    // partial sums are added) must not depend on how many rows THIS launch holds: a tensor-parallel shard of the rows
+    // has to reproduce the unsharded result bit for bit, so the tile count of the unsharded matrix decides
+    // ("ts.tp_world" = number of equal row shards), and the cap below uses no shape-dependent quantity.
+    const int tiles_full = p.tiles * std::max(1, tuning_get("ts.tp_world"));
     int split = 1;
-    if (p.tiles < sms) split = std::min(8, sms / p.tiles);
+    if (tiles_full < sms) split = std::min(8, sms / tiles_full);
     split = std::max(1, std::min(split, p.n_stage_total / 2));
+    // without the dedicated buffer the partial sums travel through the first CTA's weight ring: two stages always exist
+    const int ring_cap = 1 + (int)(2u * p.stage_bytes / ((uint32_t)MATS * p.ncols * kRows * 4));
+    if ((uint32_t)(split - 1) * MATS * p.B * kRows * 4 > 8192u) split = std::max(1, std::min(split, ring_cap));
     const int fs = tuning_get("ts.split");
     if (fs > 0) split = std::max(1, std::min({fs, 8, p.n_stage_total}));
     // partial sums of a split K range: a dedicated buffer of at most 8 KB (real batch columns only), else the weight ring
@@ -820,7 +827,8 @@ int launch_ts(TsParams& p, cudaStream_t stream) {
     stages = std::min(stages, kMaxStages);
     if (stages < 2) return B200Q_ERR_UNSUPPORTED;
     p.stages = stages;
-    while (!fast_red && split > 1 && (uint64_t)(split - 1) * dcols * kRows * 4 > (uint64_t)stages * p.stage_bytes) --split;
+    if (!fast_red && split > 1 && (uint64_t)(split - 1) * dcols * kRows * 4 > (uint64_t)stages * p.stage_bytes)
+        return B200Q_ERR_UNSUPPORTED;      // only with a forced split
     p.split = split;
     p.off_xt = 1024u + (uint32_t)stages * p.stage_bytes;
     p.off_res = p.off_xt + (uint32_t)p.x_tiles * p.xt_bytes;

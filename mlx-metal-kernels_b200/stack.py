@@ -170,7 +170,14 @@ class DecodeStack:
         self.out = torch.zeros((batch, cfg.hidden), **f16)
         self.peer_gather = False
         self.peer_fused = False
-        self.fuse_exchange = fuse_exchange
+        # The exchange fused into the kernels exists in the mma.sync matvec kernel, which takes batches of up to 4
+        # rows; larger batches run the tcgen05 kernel and exchange through the stand-alone peer kernel (or NCCL).
+        self.fuse_exchange = fuse_exchange and batch <= 4
+        self.transport = "none"
+        self.peer_gather_error = ""
+        if tp_size > 1:
+            # the tcgen05 matvec then splits K as the unsharded launch would: sharded rows == unsharded rows, bit for bit
+            _cabi.set_tuning("ts.tp_world", tp_size)
         if tp_size > 1:
             self.o_loc = torch.zeros((batch, cfg.hidden // tp_size), **f16)
             self.gather_attn = torch.zeros((tp_size, batch, self.hq * D), **f16)
@@ -203,9 +210,14 @@ class DecodeStack:
         import torch.distributed as dist
         cfg, B, W = self.cfg, self.B, self.tp_size
         widths = (cfg.n_heads * cfg.head_dim, cfg.hidden, cfg.intermediate)
+        self.transport = "nccl"
         if any((w // W) * 2 % 16 for w in widths):
+            self.peer_gather_error = "a shard row is not a multiple of 16 bytes"
             return
         try:
+            import os
+            # plain peer stores only: the buffer is never bound to an NVLink multicast object
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
             group = self.pg if self.pg is not None else dist.group.WORLD
             sizes = [B * w * 2 for w in widths]
@@ -233,9 +245,12 @@ class DecodeStack:
         torch.cuda.synchronize()
         dist.barrier(group=self.pg)                            # every rank's buffer is zeroed before anyone stores
         self.peer_gather = True
+        self.transport = "peer_kernel"
         # the same buffers as exchange slots of the kernels themselves (stores from the epilogue, waits in the
         # next prologue): three slots per stack instance
         base = DecodeStack._next_slot
+        if self.fuse_exchange and base + 3 > 16:
+            self.peer_gather_error = "the library's 16 exchange slots are in use"
         if self.fuse_exchange and base + 3 <= 16:
             DecodeStack._next_slot += 3
             self.slots = (base, base + 1, base + 2)
@@ -244,6 +259,13 @@ class DecodeStack:
                                                        self.peer_epochs[i:].data_ptr(), self.peer_counters[i:].data_ptr(),
                                                        self.tp_rank, W), "tp_register")
             self.peer_fused = True
+            self.transport = "fused_peer"
+
+    def close(self):
+        """Returns this stack's exchange slots to the process-wide pool (the last stack created is released first)."""
+        if self.peer_fused and DecodeStack._next_slot == self.slots[2] + 1:
+            DecodeStack._next_slot = self.slots[0]
+        self.peer_fused = False
 
     def _gather(self, which: int, local):
         """All-gather of ``local`` [B, n_loc] into [B, tp * n_loc] (rank-major columns); ``which`` selects the

@@ -133,6 +133,29 @@ def test_fused_norm_prologue_and_residual_epilogue(tcgen05, B, with_res, big):
     assert rel_l2(got, want) <= TOL
 
 
+@pytest.mark.parametrize("bits,B,N,K,world", [(4, 8, 4096, 4096, 2), (4, 32, 4096, 14336, 4), (4, 16, 6144, 4096, 8),
+                                              (8, 6, 2048, 2048, 2)])
+def test_row_shards_reproduce_the_unsharded_rows_bit_for_bit(tcgen05, bits, B, N, K, world):
+    """Tensor parallelism shards the weight rows.  With "ts.tp_world" set, a shard's launch splits K exactly as the
+    unsharded launch does, so its rows are the unsharded rows bit for bit - on either shape of the kernel."""
+    w, s, z = synth.quantized_weight(N, K, bits, 64, seed=71)
+    x = synth.activations((B, K), 72)
+    d = lambda t: t.to(tcgen05).contiguous()
+    full = _fn(bits)(d(x), d(w), d(s), d(z), group_size=64)
+    assert rel_l2(full, _ref(bits)(x, w, s, z, group_size=64)) <= TOL
+    per = N // world
+    try:
+        for big in (-1, 1):
+            cabi.set_tuning("ts.tp_world", world)
+            cabi.set_tuning("ts.big", big)
+            for r in (0, world - 1):
+                rows = slice(r * per, (r + 1) * per)
+                part = _fn(bits)(d(x), d(w[rows]), d(s[rows]), d(z[rows]), group_size=64)
+                assert torch.equal(part, full[:, rows]), (big, r)
+    finally:
+        cabi.set_tuning("ts.tp_world", 0)
+
+
 def test_default_routing_takes_batches_of_five_and_more(cuda):
     """With no tuning set, batch 4 runs the mma.sync kernel and batch 5 the tcgen05 kernel; both agree with the
     oracle, and with each other to within the parity bound."""
