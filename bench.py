@@ -38,9 +38,9 @@ METRIC = "decode tokens/s"
 WORKLOAD = "c5_llama3_8b_shaped_q4_stack_32_layers_q8_paged_kv_ctx4096"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes of one qgemv_kernel launch (ncu capture of the
-# 4096 x 4096 q4 case); the kernel reads every weight byte once.
-DRAM_TRAFFIC_RATIO = 1.006
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of one matvec launch, per shape, from the ncu
+# captures summarised under profiles/ (one kernel, two launches each); the kernels read every weight byte once.
+DRAM_TRAFFIC_RATIO = {"qkv": 1.006, "o": 1.006, "gate": 1.004, "down": 1.005}
 
 
 def measured_peaks():
@@ -285,6 +285,141 @@ def gemv_only_graph(stack):
     return run, 4 * len(stack.layers)
 
 
+STEPS_PER_ROUND = 128     # BASELINE config 5: 128 decode steps from context 4096; longer runs repeat the round
+
+
+def time_steps(stack, tokens, steps, warmup, barrier, local, world, e2e=False, host_out=None, min_seconds=1.0):
+    """Device time (or, with ``e2e``, host wall time with the token ids copied in from pinned memory and the hidden
+    state copied out every step) of ``repeats`` x ``steps`` decode steps; every repeat restarts from context CONTEXT
+    (and so does every STEPS_PER_ROUND-th step of a long repeat).  ``repeats`` is chosen so that the timed region
+    lasts at least ``min_seconds``.  Returns (seconds per step as the max over ranks, repeats, clock summary)."""
+    device = stack.device
+
+    def reset():
+        stack.positions.fill_(CONTEXT)
+        stack.lengths.fill_(CONTEXT + 1)
+
+    B = stack.B
+    n_tok = tokens.shape[0]
+    dev_tok = torch.empty(B, dtype=torch.int64, device=device)
+
+    def one_step(i):
+        if i and i % STEPS_PER_ROUND == 0:
+            reset()
+        if e2e:
+            dev_tok.copy_(tokens[i % n_tok], non_blocking=True)
+            host_out.copy_(stack.step(dev_tok), non_blocking=True)
+            torch.cuda.current_stream().synchronize()          # the caller reads the result before the next token
+        else:
+            stack.step(tokens[i % n_tok])
+
+    reset()
+    for i in range(warmup):
+        one_step(i)
+    # estimate the step time to size the timed region (same count on every rank)
+    reset()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(8):
+        one_step(i)
+    torch.cuda.synchronize()
+    est = torch.tensor([(time.perf_counter() - t0) / 8], device=device, dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(est, op=dist.ReduceOp.MAX)
+    repeats = max(1, int(-(-min_seconds // (steps * float(est.item())))))
+    reset()
+    barrier()
+    clocks = ClockSampler(local)
+    with clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for r in range(repeats):
+            reset()
+            for i in range(steps):
+                one_step(i)
+        e1.record()
+        e1.synchronize()
+        sec = ((time.perf_counter() - t0) if e2e else e0.elapsed_time(e1) / 1e3) / (steps * repeats)
+    barrier()
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([sec], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    return sec, repeats, clocks.summary()
+
+
+def tp_parity_check(device, rank, world, group):
+    """Two layers of the benchmark shapes at batch 3: the tensor-parallel stack against the single-GPU stack built on
+    rank 0 from the same seeds.  Returns "bitwise" or the largest absolute difference."""
+    stack_mod = importlib.import_module(f"{entry.PKG_ALIAS}.stack")
+    cfg = stack_mod.StackConfig(n_layers=2)
+    layers = [stack_mod.random_layer(cfg, 4005 + i, device) for i in range(cfg.n_layers)]
+    gen = torch.Generator(device=device).manual_seed(4005)
+    emb = torch.randn((512, cfg.hidden), generator=gen, device=device, dtype=torch.float32).to(torch.float16)
+    fnorm = torch.ones(cfg.hidden, dtype=torch.float16, device=device)
+    B, ctx = 3, 300
+    toks = torch.randint(0, 512, (2, B), generator=gen, device=device)
+
+    def make(tp_rank, tp_size, pg):
+        st = stack_mod.DecodeStack(cfg, layers, fnorm, emb, B, ctx + 8, device, tp_rank=tp_rank, tp_size=tp_size, process_group=pg)
+        for i, c in enumerate(st.caches):          # same context on every rank: fill the full cache, keep the own kv heads
+            full = stack_mod.PagedKV(cfg, cfg.n_kv_heads, st.num_pages, device)
+            full.fill_random(cfg, 4900 + i)
+            lo = tp_rank * st.hkv
+            for name in ("k_codes", "v_codes", "k_scales", "v_scales"):
+                getattr(c, name).copy_(getattr(full, name)[:, :, lo:lo + st.hkv])
+        st.positions.fill_(ctx)
+        st.lengths.fill_(ctx + 1)
+        return st
+
+    sharded = make(rank, world, group)
+    outs = [sharded.step(toks[i]).clone() for i in range(2)]
+    torch.cuda.synchronize()
+    result = None
+    if rank == 0:
+        cabi = importlib.import_module(f"{entry.PKG_ALIAS}.ops._cabi")
+        cabi.set_tuning("ts.tp_world", world)          # the single-GPU stack below must not reset the shard count
+        single = make(0, 1, None)
+        cabi.set_tuning("ts.tp_world", world)
+        ref = [single.step(toks[i]).clone() for i in range(2)]
+        torch.cuda.synchronize()
+        diff = max(float((a.float() - b.float()).abs().max()) for a, b in zip(outs, ref))
+        result = "bitwise" if all(torch.equal(a, b) for a, b in zip(outs, ref)) else diff
+    sharded.close()
+    return result
+
+
+def comm_breakdown(stack, device):
+    """Exchanges per step and the device time of one stand-alone exchange of each of the three row widths
+    (the same peer kernel / NCCL call the step uses, replayed alone in a CUDA graph)."""
+    if stack.tp_size == 1:
+        return None
+    per_layer = 4
+    out = {"transport": stack.transport, "exchanges_per_step": per_layer * stack.cfg.n_layers,
+           "bytes_per_exchange": [stack.B * w * 2 for w in (stack.cfg.n_heads * stack.cfg.head_dim, stack.cfg.hidden,
+                                                            stack.cfg.intermediate)]}
+    if stack.peer_gather_error:
+        out["note"] = stack.peer_gather_error
+    locals_ = (stack.attn, stack.o_loc, stack.act)
+    stream = torch.cuda.Stream(device)
+
+    def run():
+        for which, t in enumerate(locals_):
+            for _ in range(8):
+                stack._gather(which, t)
+    try:
+        sec = _time_graph(run, 10, stream) / 24
+        out["us_per_exchange"] = round(sec * 1e6, 2)
+        out["us_per_step"] = round(sec * 1e6 * out["exchanges_per_step"], 1)
+        out["how"] = "stand-alone exchanges replayed alone in a CUDA graph (payload + flag round trip); inside the step they overlap with nothing"
+    except Exception as exc:           # NCCL inside a private stream capture can be refused: report, do not fail the run
+        out["note"] = f"exchange timing unavailable: {exc!r}"[:200]
+    return out
+
+
 def run_own(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -296,6 +431,7 @@ def run_own(args):
     group = None
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer stores only
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
     entry.load_package()
@@ -311,50 +447,19 @@ def run_own(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    cfg, stack = build_stack(device, B, args.steps * 3 + warmup * 2 + 64, rank, world, group)
+    cfg, stack = build_stack(device, B, STEPS_PER_ROUND + warmup + 16, rank, world, group)
     gen = torch.Generator(device=device).manual_seed(77)
-    tokens = torch.randint(0, cfg.vocab, (args.steps + warmup, B), generator=gen, device=device)
+    tokens = torch.randint(0, cfg.vocab, (STEPS_PER_ROUND, B), generator=gen, device=device)
     stack.capture()
 
     # ---- headline: K graph-replayed decode steps, device-timed ----
-    for i in range(warmup):
-        stack.step(tokens[i])
-    barrier()
-    with ClockSampler(local) as clocks:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(args.steps):
-            stack.step(tokens[warmup + i])
-        e1.record()
-        e1.synchronize()
-    barrier()
-    sec_per_step = e0.elapsed_time(e1) / 1e3 / args.steps
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([sec_per_step], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sec_per_step = float(t.item())
+    sec_per_step, repeats, clocks = time_steps(stack, tokens, args.steps, warmup, barrier, local, world)
     tokens_per_s = B / sec_per_step
 
     # ---- end to end: host token ids in, host hidden state out, every step ----
     host_tokens = tokens.cpu().pin_memory()
     host_out = torch.empty((B, cfg.hidden), dtype=torch.float16).pin_memory()
-    dev_tok = torch.empty(B, dtype=torch.int64, device=device)
-    for i in range(3):
-        dev_tok.copy_(host_tokens[i], non_blocking=True)
-        host_out.copy_(stack.step(dev_tok), non_blocking=True)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        dev_tok.copy_(host_tokens[warmup + i], non_blocking=True)
-        host_out.copy_(stack.step(dev_tok), non_blocking=True)
-        torch.cuda.current_stream().synchronize()          # the caller reads the result before the next token
-    e2e_sec = (time.perf_counter() - t0) / args.steps
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([e2e_sec], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_sec = float(t.item())
+    e2e_sec, e2e_repeats, _ = time_steps(stack, host_tokens, args.steps, 3, barrier, local, world, e2e=True, host_out=host_out)
 
     # ---- roofline of the dominant kernel: the matvec launches of one step, timed alone ----
     run_gemv, n_gemv = gemv_only_graph(stack)
@@ -366,8 +471,17 @@ def run_own(args):
         for key, kdim in (("qkv", cfg.hidden), ("o", cfg.n_heads * cfg.head_dim), ("gate", cfg.hidden), ("down", cfg.intermediate)):
             act_bytes += B * kdim * 2 + B * w[key][0].shape[0] * 2 * (2 if key == "gate" else 1)
     gemv_bytes = weight_bytes + act_bytes
+    gemv_traffic = 0.0
+    for w in stack.layers:
+        for key in ("qkv", "o", "gate", "down"):
+            mats = (w["gate"], w["up"]) if key == "gate" else (w[key],)
+            gemv_traffic += DRAM_TRAFFIC_RATIO[key] * sum(t.numel() * t.element_size() for m in mats for t in m if t is not None)
+    gemv_traffic += act_bytes
     gemv_gbs = gemv_bytes / gemv_sec / 1e9
     step_bytes = weight_bytes + stack.kv_bytes_per_step(CONTEXT)
+    comm = comm_breakdown(stack, device)
+    launches_per_step = stack.launches_per_step
+    transport = stack.transport
 
     status = cabi.device_status()
     line = {
@@ -383,26 +497,50 @@ def run_own(args):
         "vs_baseline": None,
         "dtype": "f16 activations, u4 weight codes, u8 KV codes, f32 accumulate",
         "data": "synthetic (random-init weights ~N(0,0.02) quantised q4 group 64; KV ~N(0,1) quantised q8 group 32; random token ids)",
-        "config": {"workload": WORKLOAD, "batch": B, "context": CONTEXT, "parallelism": f"tp{world}",
+        "config": {"workload": WORKLOAD, "batch": B, "context": CONTEXT, "parallelism": f"tp{world}", "transport": transport,
+                   "decode_steps_per_round": STEPS_PER_ROUND,
                    "cache": "each step streams %.2f GB per GPU from HBM (> L2), no flush needed" % (step_bytes / 1e9),
                    "cuda_graph": True},
         "step_hbm": {"algorithmic_bytes_per_gpu": step_bytes, "achieved_gbs_per_gpu": round(step_bytes / sec_per_step / 1e9, 1),
                      "frac_of_peak": round(step_bytes / sec_per_step / 1e9 / peak, 4)},
         "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (all q4 matvec launches of one step, timed alone)",
                      "achieved": round(gemv_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gemv_gbs / peak, 4),
-                     "traffic": round(gemv_bytes / n_gemv * DRAM_TRAFFIC_RATIO), "traffic_source": "ncu capture of the C1 launch: dram bytes read+written / algorithmic bytes = 1.006, scaled to this launch mix",
+                     "traffic": round(gemv_traffic / n_gemv), "traffic_source": "per-shape ncu captures (profiles/): dram bytes read+written / algorithmic bytes 1.004-1.006, applied to this launch mix",
                      "peak_kind": peak_kind, "launches": n_gemv,
                      "algorithmic_bytes_per_launch": round(gemv_bytes / n_gemv), "us_per_launch": round(gemv_sec / n_gemv * 1e6, 3)},
         "e2e": {"value": round(B / e2e_sec, 2), "unit": "tokens/s", "ms_per_step": round(e2e_sec * 1e3, 4),
-                "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * cfg.hidden * 2},
-        "gpu_launches": stack.launches_per_step * args.steps,
-        "clocks": clocks.summary(),
+                "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * cfg.hidden * 2, "repeats": e2e_repeats},
+        "gpu_launches": launches_per_step * args.steps * repeats,
+        "launches_per_step": launches_per_step,
+        "repeats": repeats,
+        "timed_seconds": round(sec_per_step * args.steps * repeats, 3),
+        "timing": "the timed region is `repeats` x `steps` decode steps (at least one second); ms_per_step is its mean",
+        "clocks": clocks,
         "device_status": status,
     }
-    if rank == 0 and world == 1:
-        del stack
+    if comm is not None:
+        line["comm"] = comm
+    del stack
+    torch.cuda.empty_cache()
+
+    # ---- the same step at batch 32 (BASELINE config 5 names batch 1 and 32) ----
+    if B != 32 and not args.no_batch32:
+        cfg32, stack32 = build_stack(device, 32, STEPS_PER_ROUND + warmup + 16, rank, world, group)
+        tok32 = torch.randint(0, cfg.vocab, (STEPS_PER_ROUND, 32), generator=gen, device=device)
+        stack32.capture()
+        steps32 = max(16, min(args.steps, 64))
+        sec32, rep32, _ = time_steps(stack32, tok32, steps32, 3, barrier, local, world, min_seconds=0.5)
+        bytes32 = stack32.weight_bytes_per_step() + stack32.kv_bytes_per_step(CONTEXT)
+        line["batch32"] = {"ms_per_step": round(sec32 * 1e3, 4), "tokens_per_s": round(32 / sec32, 1), "steps": steps32, "repeats": rep32,
+                           "algorithmic_bytes_per_gpu": bytes32, "achieved_gbs_per_gpu": round(bytes32 / sec32 / 1e9, 1),
+                           "frac_of_peak": round(bytes32 / sec32 / 1e9 / peak, 4), "transport": stack32.transport,
+                           "launches_per_step": stack32.launches_per_step, "device_status": cabi.device_status()}
+        del stack32
         torch.cuda.empty_cache()
-        line["kernels"] = kernel_microbenchmarks(device, peak)
+    if world > 1:
+        line["tp_parity"] = tp_parity_check(device, rank, world, group)
+    if rank == 0 and world == 1:
+        line["kernels"] = kernel_microbenchmarks(device, peak, all_configs=True)
         line["cpu_baseline"] = cpu_baseline(B, budget_s=20.0)
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -432,14 +570,11 @@ def run_kernels_only(cpu=False):
 # ------------------------------------------------------------------------------------------------
 # CPU arm: the torch-CPU restatement of the reference path on a bounded sample
 # ------------------------------------------------------------------------------------------------
-SAMPLE_LAYERS = 1
-
-
 class CpuSample:
-    """SAMPLE_LAYERS layers of the stack at the benchmark shapes; a full step is 32 layers, so
-    tokens/s = batch / (32 / SAMPLE_LAYERS * seconds per sample)."""
+    """``n_layers`` layers of the stack at the benchmark shapes; a full step is 32 layers, so
+    tokens/s = batch / (32 / n_layers * seconds per sample)."""
 
-    def __init__(self, batch):
+    def __init__(self, batch, n_layers):
         entry.load_package()
         stack_mod = importlib.import_module(f"{entry.PKG_ALIAS}.stack")
         synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
@@ -447,12 +582,13 @@ class CpuSample:
         self.ostack = ostack
         self.cfg = cfg = stack_mod.StackConfig()
         self.batch = batch
-        self.layers = [stack_mod.random_layer(cfg, 1005 + i, "cpu") for i in range(SAMPLE_LAYERS)]
+        self.n_layers = n_layers
+        self.layers = [stack_mod.random_layer(cfg, 1005 + i, "cpu") for i in range(n_layers)]
         P = cfg.page_size
         blocks = (CONTEXT + 16 + P - 1) // P
         self.positions = torch.full((batch,), CONTEXT, dtype=torch.int32)
         self.caches = []
-        for i in range(SAMPLE_LAYERS):
+        for i in range(n_layers):
             case = synth.paged_kv_case(batch, cfg.n_kv_heads, cfg.head_dim, P, num_pages=batch * blocks, min_len=CONTEXT + 1,
                                        max_len=CONTEXT + 1, bits=cfg.kv_bits, group_size=cfg.kv_group_size, seed=2005 + i)
             self.caches.append(opq.OraclePagedKV(**case))
@@ -466,12 +602,12 @@ class CpuSample:
         return h
 
     def tokens_per_s(self, sec_per_sample):
-        return self.batch / (sec_per_sample * self.cfg.n_layers / SAMPLE_LAYERS)
+        return self.batch / (sec_per_sample * self.cfg.n_layers / self.n_layers)
 
 
 def cpu_baseline(batch, budget_s):
     torch.set_num_threads(os.cpu_count() or 1)
-    sample = CpuSample(batch)
+    sample = CpuSample(batch, 1)
     sample.run()
     n, t0 = 0, time.perf_counter()
     while n < 2 or (time.perf_counter() - t0 < budget_s and n < 20):
@@ -479,31 +615,42 @@ def cpu_baseline(batch, budget_s):
         n += 1
     sec = (time.perf_counter() - t0) / n
     return {"value": round(sample.tokens_per_s(sec), 4), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{n} runs of {SAMPLE_LAYERS} of the 32 layers (torch-CPU restatement of the reference path: dequantise W to "
+            "sample": f"{n} runs of 1 of the 32 layers (torch-CPU restatement of the reference path: dequantise W to "
                       f"fp16, fp32 matmul, paged q8 attention at context {CONTEXT}), {sec * 1e3:.0f} ms each, scaled to 32 layers"}
 
 
 def run_reference(args):
+    """The reference's CPU path for the same workload.  MLX cannot be installed here, so this is the torch-CPU
+    restatement (kind "port").  One step = a bounded sample of the 32-layer step: up to 4 layers, fewer when the
+    requested steps + warm-up would otherwise take more than about two minutes; the value is scaled to 32 layers."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    sample = CpuSample(args.batch)
-    warmup = max(3, args.warmup) if args.warmup else 1
-    for _ in range(min(warmup, 3)):
+    warmup = max(0, args.warmup)
+    probe = CpuSample(args.batch, 1)
+    probe.run()
+    t0 = time.perf_counter()
+    probe.run()
+    per_layer = time.perf_counter() - t0
+    n_layers = int(max(1, min(4, 120.0 / max(1e-3, (args.steps + warmup) * per_layer))))
+    sample = probe if n_layers == 1 else CpuSample(args.batch, n_layers)
+    for _ in range(warmup):
         sample.run()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         sample.run()
     sec = (time.perf_counter() - t0) / args.steps
     value = round(sample.tokens_per_s(sec), 4)
-    desc = (f"each step = {SAMPLE_LAYERS} of the 32 layers of {WORKLOAD} at batch {args.batch} through the torch-CPU "
+    desc = (f"each step = {n_layers} of the 32 layers of {WORKLOAD} at batch {args.batch} through the torch-CPU "
             f"restatement of the reference's pure-MLX path (MLX itself cannot be installed here); value scaled to 32 layers")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": min(warmup, 3),
-        "ms_per_step": round(sec * 1e3 * 32 / SAMPLE_LAYERS, 2), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(sec * 1e3, 2), "ms_per_full_step_extrapolated": round(sec * 1e3 * 32 / n_layers, 2),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 activations, u4 weight codes, u8 KV codes, f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch": args.batch, "context": CONTEXT, "parallelism": "cpu"},
+        "config": {"workload": WORKLOAD, "batch": args.batch, "context": CONTEXT, "parallelism": "cpu",
+                   "extrapolated": f"{n_layers} of 32 layers timed per step; value = batch / (ms_per_step * 32 / {n_layers})"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -513,8 +660,9 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
-    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=128, help="decode steps per repeat (BASELINE config 5: 128 from context 4096)")
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--no-batch32", action="store_true", help="skip the secondary measurement of the step at batch 32")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--kernels-only", action="store_true",

@@ -264,6 +264,33 @@ __device__ __forceinline__ void ts_store_cols(const TsParams& p, const float (&a
     }
 }
 
+// Sum of squares of rmsnorm's input row z = cast(x + residual) for batch row b, by one warp; fixed summation order
+// (lane-strided, then a butterfly), so every CTA and every launch shape gets the same bits.
+__device__ __forceinline__ float row_inv_rms(const TsParams& p, int b, int lane) {
+    float ss = 0.0f;
+    for (int k = lane * 8; k < p.K; k += 256) {
+        const uint4 ux = *reinterpret_cast<const uint4*>(p.x + (size_t)b * p.K + k);
+        const __half2* hx = reinterpret_cast<const __half2*>(&ux);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(hx[i]); v[2 * i + 1] = __high2float(hx[i]); }
+        if (p.res_in != nullptr) {
+            const uint4 ur = *reinterpret_cast<const uint4*>(p.res_in + (size_t)b * p.K + k);
+            const __half2* hr = reinterpret_cast<const __half2*>(&ur);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __half2float(__float2half_rn(v[2 * i] + __low2float(hr[i])));
+                v[2 * i + 1] = __half2float(__float2half_rn(v[2 * i + 1] + __high2float(hr[i])));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    return rsqrtf(ss / (float)p.K + p.eps);
+}
+
 template <int BITS, int LOGG, int MATS, bool WHOLE>
 __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_kernel(const __grid_constant__ TsParams p) {
     constexpr int DW = kDeqWarps;
@@ -450,33 +477,16 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
             __syncwarp();
         };
         if (my_total > 0) issue(xw);
-        // rmsnorm prologue: one warp per batch row, fixed summation order (bitwise the same in every CTA)
+        // rmsnorm prologue: one warp per batch row; with more rows than activation warps the dequantise warps take
+        // their share (they cannot get far before the first operand tile exists anyway)
         if (p.norm_w != nullptr) {
-            for (int b = xw; b < B; b += kXWarps) {
-                float ss = 0.0f;
-                for (int k = lane * 8; k < p.K; k += 256) {
-                    const uint4 ux = *reinterpret_cast<const uint4*>(p.x + (size_t)b * p.K + k);
-                    const __half2* hx = reinterpret_cast<const __half2*>(&ux);
-                    float v[8];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(hx[i]); v[2 * i + 1] = __high2float(hx[i]); }
-                    if (p.res_in != nullptr) {
-                        const uint4 ur = *reinterpret_cast<const uint4*>(p.res_in + (size_t)b * p.K + k);
-                        const __half2* hr = reinterpret_cast<const __half2*>(&ur);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            v[2 * i] = __half2float(__float2half_rn(v[2 * i] + __low2float(hr[i])));
-                            v[2 * i + 1] = __half2float(__float2half_rn(v[2 * i + 1] + __high2float(hr[i])));
-                        }
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                if (lane == 0) inv_rms[b] = rsqrtf(ss / (float)p.K + p.eps);
+            const bool shared = B > kXWarps;
+            const int nw = shared ? kXWarps + DW : kXWarps;
+            for (int b = xw; b < B; b += nw) {
+                const float inv = row_inv_rms(p, b, lane);
+                if (lane == 0) inv_rms[b] = inv;
             }
-            named_bar_sync(1, kXWarps * 32);
+            named_bar_sync(1, nw * 32);
         }
         const bool writes_side = cluster_id == 0;              // the cluster of tile 0 covers the whole K range
         for (int j = 0, q = xw; j < my_total; ++j, q += kXWarps) {
@@ -513,10 +523,16 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
                     }
                 }
             } else {
+                // rows z = cast(x + residual), then cast(z * inv_rms * w): a lane meets the same 8 k of every row it
+                // handles (32 % PPR == 0), so the norm weights are fetched once per stage
+                const int pc = lane % PPR;
+                const int k = k0 + pc * 8;
+                float w8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w8[i] = load_as_f32(p.norm_w, p.norm_w_dtype, k + i);
+                const bool side = q < n_st && writes_side;          // first tile of the cluster that owns tile 0
                 for (int idx = lane; idx < n_pieces; idx += 32) {
                     const int b = idx / PPR;
-                    const int pc = idx - b * PPR;
-                    const int k = k0 + pc * 8;
                     const uint32_t addr = tile_addr(tile, idx);
                     uint4 u = lds128(addr);
                     const __half2* hx = reinterpret_cast<const __half2*>(&u);
@@ -532,7 +548,6 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
                             v[2 * i + 1] = __half2float(__float2half_rn(v[2 * i + 1] + __high2float(hr[i])));
                         }
                     }
-                    const bool side = q < n_st && writes_side;      // first tile of the cluster that owns tile 0
                     if (side && p.z_out != nullptr) {
                         __half2 zo[4];
 #pragma unroll
@@ -542,11 +557,7 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
                     const float inv = inv_rms[b];
                     __half2 no[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float w0 = load_as_f32(p.norm_w, p.norm_w_dtype, k + 2 * i);
-                        const float w1 = load_as_f32(p.norm_w, p.norm_w_dtype, k + 2 * i + 1);
-                        no[i] = __floats2half2_rn(v[2 * i] * inv * w0, v[2 * i + 1] * inv * w1);
-                    }
+                    for (int i = 0; i < 4; ++i) no[i] = __floats2half2_rn(v[2 * i] * inv * w8[2 * i], v[2 * i + 1] * inv * w8[2 * i + 1]);
                     u = *reinterpret_cast<const uint4*>(no);
                     if (side && p.normed_out != nullptr) *reinterpret_cast<uint4*>(p.normed_out + (size_t)b * p.K + k) = u;
                     if (BITS == 4)
@@ -568,6 +579,15 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
         bool waited_pdl = false;
+        if (p.norm_w != nullptr && B > kXWarps) {
+            pdl_wait();
+            waited_pdl = true;
+            for (int b = kXWarps + warp; b < B; b += kXWarps + DW) {
+                const float inv = row_inv_rms(p, b, lane);
+                if (lane == 0) inv_rms[b] = inv;
+            }
+            named_bar_sync(1, (kXWarps + DW) * 32);
+        }
         uint32_t a0 = 0;                     // index of the first chunk of A of the current stage (counted over the kernel)
         int slot = 0, t = grp % NA;          // ring positions of the stage and of this group's next chunk of A
         uint32_t par = 0, a_par = (uint32_t)(grp / NA) & 1u;

@@ -168,6 +168,8 @@ class DecodeStack:
         self.attn = torch.zeros((batch, self.hq * D), **f16)
         self.act = torch.zeros((batch, cfg.intermediate // tp_size), **f16)
         self.out = torch.zeros((batch, cfg.hidden), **f16)
+        # buffer for the normalised rows: large batches run the rmsnorm as a launch of its own in front of the matvec
+        self.normed = torch.zeros((batch, cfg.hidden), **f16) if batch >= 16 else None
         self.peer_gather = False
         self.peer_fused = False
         # The exchange fused into the kernels exists in the mma.sync matvec kernel, which takes batches of up to 4
@@ -299,6 +301,8 @@ class DecodeStack:
         F16, ck = _cabi.F16, _cabi.check
         n = 0
         attn_launches = lib.b200q_attention_stage_launches(B, self.hkv, 1)
+        normed = None if self.normed is None else self.normed.data_ptr()
+        norm_launch = 0 if normed is None else 1      # the library then runs the rmsnorm as a launch of its own
         torch.index_select(self.embedding, 0, self.token_ids, out=self.h)
         pending_slot = -1
         pending = None      # tensor-parallel path: gathered down-projection rows whose residual add (h2 + rows -> h)
@@ -307,13 +311,13 @@ class DecodeStack:
             qw, qs, qz = w["qkv"]
             if pending is None:
                 ck(lib.b200q_norm_qmatvec(bits, self.h.data_ptr(), None, w["input_norm"].data_ptr(), F16, cfg.eps, None,
-                                          None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(), None, self.qkv.data_ptr(), B,
+                                          normed, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(), None, self.qkv.data_ptr(), B,
                                           qw.shape[0], cfg.hidden, G, F16, F16, st), "norm_qmatvec")
             else:
                 if pending_slot >= 0:
                     ck(lib.b200q_tp_next(pending_slot, -1), "tp_next")
                 ck(lib.b200q_norm_qmatvec(bits, pending.data_ptr(), self.h2.data_ptr(), w["input_norm"].data_ptr(), F16,
-                                          cfg.eps, self.h.data_ptr(), None, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(),
+                                          cfg.eps, self.h.data_ptr(), normed, qw.data_ptr(), qs.data_ptr(), qz.data_ptr(),
                                           None, self.qkv.data_ptr(), B, qw.shape[0], cfg.hidden, G, F16, F16, st),
                    "norm_qmatvec")
             if self.peer_fused:
@@ -339,12 +343,12 @@ class DecodeStack:
                    "o_proj")
                 ck(lib.b200q_gate_up_swiglu(bits, self.h2.data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
                                             us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, self.act.data_ptr(),
-                                            None, w["post_norm"].data_ptr(), F16, cfg.eps, None, None, B,
+                                            None, w["post_norm"].data_ptr(), F16, cfg.eps, None, normed, B,
                                             cfg.intermediate, cfg.hidden, G, F16, F16, st), "gate_up")
                 ck(lib.b200q_qmatvec(bits, self.act.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
                                      self.h2.data_ptr(), self.h.data_ptr(), B, cfg.hidden, cfg.intermediate, G, F16, F16, st),
                    "down_proj")
-                n += 4 + attn_launches
+                n += 4 + attn_launches + 2 * norm_launch
             elif not self.peer_fused:
                 attn_full = self._gather(0, self.attn)
                 ck(lib.b200q_qmatvec(bits, attn_full.data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
@@ -354,12 +358,12 @@ class DecodeStack:
                 ck(lib.b200q_gate_up_swiglu(bits, o_full.data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
                                             us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, self.act.data_ptr(),
                                             self.h.data_ptr(), w["post_norm"].data_ptr(), F16, cfg.eps, self.h2.data_ptr(),
-                                            None, B, gw.shape[0], cfg.hidden, G, F16, F16, st), "gate_up")
+                                            normed, B, gw.shape[0], cfg.hidden, G, F16, F16, st), "gate_up")
                 act_full = self._gather(2, self.act)
                 ck(lib.b200q_qmatvec(bits, act_full.data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(), None,
                                      self.o_loc.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
                 pending = self._gather(1, self.o_loc)      # h = cast(h2 + down) happens in the next prologue
-                n += 4 + attn_launches + (4 if self.peer_gather else 0)
+                n += 4 + attn_launches + (4 if self.peer_gather else 0) + 2 * norm_launch
             else:
                 # exchanges fused into the kernels: the O, gate/up and down launches wait for the rows they read and
                 # store the rows they produce straight into every rank's buffers (the attention rows were stored by
@@ -389,7 +393,7 @@ class DecodeStack:
                                          None, None, B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
                     pending = self.peer_full[1]
                     pending_slot = sh
-                    n += 4 + attn_launches
+                    n += 4 + attn_launches + 2 * norm_launch
         if pending is None:
             ck(lib.b200q_rmsnorm_residual(self.h.data_ptr(), None, self.final_norm.data_ptr(), self.out.data_ptr(), None,
                                           B, cfg.hidden, cfg.eps, F16, _cabi.dtype_code(self.final_norm.dtype), st),
