@@ -417,6 +417,11 @@ def comm_breakdown(stack, device):
         out["how"] = "stand-alone exchanges replayed alone in a CUDA graph (payload + flag round trip); inside the step they overlap with nothing"
     except Exception as exc:           # NCCL inside a private stream capture can be refused: report, do not fail the run
         out["note"] = f"exchange timing unavailable: {exc!r}"[:200]
+    try:                               # host-side check: every rank issued the same exchanges
+        out["exchange_counts_agree"] = stack.verify_exchanges() is not None or None
+    except Exception as exc:
+        out["exchange_counts_agree"] = False
+        out["note"] = str(exc)[:200]
     return out
 
 

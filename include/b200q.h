@@ -60,11 +60,13 @@ int b200q_device_status(int reset, void* stream);
  *   "gemv.stage_k", "gemv.stages", "gemv.interleave"   ring geometry / row dealing of the mma.sync kernel
  *   "ts.stages", "ts.smem_kb", "ts.split", "ts.big"     ring depth, shared-memory budget, K split, shape of the tcgen05 kernel
  *   "ts.tp_world"        number of equal row shards the matrices of this process are split into (tensor parallelism):
- *                        the tcgen05 kernel then splits K as the unsharded launch would, which keeps a shard's rows
- *                        bit-identical to the unsharded result
+ *                        the tcgen05 kernel then splits K, and the attention picks its kernel, as the unsharded call
+ *                        would, which keeps a shard's rows bit-identical to the unsharded result
  *   "attn.ctas_per_sm", "attn.min_pages"                grid sizing of the split-KV attention kernel
  *   "attn.cluster"       1 = the one-kernel cluster form of the attention whenever it applies, -1 = never, 0 = small batches
  *   "attn.force_simple"  1 = always the one-warp-per-head attention kernel
+ *   "peer.spin_limit", "tp.spin_limit"   flag probes after which b200q_peer_allgather / the wait of an exchange fused
+ *                        into a kernel gives up and records event 5 (default 2^22; tests shorten it)
  *   "no_pdl"             1 = launch without programmatic dependent launch */
 int b200q_set_tuning(const char* key, int value);
 
@@ -268,6 +270,12 @@ int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* co
 int b200q_tp_register(int slot, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* counter,
                       int rank, int world);
 int b200q_tp_next(int in_slot, int out_slot);
+
+/* Diagnostics (no counterpart in the reference): one CTA waits on a shared-memory barrier that nothing arrives on, with
+ * the bounded wait the matvec and attention kernels use, for `limit` probes (1..65536).  The wait runs out, the kernel
+ * returns, b200q_device_status() then reports event 1 and *probes_out (device uint32, may be NULL) holds `limit`.
+ * Lets a caller check that an expired device wait reaches the host as a status instead of a hang. */
+int b200q_wait_expiry_selftest(unsigned limit, uint32_t* probes_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -68,6 +68,7 @@ int quantize_kv_impl(int bits, const void* values, uint8_t* codes, void* scales,
                      int in_dtype, cudaStream_t stream);
 int peer_allgather_impl(const void* local, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch,
                         int rank, int world, int rows, int64_t row_bytes_local, cudaStream_t stream);
+int wait_expiry_selftest_impl(uint32_t limit, uint32_t* probes_out, cudaStream_t stream);
 int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scales, const void* zeros,
                  const void* residual, void* y, int B, int64_t N, int64_t K, int group_size, int act_dtype,
                  int scale_dtype, const void* residual_in, const void* norm_weight, int norm_w_dtype, float eps,
@@ -284,6 +285,11 @@ int b200q_peer_allgather(const void* local, void* const* peer_full, uint32_t* co
     tp_discard();
     return peer_allgather_impl(local, peer_full, peer_flags, epoch, rank, world, rows, row_bytes_local,
                                (cudaStream_t)stream);
+}
+
+int b200q_wait_expiry_selftest(unsigned limit, uint32_t* probes_out, void* stream) {
+    tp_discard();
+    return wait_expiry_selftest_impl(limit, probes_out, (cudaStream_t)stream);
 }
 
 int b200q_tp_register(int slot, void* const* peer_full, uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* counter,

@@ -61,6 +61,7 @@ struct TpIn {
     const uint32_t* flags;          // this rank's flag words [world]
     const uint32_t* epoch;          // this rank's publication counter (already advanced by the local writer)
     int world;                      // world == 0: nothing to wait for
+    uint32_t spin_limit;            // acquire loads before the wait gives up (0: kTpSpinLimit); tuning key "tp.spin_limit"
 };
 struct TpSlot { TpOut out; };       // host table entry
 const TpSlot* tp_slot(int slot);    // nullptr if the slot was never registered
@@ -166,7 +167,8 @@ __device__ __forceinline__ void tp_finish_writer(const TpOut& out, int lane, uns
 // Called by threads 0 .. world-1 of the reader; returns false when the bounded wait ran out.
 __device__ __forceinline__ bool tp_wait_source(const TpIn& in, int src) {
     const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(in.epoch);
-    for (uint32_t it = 0; it < kTpSpinLimit; ++it)
+    const uint32_t limit = in.spin_limit ? in.spin_limit : kTpSpinLimit;
+    for (uint32_t it = 0; it < limit; ++it)
         if ((int32_t)(ld_acquire_sys(in.flags + src) - seq) >= 0) return true;
     return false;
 }

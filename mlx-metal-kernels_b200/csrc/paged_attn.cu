@@ -1012,7 +1012,9 @@ int cluster_size_for(int B, int Hkv) {
     if (mode < 0) return 0;
     const int pairs = B * Hkv;
     const int sms = sm_count();
-    if (mode == 0 && pairs * 8 > 2 * sms) return 0;
+    // the choice follows the kv heads of the UNSHARDED cache ("ts.tp_world" equal head shards), so that a
+    // tensor-parallel rank runs the same kernel, and the same summation order, as the unsharded call
+    if (mode == 0 && pairs * std::max(1, tuning_get("ts.tp_world")) * 8 > 2 * sms) return 0;
     if (mode > 0 && pairs > 65535) return 0;
     // 8 CTAs per cluster; the opt-in size 16 measured slower (placing one cluster per GPC costs more than the shorter
     // page walk saves: 17.8 us against 12.9 us per stage at batch 1, context 4096)

@@ -25,6 +25,7 @@ struct PeerGatherParams {
     uint32_t* flags[kMaxRanks];         // flag array [world] of rank r as seen from this GPU
     uint32_t* epoch;                    // this rank's sequence counter for this buffer (device memory)
     int rank, world, rows, vec_loc;     // vec_loc = 16-byte vectors per row of the local shard
+    uint32_t spin_limit;                // acquire loads before the wait gives up (tuning key "peer.spin_limit")
 };
 
 __global__ void __launch_bounds__(512) peer_allgather_kernel(const __grid_constant__ PeerGatherParams p) {
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(512) peer_allgather_kernel(const __grid_consta
         // wait for source rank threadIdx.x; the sequence numbers only grow (wrap-around compared as signed distance)
         const uint32_t* mine = p.flags[p.rank] + threadIdx.x;
         bool seen = false;
-        for (uint32_t it = 0; it < kPeerSpinLimit; ++it) {
+        for (uint32_t it = 0; it < p.spin_limit; ++it) {
             if ((int32_t)(ld_acquire_sys(mine) - seq) >= 0) { seen = true; break; }
         }
         if (!seen) atomicMax(&g_device_status, (int)EV_PEER_WAIT);
@@ -74,7 +75,32 @@ int peer_allgather_impl(const void* local, void* const* peer_full, uint32_t* con
     }
     p.epoch = epoch;
     p.rank = rank; p.world = world; p.rows = rows; p.vec_loc = (int)(row_bytes_local / 16);
+    const int limit = tuning_get("peer.spin_limit");
+    p.spin_limit = limit > 0 ? (uint32_t)limit : kPeerSpinLimit;
     peer_allgather_kernel<<<1, 512, 0, stream>>>(p);
+    return finish_launch();
+}
+
+// One CTA whose first thread waits, with the given bound, on an mbarrier that nothing ever arrives on: the wait runs
+// out, EV_GEMV_FULL_WAIT is recorded in this unit's status word and the kernel returns.  It is the bounded-wait helper
+// of the matvec and attention kernels run by itself, so that the give-up branch can be tested without making a
+// product kernel lose a copy.
+__global__ void wait_expiry_selftest_kernel(uint32_t limit, uint32_t* probes_out) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool got = mbar_wait_bounded(&bar, 0, &g_device_status, (int)EV_GEMV_FULL_WAIT, limit);
+        if (probes_out != nullptr) *probes_out = got ? 0u : limit;
+    }
+}
+
+int wait_expiry_selftest_impl(uint32_t limit, uint32_t* probes_out, cudaStream_t stream) {
+    if (limit == 0 || limit > (1u << 16)) return B200Q_ERR_BAD_ARG;      // a test hook: short waits only
+    wait_expiry_selftest_kernel<<<1, 32, 0, stream>>>(limit, probes_out);
     return finish_launch();
 }
 

@@ -47,9 +47,32 @@ class StackConfig:
 
 
 def rope_tables(head_dim: int, theta: float, length: int, device):
-    inv_freq = 1.0 / (float(theta) ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / float(head_dim)))
-    freqs = torch.arange(length, dtype=torch.float32, device=device).reshape(length, 1) * inv_freq.reshape(1, -1)
-    return torch.cos(freqs).contiguous(), torch.sin(freqs).contiguous()
+    """cos / sin [length, head_dim/2] fp32 (models/llama_config.py:107-124 of the reference).  Built on the host so that
+    the table does not depend on the device's pow / cos implementation, then moved."""
+    inv_freq = 1.0 / (float(theta) ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / float(head_dim)))
+    freqs = torch.arange(length, dtype=torch.float32).reshape(length, 1) * inv_freq.reshape(1, -1)
+    return torch.cos(freqs).contiguous().to(device), torch.sin(freqs).contiguous().to(device)
+
+
+class ExchangeDesync(RuntimeError):
+    """The ranks of a tensor-parallel group have not issued the same exchanges."""
+
+
+def verify_exchange_counts(local_counts, group=None):
+    """Host-side check between steps: every rank reports how many exchanges it has issued on each of its buffers
+    (the sequence numbers its kernels publish); the counts must agree, because a rank that skipped an exchange, or
+    stopped stepping, leaves its peers' next wait to run out.  Raises ``ExchangeDesync`` on every rank, naming the
+    ranks that lag behind; works on any backend (the counts travel as Python objects)."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    mine = [int(c) for c in local_counts]
+    counts = [None] * world
+    dist.all_gather_object(counts, mine, group=group)
+    ahead = [max(c[i] for c in counts) for i in range(len(mine))]
+    behind = {r: c for r, c in enumerate(counts) if c != ahead}
+    if behind:
+        raise ExchangeDesync(f"exchange counts differ: expected {ahead}, lagging ranks {behind}")
+    return ahead
 
 
 def shard_rows(n_rows: int, rank: int, world: int):
@@ -178,9 +201,7 @@ class DecodeStack:
         self.transport = "none"
         self.peer_gather_error = ""
         if tp_size > 1:
-            # the tcgen05 matvec then splits K as the unsharded launch would: sharded rows == unsharded rows, bit for bit
-            _cabi.set_tuning("ts.tp_world", tp_size)
-        if tp_size > 1:
+            self.transport = "nccl"
             self.o_loc = torch.zeros((batch, cfg.hidden // tp_size), **f16)
             self.gather_attn = torch.zeros((tp_size, batch, self.hq * D), **f16)
             self.gather_h = torch.zeros((tp_size, batch, cfg.hidden // tp_size), **f16)
@@ -263,6 +284,13 @@ class DecodeStack:
             self.peer_fused = True
             self.transport = "fused_peer"
 
+    def verify_exchanges(self):
+        """Compares this rank's exchange sequence numbers with its peers' (call between steps; synchronises)."""
+        if not self.peer_gather:
+            return None
+        torch.cuda.synchronize(self.device)
+        return verify_exchange_counts(self.peer_epochs.cpu().tolist(), self.pg)
+
     def close(self):
         """Returns this stack's exchange slots to the process-wide pool (the last stack created is released first)."""
         if self.peer_fused and DecodeStack._next_slot == self.slots[2] + 1:
@@ -300,6 +328,8 @@ class DecodeStack:
         D, G, bits = cfg.head_dim, cfg.group_size, cfg.bits
         F16, ck = _cabi.F16, _cabi.check
         n = 0
+        # the tcgen05 matvec splits K as the unsharded launch would: sharded rows == unsharded rows, bit for bit
+        _cabi.set_tuning("ts.tp_world", self.tp_size)
         attn_launches = lib.b200q_attention_stage_launches(B, self.hkv, 1)
         normed = None if self.normed is None else self.normed.data_ptr()
         norm_launch = 0 if normed is None else 1      # the library then runs the rmsnorm as a launch of its own

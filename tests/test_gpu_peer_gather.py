@@ -1,5 +1,5 @@
-"""Two-GPU checks of the NVLink peer all-gather and of the tensor-parallel stack built on it (skipped on a
-single GPU): the gathered rows equal torch's all_gather, repeated calls and CUDA-graph replays keep working,
+"""Checks on 2, 4 and 8 GPUs of the NVLink peer all-gather and of the tensor-parallel stack built on it (each world
+size is skipped when fewer GPUs are visible): the gathered rows equal torch's all_gather, repeated calls and CUDA-graph replays keep working,
 and the sharded stack, over peer gathers as over NCCL gathers, reproduces the unsharded one bit for bit (the
 matvec sums a row's k-spans in k order whatever CTA holds the row, and the attention cuts the page list
 independently of the number of heads)."""
@@ -21,27 +21,31 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, result_path):
+def _rank_main(rank, world, port, result_path, batch):
+    import traceback
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
-    torch.cuda.set_device(rank)
-    device = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
-    ok = {}
+    code = 1
     try:
+        torch.cuda.set_device(rank)
+        device = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+        ok = {}
         import __graft_entry__ as entry
         entry.load_package()
         stack_mod = importlib.import_module("mlx_metal_kernels_b200.stack")
         cabi = importlib.import_module("mlx_metal_kernels_b200.ops._cabi")
-        cfg = stack_mod.StackConfig(hidden=512, intermediate=1024, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128,
-                                    vocab=97, bits=4, group_size=64, kv_bits=8, kv_group_size=32)
+        n_kv = max(2, world)
+        cfg = stack_mod.StackConfig(hidden=512, intermediate=1024, n_layers=2, n_heads=2 * n_kv, n_kv_heads=n_kv,
+                                    head_dim=128, vocab=97, bits=4, group_size=64, kv_bits=8, kv_group_size=32)
         layers = [stack_mod.random_layer(cfg, 100 + i, device) for i in range(cfg.n_layers)]
         gen = torch.Generator(device=device).manual_seed(5)
         emb = torch.randn((cfg.vocab, cfg.hidden), generator=gen, device=device).to(torch.float16)
         fnorm = torch.ones(cfg.hidden, dtype=torch.float16, device=device)
-        B = 3
+        B = batch
 
         def make(tp_rank, tp_size, peer, fused=False):
             st = stack_mod.DecodeStack(cfg, layers, fnorm, emb, B, 96, device, tp_rank=tp_rank, tp_size=tp_size,
@@ -62,7 +66,9 @@ def _rank_main(rank, world, port, result_path):
         fused = make(rank, world, True, fused=True)
         ok["peer_enabled"] = bool(peer.peer_gather)
         ok["fused_enabled"] = bool(fused.peer_fused)
-        ok["peer_error"] = getattr(peer, "peer_gather_error", "")
+        ok["fused_expected"] = bool(fused.fuse_exchange)       # the stack fuses the exchange at small batches only
+        ok["transports"] = (nccl.transport, peer.transport, fused.transport)
+        ok["peer_error"] = getattr(peer, "peer_gather_error", "") or getattr(fused, "peer_gather_error", "")
         # the gather by itself, several calls in a row
         if peer.peer_gather:
             for it in range(5):
@@ -87,33 +93,70 @@ def _rank_main(rank, world, port, result_path):
         if rank == 0:
             torch.save(gathered, result_path)
         torch.cuda.synchronize()
-        dist.barrier()
+        dist.barrier()                     # no rank leaves while a peer still runs kernels on the shared buffers
+        code = 0
+    except BaseException:                  # noqa: BLE001 - reported through the exit code and the error file
+        with open(f"{result_path}.rank{rank}.err", "w") as fh:
+            fh.write(traceback.format_exc())
     finally:
         sys.stdout.flush()
-        os._exit(0)          # captured graphs hold NCCL kernels: leave without the library teardown
+        sys.stderr.flush()
+        # captured graphs hold NCCL kernels, so the library teardown is skipped; a rank that failed leaves with a
+        # non-zero code and the parent ends the others
+        os._exit(code)
 
 
-def test_peer_gather_and_sharded_stack(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+def _run_world(world, batch, tmp_path):
+    import time
     import torch.multiprocessing as mp
     result = str(tmp_path / "result.pt")
     ctx = mp.get_context("spawn")
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, result)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, result, batch)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=240)
+    deadline = time.time() + 300
+    while time.time() < deadline and any(p.is_alive() for p in procs):
+        if any(p.exitcode not in (None, 0) for p in procs):
+            break                          # a rank failed: its peers may be waiting for it
+        time.sleep(0.2)
+    stragglers = [p for p in procs if p.is_alive()]
+    if stragglers and all(p.exitcode in (None, 0) for p in procs) and time.time() < deadline:
+        for p in stragglers:
+            p.join(timeout=10)
+        stragglers = [p for p in procs if p.is_alive()]
+    for p in stragglers:
+        p.terminate()
+    for p in stragglers:
+        p.join(timeout=20)
+        if p.is_alive():
+            p.kill()
+            p.join(timeout=20)
+    errors = []
+    for r in range(world):
+        path = f"{result}.rank{r}.err"
+        if os.path.exists(path):
+            errors.append(f"rank {r}:\n" + open(path).read())
+    assert not errors, "\n".join(errors)
+    assert not stragglers, f"{len(stragglers)} rank(s) had to be terminated"
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
-    rows = torch.load(result)
+    return torch.load(result)
+
+
+@pytest.mark.parametrize("world,batch", [(2, 3), (2, 20), (4, 3), (4, 32), (8, 3), (8, 32)])
+def test_peer_gather_and_sharded_stack(tmp_path, world, batch):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    rows = _run_world(world, batch, tmp_path)
+    assert all(ok["nccl_equals_single"] and ok["status"] == 0 for ok in rows), rows
+    if not rows[0]["peer_enabled"]:
+        pytest.skip(f"symmetric memory unavailable, NCCL transport only: {rows[0]['peer_error']}")
     for ok in rows:
         assert ok["status"] == 0, ok
         assert ok["nccl_equals_single"], ok
-        if ok["peer_enabled"]:
-            assert ok["peer_equals_single"], ok
-        if ok["fused_enabled"]:
-            assert ok["fused_equals_single"], ok
-            assert all(v for k, v in ok.items() if k.startswith("gather_")), ok
-    print("peer gather enabled:", rows[0]["peer_enabled"], "fused exchange enabled:", rows[0]["fused_enabled"],
-          rows[0]["peer_error"])
+        assert ok["peer_enabled"], ok
+        assert ok["peer_equals_single"], ok
+        assert all(v for k, v in ok.items() if k.startswith("gather_")), ok
+        assert ok["fused_enabled"] == ok["fused_expected"], ok
+        assert ok["fused_equals_single"], ok          # at large batches this stack runs the stand-alone exchange
+        assert ok["transports"] == ("nccl", "peer_kernel", "fused_peer" if ok["fused_expected"] else "peer_kernel"), ok

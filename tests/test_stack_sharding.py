@@ -55,7 +55,7 @@ def _slice_heads(cache, lo, hi):
                              group_size=cache.group_size, original_page_shape=(n, P, hi - lo, D))
 
 
-def _rank_main(rank, WORLD, port, result_path):
+def _rank_main(rank, WORLD, port, result_path, B=3):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -71,10 +71,12 @@ def _rank_main(rank, WORLD, port, result_path):
 
         torch.manual_seed(0)
         cfg, layer = _tiny(stack_mod)
-        B, context = 3, 21
+        context = 21
         D, bits, G = cfg.head_dim, cfg.bits, cfg.group_size
         h = (torch.randn(B, 1, cfg.hidden, generator=torch.Generator().manual_seed(3)) * 0.5).to(torch.float16)
         positions = torch.full((B,), context, dtype=torch.int32)
+        if B > 3:                                           # ragged batch: every length from 1 to the full context
+            positions = (torch.arange(B, dtype=torch.int32) * 5) % (context + 1)
         cos, sin = ostack.rope_tables(D, cfg.rope_theta, 64)
 
         # unsharded answer
@@ -118,16 +120,59 @@ def _rank_main(rank, WORLD, port, result_path):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("WORLD", [2, 4])
-def test_sharded_layer_matches_unsharded(tmp_path, WORLD):
+@pytest.mark.parametrize("WORLD,B", [(2, 3), (4, 3), (2, 32)])
+def test_sharded_layer_matches_unsharded(tmp_path, WORLD, B):
     result = str(tmp_path / "result.pt")
-    mp.spawn(_rank_main, args=(WORLD, _free_port(), result), nprocs=WORLD, join=True)
+    mp.spawn(_rank_main, args=(WORLD, _free_port(), result, B), nprocs=WORLD, join=True)
     rows = torch.load(result)
     assert len(rows) == WORLD
     for err, ref, ok_shapes in rows:
         assert ok_shapes
         # same dot products on both sides; only the host BLAS blocking may differ between row subsets
         assert err <= 2.0 ** -10 * max(ref, 1.0), (err, ref)
+
+
+def _desync_rank(rank, WORLD, port, result_path):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        import __graft_entry__ as entry
+        entry.load_package()
+        stack_mod = importlib.import_module("mlx_metal_kernels_b200.stack")
+        counts = [0, 0, 0]                       # exchanges issued per buffer (attention rows, hidden rows, MLP rows)
+        report = {}
+        for step in range(3):
+            for which in (0, 1, 2, 1):           # the four exchanges of a layer
+                if step == 1 and rank == WORLD - 1 and which == 2:
+                    continue                     # this rank skips one exchange of the second step
+                counts[which] += 1
+            try:
+                report[step] = ("ok", stack_mod.verify_exchange_counts(counts))
+            except stack_mod.ExchangeDesync as exc:
+                report[step] = ("desync", str(exc))
+                break                            # every rank stops before its next launch
+        rows = [None] * WORLD
+        dist.all_gather_object(rows, report)
+        if rank == 0:
+            torch.save(rows, result_path)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("WORLD", [2, 3])
+def test_skipped_exchange_is_reported_on_every_rank(tmp_path, WORLD):
+    """A rank that skips an exchange is found by the host-side count check before the next step on ALL ranks
+    (the device-side symptom would be the peers' bounded wait running out one step later)."""
+    result = str(tmp_path / "result.pt")
+    mp.spawn(_desync_rank, args=(WORLD, _free_port(), result), nprocs=WORLD, join=True)
+    rows = torch.load(result)
+    assert len(rows) == WORLD
+    for report in rows:
+        assert report[0] == ("ok", [1, 2, 1])
+        kind, text = report[1]
+        assert kind == "desync" and f"lagging ranks {{{WORLD - 1}: [2, 4, 1]}}" in text and "[2, 4, 2]" in text
+        assert 2 not in report
 
 
 def test_shard_rows_and_qkv_layout():
