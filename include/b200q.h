@@ -169,6 +169,39 @@ int b200q_paged_gqa_decode_window(int bits, const void* q, const uint8_t* k_code
                                   int group_size, float scale, int q_dtype, int scale_dtype, int sink_tokens,
                                   int window_size, void* stream);
 
+/* The same attention under a block-sparse mask: with L = min(lengths[b], max_blocks*page_size) the query sits at
+ * position L - 1 and key j < L takes part iff block_mask[(L-1)/block_size][j/block_size] != 0 (the decode row of the
+ * reference's "block_sparse" pattern, build_sparse_attention_mask, ops/sparse_attention_ops.py:98-107; its causal
+ * bound j <= L - 1 holds for every cached token).  The reference has this over a quantized cache only as the pure-MLX
+ * scaffold of ops/paged_quantized_kv_ops.py:669-714.
+ *   block_mask   [n_qblocks, n_kblocks] bytes in device memory; a row or column index beyond it counts as masked
+ *   page_scratch B*(max_blocks+1) int32 of device scratch, or NULL.  With scratch and block_size a multiple of
+ *                page_size, one small kernel compacts every sequence's attended pages into a private block table and
+ *                the dense kernels above run on it (cost follows the attended pages); otherwise the one-warp-per-head
+ *                kernel tests every token.
+ * A sequence whose mask row hides every key writes zeros (the reference scaffold degenerates to a uniform average
+ * over all keys there).  Other arguments as b200q_paged_gqa_decode. */
+int b200q_paged_gqa_decode_block_sparse(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                        const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                        const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
+                                        const uint8_t* block_mask, int n_qblocks, int n_kblocks, int block_size,
+                                        int32_t* page_scratch, int B, int Hq, int Hkv, int D, int page_size,
+                                        int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                                        int scale_dtype, void* stream);
+
+/* Decode attention over an UNQUANTISED paged cache with grouped query heads: K/V pages
+ * [num_pages, page_size, Hkv, D] in `dtype` (B200Q_F16 or B200Q_BF16, also the type of q and out), D <= 128,
+ * fp32 scores and sums.  Replaces kernels/paged_decode_attention{,_threadgroup,_d64,_d128}.metal as launched by
+ * paged_decode_attention (ops/paged_kv_ops.py:307-360; Hq == Hkv there) and serves
+ * reference_paged_gqa_decode_attention's shapes (ops/gqa_ops.py:307-340; Hq a multiple of Hkv).  Tokens whose
+ * block-table entry is negative take no part; a sequence with no valid token writes zeros.
+ * workspace: b200q_paged_fp16_gqa_workspace_bytes(B, Hq, Hkv, max_blocks) bytes (0 when one CTA per head suffices). */
+size_t b200q_paged_fp16_gqa_workspace_bytes(int B, int Hq, int Hkv, int max_blocks);
+int b200q_paged_fp16_gqa_decode(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_table,
+                                const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes, int B, int Hq,
+                                int Hkv, int D, int page_size, int64_t num_pages, int max_blocks, float scale, int dtype,
+                                void* stream);
+
 /* The same attention for callers that cannot allocate device memory at all.  (No counterpart in the
  * reference: its runtime allocates every kernel output itself.)  Some hosts of this library may not
  * call cudaMalloc: a plugin running inside another runtime's memory budget, a worker that must not

@@ -87,6 +87,18 @@ int rope_append_attention_impl(const void* qkv, const float* cos_table, const fl
                                const int32_t* block_table, const int32_t* lengths, void* out, void* q_scratch, void* workspace,
                                size_t workspace_bytes, int B, int Hq, int Hkv, int D, int page_size, int64_t num_pages,
                                int max_blocks, int group_size, float scale, cudaStream_t stream);
+int paged_gqa_decode_block_sparse_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                       const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                       const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
+                                       const uint8_t* block_mask, int n_qblocks, int n_kblocks, int block_size,
+                                       int32_t* page_scratch, int B, int Hq, int Hkv, int D, int page_size,
+                                       int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                                       int scale_dtype, cudaStream_t stream);
+size_t paged_fp16_workspace_bytes_impl(int B, int Hq, int Hkv, int max_blocks);
+int paged_fp16_gqa_decode_impl(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_table,
+                               const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes, int B, int Hq,
+                               int Hkv, int D, int page_size, int64_t num_pages, int max_blocks, float scale, int dtype,
+                               cudaStream_t stream);
 size_t paged_gqa_workspace_bytes_impl(int B, int Hq, int Hkv, int D);
 int attention_stage_launches_impl(int B, int Hkv, int with_append);
 size_t paged_gqa_static_scratch_bytes_impl();
@@ -457,6 +469,32 @@ int b200q_paged_gqa_decode_window(int bits, const void* q, const uint8_t* k_code
     return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out, workspace,
                                  workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
                                  q_dtype, scale_dtype, sink_tokens, window_size, (cudaStream_t)stream);
+}
+
+int b200q_paged_gqa_decode_block_sparse(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                        const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                        const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
+                                        const uint8_t* block_mask, int n_qblocks, int n_kblocks, int block_size,
+                                        int32_t* page_scratch, int B, int Hq, int Hkv, int D, int page_size,
+                                        int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                                        int scale_dtype, void* stream) {
+    return paged_gqa_decode_block_sparse_impl(bits, q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out,
+                                              workspace, workspace_bytes, block_mask, n_qblocks, n_kblocks, block_size,
+                                              page_scratch, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size,
+                                              scale, q_dtype, scale_dtype, (cudaStream_t)stream);
+}
+
+size_t b200q_paged_fp16_gqa_workspace_bytes(int B, int Hq, int Hkv, int max_blocks) {
+    return paged_fp16_workspace_bytes_impl(B, Hq, Hkv, max_blocks);
+}
+
+int b200q_paged_fp16_gqa_decode(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_table,
+                                const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes, int B, int Hq,
+                                int Hkv, int D, int page_size, int64_t num_pages, int max_blocks, float scale, int dtype,
+                                void* stream) {
+    tp_discard();
+    return paged_fp16_gqa_decode_impl(q, k_pages, v_pages, block_table, lengths, out, workspace, workspace_bytes, B, Hq,
+                                      Hkv, D, page_size, num_pages, max_blocks, scale, dtype, (cudaStream_t)stream);
 }
 
 int b200q_quantize_kv(int bits, const void* values, uint8_t* codes, void* scales, int64_t rows, int D, int group_size,

@@ -934,6 +934,8 @@ struct SimpleParams {
     int64_t num_pages;
     float scale;
     int sink, window;
+    const uint8_t* block_mask;      // block-sparse decode: [n_qblocks, n_kblocks] bytes, or null
+    int block_size, n_qblocks, n_kblocks;
 };
 
 __global__ void __launch_bounds__(128) paged_attn_simple_kernel(const __grid_constant__ SimpleParams p) {
@@ -953,8 +955,15 @@ __global__ void __launch_bounds__(128) paged_attn_simple_kernel(const __grid_con
     }
     float m = -INFINITY, l = 0.0f;
     const float off = p.bits == 4 ? 8.0f : 128.0f;
+    // block-sparse: the query sits at position L - 1, i.e. in row (L - 1) / block_size of the mask
+    const int qb = (p.block_mask != nullptr && L > 0) ? (L - 1) / p.block_size : 0;
+    const uint8_t* mask_row = (p.block_mask != nullptr && qb < p.n_qblocks) ? p.block_mask + (size_t)qb * p.n_kblocks : nullptr;
     for (int j = 0; j < L; ++j) {
         if (p.window > 0 && j >= p.sink && j < L - p.window) continue;     // outside sink and window
+        if (p.block_mask != nullptr) {
+            const int kb = j / p.block_size;
+            if (mask_row == nullptr || kb >= p.n_kblocks || mask_row[kb] == 0) continue;
+        }
         const int page = p.block_table[(int64_t)b * p.max_blocks + j / p.P];
         if (page < 0 || page >= p.num_pages) continue;
         const int64_t tok = ((int64_t)page * p.P + (j % p.P)) * p.Hkv + hkv;
@@ -1112,7 +1121,7 @@ int paged_gqa_decode_impl(int bits, const void* q, const uint8_t* k_codes, const
     if (!fast_ok) {
         SimpleParams sp = {q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out,
                            B, Hq, Hkv, D, page_size, max_blocks, group_size, Gd, bits, q_dtype, scale_dtype,
-                           num_pages, scale, sink_tokens, window_size};
+                           num_pages, scale, sink_tokens, window_size, nullptr, 0, 0, 0};
         const int warps = 4;
         paged_attn_simple_kernel<<<(B * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(sp);
         return finish_launch();
@@ -1332,6 +1341,92 @@ int paged_gqa_decode_static_impl(int bits, const void* q, const uint8_t* k_codes
                                          kStaticScratchBytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size,
                                          scale, q_dtype, scale_dtype, 0, 0, stream);
     return rc == B200Q_ERR_WORKSPACE ? B200Q_ERR_STATIC_SCRATCH : rc;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Block-sparse decode: key j of a sequence of L tokens is attended iff block_mask[(L-1)/bs][j/bs] != 0 (the decode
+// row of the reference's block_sparse mask; the causal bound j <= L-1 holds for every cached token).
+// When bs is a multiple of the page size the attended keys are whole pages (and possibly the partly filled last
+// one), and softmax attention does not depend on the order of its keys: one warp per sequence compacts the
+// attended pages into a private block table with the matching length, and the dense kernels run on that.
+// ------------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(128) block_sparse_pages_kernel(const int32_t* block_table, const int32_t* lengths,
+                                                                 const uint8_t* block_mask, int n_qblocks, int n_kblocks,
+                                                                 int pages_per_block, int P, int max_blocks, int B,
+                                                                 int32_t* table_out, int32_t* lengths_out) {
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= B) return;
+    const int L = clamp_len(lengths[b], max_blocks * P);
+    const int npages = (L + P - 1) / P;
+    const int bs = pages_per_block * P;
+    const int qb = L > 0 ? (L - 1) / bs : 0;
+    const uint8_t* row = (L > 0 && qb < n_qblocks) ? block_mask + (size_t)qb * n_kblocks : nullptr;
+    const int32_t* src = block_table + (size_t)b * max_blocks;
+    int32_t* dst = table_out + (size_t)b * max_blocks;
+    int count = 0, tokens = 0;
+    for (int p0 = 0; p0 < npages; p0 += 32) {
+        const int pg = p0 + lane;
+        bool vis = false;
+        if (pg < npages && row != nullptr) {
+            const int kb = pg / pages_per_block;
+            vis = kb < n_kblocks && row[kb] != 0;
+        }
+        const uint32_t ballot = __ballot_sync(0xffffffffu, vis);
+        if (vis) dst[count + __popc(ballot & ((1u << lane) - 1u))] = src[pg];
+        count += __popc(ballot);
+        // every attended page is full except the sequence's last page
+        tokens += __popc(ballot) * P;
+        if (npages - 1 >= p0 && npages - 1 < p0 + 32 && ((ballot >> (npages - 1 - p0)) & 1u)) tokens -= npages * P - L;
+    }
+    for (int i = count + lane; i < max_blocks; i += 32) dst[i] = -1;
+    if (lane == 0) lengths_out[b] = tokens;
+}
+}  // namespace
+
+int paged_gqa_decode_block_sparse_impl(int bits, const void* q, const uint8_t* k_codes, const uint8_t* v_codes,
+                                       const void* k_scales, const void* v_scales, const int32_t* block_table,
+                                       const int32_t* lengths, void* out, void* workspace, size_t workspace_bytes,
+                                       const uint8_t* block_mask, int n_qblocks, int n_kblocks, int block_size,
+                                       int32_t* page_scratch, int B, int Hq, int Hkv, int D, int page_size,
+                                       int64_t num_pages, int max_blocks, int group_size, float scale, int q_dtype,
+                                       int scale_dtype, cudaStream_t stream) {
+    if (block_mask == nullptr || n_qblocks <= 0 || n_kblocks <= 0 || block_size <= 0) {
+        tp_discard();
+        return B200Q_ERR_BAD_ARG;
+    }
+    if (page_scratch != nullptr && page_size > 0 && block_size % page_size == 0 && B > 0 && max_blocks > 0 &&
+        block_table != nullptr && lengths != nullptr) {
+        int32_t* table2 = page_scratch;
+        int32_t* lengths2 = page_scratch + (size_t)B * max_blocks;
+        block_sparse_pages_kernel<<<(B + 3) / 4, 128, 0, stream>>>(block_table, lengths, block_mask, n_qblocks, n_kblocks,
+                                                                  block_size / page_size, page_size, max_blocks, B, table2,
+                                                                  lengths2);
+        const int rc = finish_launch();
+        if (rc != B200Q_OK) {
+            tp_discard();
+            return rc;
+        }
+        return paged_gqa_decode_impl(bits, q, k_codes, v_codes, k_scales, v_scales, table2, lengths2, out, workspace,
+                                     workspace_bytes, B, Hq, Hkv, D, page_size, num_pages, max_blocks, group_size, scale,
+                                     q_dtype, scale_dtype, 0, 0, stream);
+    }
+    // any block size: the one-warp-per-head kernel with a per-token test
+    tp_discard();
+    if ((bits != 4 && bits != 8) || q == nullptr || k_codes == nullptr || v_codes == nullptr || k_scales == nullptr ||
+        v_scales == nullptr || block_table == nullptr || lengths == nullptr || out == nullptr)
+        return B200Q_ERR_BAD_ARG;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 ||
+        group_size <= 0 || Hq % Hkv != 0 || !is_act_dtype(q_dtype) || !is_scale_dtype(scale_dtype))
+        return B200Q_ERR_BAD_ARG;
+    if (D > 128) return B200Q_ERR_UNSUPPORTED;
+    SimpleParams sp = {q, k_codes, v_codes, k_scales, v_scales, block_table, lengths, out,
+                       B, Hq, Hkv, D, page_size, max_blocks, group_size, (D + group_size - 1) / group_size, bits, q_dtype,
+                       scale_dtype, num_pages, scale, 0, 0, block_mask, block_size, n_qblocks, n_kblocks};
+    const int warps = 4;
+    paged_attn_simple_kernel<<<(B * Hq + warps - 1) / warps, warps * 32, 0, stream>>>(sp);
+    return finish_launch();
 }
 
 }  // namespace b200q

@@ -55,6 +55,11 @@ SIGNATURES = {
                                     _i, _i, _f, _i, _i, _vp]),
     "b200q_paged_gqa_decode_window": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64,
                                            _i, _i, _f, _i, _i, _i, _i, _vp]),
+    "b200q_paged_gqa_decode_block_sparse": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _i, _i,
+                                                 _vp, _i, _i, _i, _i, _i, _i64, _i, _i, _f, _i, _i, _vp]),
+    "b200q_paged_fp16_gqa_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "b200q_paged_fp16_gqa_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i64, _i, _f, _i,
+                                         _vp]),
 }
 
 _lib = None

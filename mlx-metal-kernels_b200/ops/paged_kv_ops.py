@@ -1,4 +1,5 @@
-"""Block-table gather (reference ops/paged_kv_ops.py:99-182, ops/kv_cache_ops.py:37-61)."""
+"""Block-table gather (reference ops/paged_kv_ops.py:99-182, ops/kv_cache_ops.py:37-61) and decode attention over
+an unquantised paged cache (ops/paged_kv_ops.py:258-360, ops/gqa_ops.py:307-340)."""
 from __future__ import annotations
 
 import math
@@ -74,3 +75,79 @@ def block_table_lookup(block_table, positions, PAGE_SIZE: int, *, backend: str =
         "b200q_block_table_lookup",
     )
     return page_ids, offsets
+
+
+def _validate_page_tensors(K_pages, V_pages, block_table):
+    if K_pages.ndim != 4 or V_pages.ndim != 4:
+        raise ValueError(f"K_pages and V_pages must be [NUM_PAGES,PAGE_SIZE,H,D], got {tuple(K_pages.shape)}, {tuple(V_pages.shape)}")
+    if K_pages.shape != V_pages.shape:
+        raise ValueError(f"K_pages and V_pages must have identical shapes, got {tuple(K_pages.shape)}, {tuple(V_pages.shape)}")
+    if block_table.ndim != 2:
+        raise ValueError(f"block_table must be [B,MAX_BLOCKS], got {tuple(block_table.shape)}")
+    NUM_PAGES, PAGE_SIZE, H, D = K_pages.shape
+    B, MAX_BLOCKS = block_table.shape
+    return NUM_PAGES, PAGE_SIZE, H, D, B, MAX_BLOCKS
+
+
+_workspaces: dict = {}
+
+
+def paged_fp16_attention_launch(q3d, K_pages, V_pages, block_table, lengths, scale):
+    """q3d [B,Hq,D], pages [NUM_PAGES,PAGE_SIZE,Hkv,D] in q's dtype, lengths int32 [B] -> [B,Hq,D]."""
+    B, Hq, D = q3d.shape
+    NUM_PAGES, PAGE_SIZE, Hkv, _ = K_pages.shape
+    MAX_BLOCKS = block_table.shape[1]
+    lib = _cabi.load()
+    q3d = _cabi.contiguous(q3d)
+    K_pages, V_pages = _cabi.contiguous(K_pages.to(q3d.dtype)), _cabi.contiguous(V_pages.to(q3d.dtype))
+    bt = _cabi.contiguous(block_table.to(torch.int32))
+    ln = _cabi.contiguous(lengths.reshape(B).to(torch.int32))
+    out = torch.empty_like(q3d)
+    nbytes = lib.b200q_paged_fp16_gqa_workspace_bytes(B, Hq, Hkv, MAX_BLOCKS)
+    key = (q3d.device, torch.cuda.current_stream(q3d.device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < max(nbytes, 16):
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q3d.device)
+        _workspaces[key] = ws
+    _cabi.check(lib.b200q_paged_fp16_gqa_decode(q3d.data_ptr(), K_pages.data_ptr(), V_pages.data_ptr(), bt.data_ptr(),
+                                                ln.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), B, Hq, Hkv, D,
+                                                PAGE_SIZE, NUM_PAGES, MAX_BLOCKS, float(scale),
+                                                _cabi.dtype_code(q3d.dtype), _cabi.stream()),
+                "b200q_paged_fp16_gqa_decode")
+    return out
+
+
+def _lengths_for_decode(lengths, B: int, capacity: int, device):
+    """Scalar / [B] / None lengths -> int32 [B] in [0, capacity] (checked on the host like the reference's)."""
+    return normalize_positions(capacity if lengths is None else lengths, B, capacity + 1, device=device)
+
+
+def reference_paged_decode_attention(q, K_pages, V_pages, block_table, lengths, *, scale=None):
+    _cabi.reference_unavailable("reference_paged_decode_attention")
+
+
+def paged_decode_attention(q, K_pages, V_pages, block_table, lengths, *, scale=None, backend: str = "auto"):
+    """Decode attention over an fp16 / bf16 paged cache, q [B,1,H,D] with as many query as kv heads
+    (ops/paged_kv_ops.py:307-360 of the reference; for Hq != Hkv see ``paged_gqa_decode_attention``).  Every Metal
+    backend name selects the one CUDA kernel."""
+    NUM_PAGES, PAGE_SIZE, H, D, B, MAX_BLOCKS = _validate_page_tensors(K_pages, V_pages, block_table)
+    if q.ndim != 4 or tuple(q.shape) != (B, 1, H, D):
+        raise ValueError(
+            f"q must have shape [B,1,H,D]={B,1,H,D}, got {tuple(q.shape)}. "
+            "For GQA/MQA paged decode with Hq != Hkv, use ops.gqa_ops.reference_paged_gqa_decode_attention."
+        )
+    if D > 128:
+        raise ValueError(f"paged_decode_attention currently supports D <= 128, got {D}")
+    lengths_arr = _lengths_for_decode(lengths, B, MAX_BLOCKS * PAGE_SIZE, q.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    name = backend.lower()
+    if _cabi.safe_mode_enabled() or name == "reference":
+        _cabi.reference_unavailable("paged_decode_attention")
+    if name not in ("auto", "cuda", "metal", "metal_threadgroup", "metal_d64", "metal_d128"):
+        raise ValueError("backend must be one of 'reference', 'metal', 'metal_threadgroup', 'metal_d64', 'metal_d128', "
+                         "'auto', 'cuda'")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"q dtype must be float16 or bfloat16, got {q.dtype}")
+    _cabi.require_cuda(q, K_pages, V_pages, block_table, lengths_arr)
+    return paged_fp16_attention_launch(q.reshape(B, H, D), K_pages, V_pages, block_table, lengths_arr, scale).reshape(B, 1, H, D)

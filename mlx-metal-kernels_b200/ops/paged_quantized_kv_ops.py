@@ -17,7 +17,7 @@ import torch
 from . import _cabi
 from .gqa_ops import validate_gqa_heads
 from .quant_ops import dequant_codes
-from .sparse_attention_ops import decode_window
+from .sparse_attention_ops import SparseAttentionPattern, decode_block_mask, decode_window
 
 _MAX_HEAD_DIM = 128
 
@@ -276,9 +276,11 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
-def paged_attention_launch(q3d, paged_qkv, scale, out=None, workspace=None, *, sink_tokens: int = 0, window_size: int = 0):
+def paged_attention_launch(q3d, paged_qkv, scale, out=None, workspace=None, *, sink_tokens: int = 0, window_size: int = 0,
+                           block_mask=None, block_size: int = 0):
     """q3d [B,Hq,D] -> [B,Hq,D]; all tensors already on one CUDA device.  ``window_size > 0`` restricts the
-    attention to positions ``< sink_tokens`` or ``>= length - window_size``."""
+    attention to positions ``< sink_tokens`` or ``>= length - window_size``; ``block_mask`` (uint8 [q_blocks, k_blocks]
+    on the device) with ``block_size`` to the keys j with ``block_mask[(length-1)//block_size, j//block_size]``."""
     B, Hq, D = q3d.shape
     NUM_PAGES, PAGE_SIZE, Hkv, _ = paged_qkv.original_page_shape
     MAX_BLOCKS = paged_qkv.block_table.shape[1]
@@ -299,7 +301,12 @@ def paged_attention_launch(q3d, paged_qkv, scale, out=None, workspace=None, *, s
     args = (paged_qkv.bits, q3d.data_ptr(), kq.data_ptr(), vq.data_ptr(), ks.data_ptr(), vs.data_ptr(), bt.data_ptr(),
             ln.data_ptr(), out.data_ptr(), workspace.data_ptr(), workspace.numel(), B, Hq, Hkv, D, PAGE_SIZE, NUM_PAGES,
             MAX_BLOCKS, paged_qkv.group_size, float(scale), _cabi.dtype_code(q3d.dtype), _cabi.dtype_code(ks.dtype))
-    if window_size > 0:
+    if block_mask is not None:
+        scratch = torch.empty(B * (MAX_BLOCKS + 1), dtype=torch.int32, device=q3d.device)
+        _cabi.check(lib.b200q_paged_gqa_decode_block_sparse(
+            *args[:11], block_mask.data_ptr(), block_mask.shape[0], block_mask.shape[1], int(block_size),
+            scratch.data_ptr(), *args[11:], _cabi.stream()), "b200q_paged_gqa_decode_block_sparse")
+    elif window_size > 0:
         _cabi.check(lib.b200q_paged_gqa_decode_window(*args, int(sink_tokens), int(window_size), _cabi.stream()),
                     "b200q_paged_gqa_decode_window")
     else:
@@ -347,12 +354,15 @@ def paged_quantized_kv_gqa_decode_attention(q, paged_qkv: PagedQuantizedKVCache,
 
 def sparse_paged_quantized_kv_gqa_decode_attention(q, paged_qkv: PagedQuantizedKVCache, pattern, *,
                                                    scale: float | None = None, backend: str = "cuda"):
-    """Sliding-window (+ attention sink) decode over the paged quantized cache: q [B,1,Hq,D] -> [B,1,Hq,D].
+    """Sparse decode over the paged quantized cache: q [B,1,Hq,D] -> [B,1,Hq,D].
     The reference has this as a pure-MLX scaffold only (reference_sparse_paged_quantized_kv_gqa_decode_attention,
     ops/paged_quantized_kv_ops.py:669-714); ``backend="reference"`` raises here like every reference path.
-    ``pattern`` is a ``SparseAttentionPattern`` (dense, sliding_window, sliding_window_sink); every sequence
-    needs at least one token, as in the reference."""
-    sink_tokens, window_size = decode_window(pattern)
+    ``pattern`` is a ``SparseAttentionPattern`` (dense, sliding_window, sliding_window_sink, block_sparse); every
+    sequence needs at least one token, as in the reference.  A block_sparse row that hides every key yields zeros."""
+    if not isinstance(pattern, SparseAttentionPattern):
+        raise TypeError("pattern must be a SparseAttentionPattern")
+    block_sparse = pattern.validate().pattern == "block_sparse"
+    sink_tokens, window_size = (0, 0) if block_sparse else decode_window(pattern)
     B, MAX_S, PAGE_SIZE, MAX_BLOCKS, Hq, Hkv, D, NUM_PAGES = _validate_paged_quantized_decode_inputs(q, paged_qkv)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
@@ -367,5 +377,9 @@ def sparse_paged_quantized_kv_gqa_decode_attention(q, paged_qkv: PagedQuantizedK
         raise TypeError(f"q dtype must be float16 or bfloat16, got {q.dtype}")
     _cabi.require_cuda(q, paged_qkv.k_pages_q, paged_qkv.v_pages_q, paged_qkv.k_scales, paged_qkv.v_scales,
                        paged_qkv.block_table, paged_qkv.lengths)
-    out = paged_attention_launch(q.reshape(B, Hq, D), paged_qkv, scale, sink_tokens=sink_tokens, window_size=window_size)
+    if block_sparse:
+        mask, block_size = decode_block_mask(pattern, q.device)
+        out = paged_attention_launch(q.reshape(B, Hq, D), paged_qkv, scale, block_mask=mask, block_size=block_size)
+    else:
+        out = paged_attention_launch(q.reshape(B, Hq, D), paged_qkv, scale, sink_tokens=sink_tokens, window_size=window_size)
     return out.reshape(B, 1, Hq, D)

@@ -23,7 +23,7 @@ from .gqa_ops import validate_gqa_heads
 from .paged_kv_ops import normalize_positions
 from .paged_quantized_kv_ops import PagedQuantizedKVCache, _quantize_groups, paged_attention_launch
 from .quant_ops import dequant_codes
-from .sparse_attention_ops import SparseAttentionPattern, decode_window
+from .sparse_attention_ops import SparseAttentionPattern, decode_block_mask, decode_window
 
 _MAX_HEAD_DIM = 128
 _FAST_PAGE = 16
@@ -273,7 +273,7 @@ def quantized_kv_sparse_gqa_decode_attention(q, qkv_cache, lengths, pattern, *, 
     """The reference offers this with ``backend="reference"`` only; its Metal backends raise NotImplementedError
     (ops/quantized_kv_cache_ops.py:586-603), and so do the Metal names here.  ``backend="cuda"`` runs the dense,
     sliding_window and sliding_window_sink patterns on the split-KV kernels, which skip the pages outside the
-    window."""
+    window, and block_sparse on the same kernels over the attended pages."""
     if not isinstance(pattern, SparseAttentionPattern):
         raise TypeError("pattern must be a SparseAttentionPattern")
     name = backend.lower()
@@ -284,7 +284,8 @@ def quantized_kv_sparse_gqa_decode_attention(q, qkv_cache, lengths, pattern, *, 
             "Metal sparse+quantized backend is not implemented yet. "
             "Use backend='reference' or see sparse+gqa decode attention for fp16."
         )
-    sink_tokens, window_size = decode_window(pattern)
+    block_sparse = pattern.validate().pattern == "block_sparse"
+    sink_tokens, window_size = (0, 0) if block_sparse else decode_window(pattern)
     lengths_arr, B, MAX_S, Hq, Hkv, D = _validate_quantized_decode_inputs(q, qkv_cache, lengths)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
@@ -293,6 +294,11 @@ def quantized_kv_sparse_gqa_decode_attention(q, qkv_cache, lengths, pattern, *, 
     if q.dtype not in (torch.float16, torch.bfloat16):
         raise TypeError(f"q dtype must be float16 or bfloat16, got {q.dtype}")
     _cabi.require_cuda(q, qkv_cache.k_q, qkv_cache.v_q, qkv_cache.k_scales, qkv_cache.v_scales)
-    out = paged_attention_launch(q.reshape(B, Hq, D), as_paged_view(qkv_cache, lengths_arr), scale,
-                                 sink_tokens=sink_tokens, window_size=window_size)
+    if block_sparse:
+        mask, block_size = decode_block_mask(pattern, q.device)
+        out = paged_attention_launch(q.reshape(B, Hq, D), as_paged_view(qkv_cache, lengths_arr), scale,
+                                     block_mask=mask, block_size=block_size)
+    else:
+        out = paged_attention_launch(q.reshape(B, Hq, D), as_paged_view(qkv_cache, lengths_arr), scale,
+                                     sink_tokens=sink_tokens, window_size=window_size)
     return out.reshape(B, 1, Hq, D)

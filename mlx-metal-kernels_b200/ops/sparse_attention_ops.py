@@ -1,9 +1,11 @@
 """Sparse attention patterns as far as the quantized decode path uses them.
 
 Mirrors the pattern dataclass of ops/sparse_attention_ops.py:20-47 of the reference.  For single-token
-decode the query sits at position L - 1 of a sequence of L tokens, so a pattern reduces to a
+decode the query sits at position L - 1 of a sequence of L tokens, so a sliding-window pattern reduces to a
 (sink_tokens, window_size) pair: the row of build_sparse_attention_mask
-(ops/sparse_attention_ops.py:85-105) that a decode step sees is ``j < sink_tokens or j >= L - window_size``.
+(ops/sparse_attention_ops.py:85-105) that a decode step sees is ``j < sink_tokens or j >= L - window_size``;
+a block_sparse pattern reduces to row (L - 1) // block_size of its block mask
+(ops/sparse_attention_ops.py:98-107).
 """
 from __future__ import annotations
 
@@ -53,4 +55,19 @@ def decode_window(pattern: SparseAttentionPattern) -> tuple[int, int]:
         return 0, int(pattern.window_size)
     if pattern.pattern == "sliding_window_sink":
         return int(pattern.sink_tokens), int(pattern.window_size)
-    raise NotImplementedError("block_sparse decode over a quantized cache is not implemented in the CUDA backend")
+    raise ValueError("block_sparse has no (sink, window) form; use decode_block_mask")
+
+
+def decode_block_mask(pattern: SparseAttentionPattern, device):
+    """(block_mask uint8 [n_qblocks, n_kblocks] on ``device``, block_size) of a block_sparse pattern."""
+    import torch
+    pattern = pattern.validate()
+    if pattern.pattern != "block_sparse":
+        raise ValueError("decode_block_mask needs a block_sparse pattern")
+    mask = pattern.block_mask
+    if hasattr(mask, "tolist") and not isinstance(mask, torch.Tensor):
+        mask = mask.tolist()
+    mask = torch.as_tensor(mask)
+    if mask.ndim != 2 or mask.shape[0] == 0 or mask.shape[1] == 0:
+        raise ValueError(f"block_mask must be 2-D [q_blocks, k_blocks], got {tuple(mask.shape)}")
+    return (mask != 0).to(device=device, dtype=torch.uint8).contiguous(), int(pattern.block_size)

@@ -140,14 +140,16 @@ def pages_to_contiguous_kv(K_pages, V_pages, block_table, lengths, *, max_seq_le
     return K_cache, V_cache
 
 
-def reference_paged_quantized_kv_gqa_decode_attention(q, cache, *, scale=None, window=None):
+def reference_paged_quantized_kv_gqa_decode_attention(q, cache, *, scale=None, window=None, keep_fn=None):
     """softmax(scale * q K^T) V over the valid tokens of every sequence, K and V dequantised
     and rounded to fp16 first, fp32 math, result cast to q.dtype
     (ops/paged_quantized_kv_ops.py:469-515, generalised to ragged lengths).
 
     ``window=(sink, recent)`` keeps only the first ``sink`` and last ``recent`` valid positions,
     the mask shape used by the reference's sparse scaffold
-    (ops/paged_quantized_kv_ops.py:669-714); ``None`` means dense.
+    (ops/paged_quantized_kv_ops.py:669-714); ``None`` means dense.  ``keep_fn(L)`` -> bool [L] is any other decode
+    row of that scaffold's mask (block_sparse).  The scaffold masks scores to -1e9; dropping the masked keys is the
+    same softmax whenever one key is visible, and a row that hides every key gives zeros here.
     """
     if q.ndim != 4 or q.shape[1] != 1:
         raise ValueError(f"q must have shape [B,1,Hq,D], got {tuple(q.shape)}")
@@ -180,6 +182,8 @@ def reference_paged_quantized_kv_gqa_decode_attention(q, cache, *, scale=None, w
         if window is not None:
             sink, recent = window
             keep &= (pos < sink) | (pos >= L - recent)
+        if keep_fn is not None:
+            keep &= keep_fn(L)
         pos, pages = pos[keep], pages[keep]
         if pos.numel() == 0:
             continue

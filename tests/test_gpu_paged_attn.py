@@ -231,3 +231,94 @@ def test_cluster_kernel_matches_oracle(cuda, bits, lengths, Hq, Hkv, G):
     assert float((got.cpu().float() - want.float()).abs().max()) <= ATOL
     assert float((got.float() - split.float()).abs().max()) <= ATOL
     assert cabi.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("block_size", [16, 32, 64, 8, 24])
+@pytest.mark.parametrize("Hq,Hkv,D,P", [(8, 2, 128, 16), (32, 8, 128, 16), (6, 3, 64, 8)])
+def test_block_sparse_decode_matches_oracle(cuda, bits, block_size, Hq, Hkv, D, P):
+    """block_sparse decode: key j of a sequence of L tokens is attended iff block_mask[(L-1)//bs][j//bs].  Block sizes
+    that are a multiple of the page size run the dense kernels on a compacted block table, the others (8, 24) the
+    per-token test of the general kernel; both against the oracle's masked softmax."""
+    sparse_ops = importlib.import_module("mlx_metal_kernels_b200.ops.sparse_attention_ops")
+    from oracle.sparse_attention_ops import decode_row
+    lengths = [1, 15, 16, 17, 37, 200, 333, 64]
+    nblk = (max(lengths) + block_size - 1) // block_size
+    g = torch.Generator().manual_seed(block_size + bits)
+    mask = torch.rand((nblk, nblk), generator=g) < 0.45
+    mask |= torch.eye(nblk, dtype=torch.bool)                   # every query block sees itself: no empty rows
+    case = _case_with_lengths(lengths, Hkv, D, P, bits, 32, seed=500 + block_size)
+    q = synth.activations((len(lengths), 1, Hq, D), 72)
+    keep = lambda L: decode_row(L, "block_sparse", block_size=block_size, block_mask=mask)   # noqa: E731
+    want = opq.reference_paged_quantized_kv_gqa_decode_attention(q, _oracle_cache(case), keep_fn=keep)
+    pattern = sparse_ops.SparseAttentionPattern("block_sparse", block_size=block_size, block_mask=mask)
+    got = pq_ops.sparse_paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), pattern)
+    err = float((got.cpu().float() - want.float()).abs().max())
+    assert err <= ATOL, err
+    # an all-ones mask is the dense result
+    ones = sparse_ops.SparseAttentionPattern("block_sparse", block_size=block_size, block_mask=torch.ones_like(mask))
+    got1 = pq_ops.sparse_paged_quantized_kv_gqa_decode_attention(q.to(cuda), _device_cache(case, cuda), ones)
+    dense = opq.reference_paged_quantized_kv_gqa_decode_attention(q, _oracle_cache(case))
+    assert float((got1.cpu().float() - dense.float()).abs().max()) <= ATOL
+    # a row that hides every key gives zeros
+    hidden = mask.clone()
+    hidden[(lengths[5] - 1) // block_size] = False
+    got0 = pq_ops.sparse_paged_quantized_kv_gqa_decode_attention(
+        q.to(cuda), _device_cache(case, cuda),
+        sparse_ops.SparseAttentionPattern("block_sparse", block_size=block_size, block_mask=hidden))
+    assert float(got0[5].abs().max()) == 0.0
+    assert cabi.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D,P", [(4, 4, 64, 4), (8, 2, 128, 16), (32, 8, 128, 16), (6, 3, 40, 8), (16, 1, 128, 16),
+                                        (12, 2, 20, 5)])
+def test_fp16_paged_gqa_decode_matches_oracle(cuda, dtype, Hq, Hkv, D, P):
+    """Decode attention over an unquantised paged cache (fp16 / bf16), equal and grouped heads, ragged lengths, pages
+    drawn from a shuffled pool, D not a multiple of 8, unassigned block-table entries past the length."""
+    gqa_ops = importlib.import_module("mlx_metal_kernels_b200.ops.gqa_ops")
+    lengths = [1, 15, 16, 17, 37, 200, 777, 0]
+    B = len(lengths)
+    blocks = [(L + P - 1) // P for L in lengths]
+    num_pages = sum(blocks) + 5
+    max_blocks = max(blocks) + 1
+    g = torch.Generator().manual_seed(D + Hq)
+    perm = torch.randperm(num_pages, generator=g).to(torch.int32)
+    bt = torch.full((B, max_blocks), -1, dtype=torch.int32)
+    cur = 0
+    for b, n in enumerate(blocks):
+        bt[b, :n] = perm[cur:cur + n]
+        cur += n
+    K = torch.randn((num_pages, P, Hkv, D), generator=g).to(dtype)
+    V = torch.randn((num_pages, P, Hkv, D), generator=g).to(dtype)
+    q = torch.randn((B, 1, Hq, D), generator=g).to(dtype)
+    ln = torch.tensor(lengths, dtype=torch.int32)
+    want = opk.reference_paged_gqa_decode_attention(q, K, V, bt, ln)
+    got = gqa_ops.paged_gqa_decode_attention(q.to(cuda), K.to(cuda), V.to(cuda), bt.to(cuda), ln.to(cuda))
+    assert got.shape == q.shape and got.dtype == dtype
+    tol = ATOL if dtype == torch.float16 else 1.6e-2             # one bf16 rounding of values up to ~2
+    assert float((got.cpu().float() - want.float()).abs().max()) <= tol
+    assert float(got[-1].abs().max()) == 0.0                     # no valid token: zeros
+    if Hq == Hkv:
+        got2 = pkv_ops.paged_decode_attention(q.to(cuda), K.to(cuda), V.to(cuda), bt.to(cuda), ln.to(cuda), backend="metal_d64")
+        assert torch.equal(got2, got)
+        with pytest.raises(ValueError, match=r"q must have shape \[B,1,H,D\]"):
+            pkv_ops.paged_decode_attention(q[:, :, :1].to(cuda), K.to(cuda), V.to(cuda), bt.to(cuda), ln.to(cuda))
+
+
+def test_fp16_paged_gqa_decode_long_context(cuda):
+    """Context 4096, batch 16, 32 / 8 heads of 128: the split-over-CTAs path with its merge kernel."""
+    gqa_ops = importlib.import_module("mlx_metal_kernels_b200.ops.gqa_ops")
+    B, Hq, Hkv, D, P, ctx = 16, 32, 8, 128, 16, 4096
+    g = torch.Generator().manual_seed(3)
+    blocks = ctx // P
+    num_pages = B * blocks
+    bt = torch.randperm(num_pages, generator=g).to(torch.int32).reshape(B, blocks)
+    K = torch.randn((num_pages, P, Hkv, D), generator=g).to(torch.float16)
+    V = torch.randn((num_pages, P, Hkv, D), generator=g).to(torch.float16)
+    q = torch.randn((B, 1, Hq, D), generator=g).to(torch.float16)
+    ln = torch.randint(1, ctx + 1, (B,), generator=g, dtype=torch.int32)
+    ln[0] = ctx
+    want = opk.reference_paged_gqa_decode_attention(q, K, V, bt, ln)
+    got = gqa_ops.paged_gqa_decode_attention(q.to(cuda), K.to(cuda), V.to(cuda), bt.to(cuda), ln.to(cuda))
+    assert float((got.cpu().float() - want.float()).abs().max()) <= ATOL

@@ -312,9 +312,15 @@ def test_contiguous_quantized_cache_host_logic():
         qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("dense"))
     with pytest.raises(NotImplementedError):
         qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("dense"), backend="metal_q4")
-    with pytest.raises(NotImplementedError, match="block_sparse"):
+    with pytest.raises(cabi.B200QError, match="no CPU route"):      # block_sparse is served by the CUDA backend too
         qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("block_sparse", block_size=4, block_mask=[[1]]),
                                                          backend="cuda")
+    with pytest.raises(ValueError, match="block_sparse requires block_mask"):
+        qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("block_sparse", block_size=4), backend="cuda")
+    with pytest.raises(ValueError, match="decode_block_mask"):
+        sparse_ops.decode_window(P("block_sparse", block_size=4, block_mask=[[1]]))
+    bm, bs = sparse_ops.decode_block_mask(P("block_sparse", block_size=4, block_mask=[[1, 0], [2, 1]]), "cpu")
+    assert bs == 4 and bm.dtype == torch.uint8 and bm.tolist() == [[1, 0], [1, 1]]
     with pytest.raises(ValueError, match="window_size > 0"):
         qkv_ops.quantized_kv_sparse_gqa_decode_attention(q, cache, None, P("sliding_window"), backend="cuda")
     with pytest.raises(cabi.B200QError, match="no CPU route"):

@@ -135,3 +135,27 @@ def test_block_table_lookup_matches_metal_kernel_body(golden):
     pages, offsets = paged_kv_ops.reference_block_table_lookup(t(golden["mtl_btl_table"]), t(golden["mtl_btl_pos"]), 8)
     assert torch.equal(pages, t(golden["mtl_btl_pages"]))
     assert torch.equal(offsets, t(golden["mtl_btl_offsets"]))
+
+
+def test_sparse_mask_rule_known_answers():
+    """The mask rows the reference's own tests expect of build_sparse_attention_mask
+    (tests/test_sparse_attention_reference.py:15-39): sliding window, window + sinks, overlap of sinks and window,
+    and the block_sparse rule on a 2x2 block mask."""
+    from oracle.sparse_attention_ops import build_sparse_attention_mask, decode_row
+    rows = build_sparse_attention_mask(4, 6, "sliding_window", window_size=3, start_position=2).tolist()
+    assert rows[0] == [True, True, True, False, False, False]
+    assert rows[1] == [False, True, True, True, False, False]
+    assert rows[3] == [False, False, False, True, True, True]
+    row = build_sparse_attention_mask(1, 6, "sliding_window_sink", window_size=3, sink_tokens=2, start_position=4)
+    assert row.tolist()[0] == [True, True, True, True, True, False]
+    row = build_sparse_attention_mask(1, 5, "sliding_window_sink", window_size=4, sink_tokens=2, start_position=1)
+    assert row.tolist()[0] == [True, True, False, False, False]
+    block_mask = [[True, False], [True, True]]
+    m = build_sparse_attention_mask(4, 4, "block_sparse", block_size=2, block_mask=block_mask)
+    assert tuple(m.shape) == (4, 4)
+    assert m.tolist() == [[True, False, False, False], [True, True, False, False],
+                          [True, True, True, False], [True, True, True, True]]
+    # the decode row is the last row of the square mask
+    assert decode_row(4, "block_sparse", block_size=2, block_mask=block_mask).tolist() == m.tolist()[3]
+    assert decode_row(6, "sliding_window_sink", window_size=3, sink_tokens=2).tolist() == \
+        build_sparse_attention_mask(6, 6, "sliding_window_sink", window_size=3, sink_tokens=2).tolist()[5]
