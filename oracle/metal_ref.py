@@ -146,3 +146,118 @@ def block_table_lookup(block_table, positions, page_size):
     offsets = np.empty((B,), dtype=np.int32)
     _call(_get().ref_block_table_lookup, bt, pos, _i32(B, max_blocks, page_size), page_ids, offsets, B)
     return page_ids, offsets
+
+
+# ---------------------------------------------------------------------------------------------
+# bodies pinned since the threadgroup emulator exists (metal_shim.cpp, second half)
+# ---------------------------------------------------------------------------------------------
+def _call_tg(fn, *arrays_then_groups_threads):
+    *arrays, groups, threads = arrays_then_groups_threads
+    for a in arrays:
+        assert isinstance(a, np.ndarray) and a.flags["C_CONTIGUOUS"]
+    fn(*[ctypes.c_void_p(a.ctypes.data) for a in arrays], ctypes.c_longlong(int(groups)), ctypes.c_longlong(int(threads)))
+
+
+def residual_add(x, residual):
+    """kernels/residual_add.metal; meta as in ops/fused_ops.py:168-180 (total element count)."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    r = np.ascontiguousarray(residual, dtype=np.float16)
+    y = np.empty_like(x)
+    _call(_get().ref_residual_add_f16, x, r, _i32(x.size), y, x.size)
+    return y
+
+
+def swiglu(gate, up):
+    """kernels/swiglu.metal; gate/up [B,S,D], meta = (B, S, D) as in ops/activation_ops.py:112-123."""
+    gate = np.ascontiguousarray(gate, dtype=np.float16)
+    up = np.ascontiguousarray(up, dtype=np.float16)
+    B, S, D = gate.shape
+    out = np.empty_like(gate)
+    _call(_get().ref_swiglu_f16, gate, up, _i32(B, S, D), out, gate.size)
+    return out
+
+
+def rms_norm(x, weight, eps, threads=256):
+    """kernels/rms_norm.metal: one threadgroup of 256 threads per row, meta = (B, S, D) (ops/norm_ops.py:12,76-85)."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    w = np.ascontiguousarray(weight, dtype=np.float16)
+    B, S, D = x.shape
+    y = np.empty_like(x)
+    _call_tg(_get().ref_rms_norm_f16, x, w, _i32(B, S, D), np.asarray([eps], dtype=np.float32), y, B * S, threads)
+    return y
+
+
+def rmsnorm_residual(x, residual, weight, eps, threads=256):
+    """kernels/rmsnorm_residual.metal: (y, z), meta = (rows, D), 256 threads per row (ops/fused_ops.py:16,228-240)."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    r = np.ascontiguousarray(residual, dtype=np.float16)
+    w = np.ascontiguousarray(weight, dtype=np.float16)
+    D = x.shape[-1]
+    rows = x.size // D
+    y, z = np.empty_like(x), np.empty_like(x)
+    _call_tg(_get().ref_rmsnorm_residual_f16, x, r, w, _i32(rows, D), np.asarray([eps], dtype=np.float32), y, z, rows,
+             threads)
+    return y, z
+
+
+def matvec_parallel(bits, x, codes, scales, zeros, group_size, threads=128):
+    """kernels/q{4,8}_matvec_decode_parallel.metal: one threadgroup of 128 threads per output
+    (ops/quant_ops.py:24, meta as built for the ``metal_parallel`` backend)."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    B, K = x.shape
+    N = codes.shape[0]
+    groups = (K + group_size - 1) // group_size
+    z, has_zero = _zeros_or_dummy(zeros, scales)
+    y = np.empty((B, N), dtype=np.float16)
+    if bits == 4:
+        meta = _i32(B, N, K, codes.shape[1], group_size, groups, has_zero)
+        _call_tg(_get().ref_q4_matvec_parallel_f16, x, codes, _f32(scales), z, meta, y, B * N, threads)
+    else:
+        meta = _i32(B, N, K, group_size, groups, has_zero)
+        _call_tg(_get().ref_q8_matvec_parallel_f16, x, codes, _f32(scales), z, meta, y, B * N, threads)
+    return y
+
+
+def matvec_tiled(bits, x, codes, scales, zeros, group_size, n_tile=4, threads=128):
+    """kernels/q{4,8}_matvec_decode_tiled.metal: four outputs per threadgroup of 128 threads
+    (ops/quant_ops.py:25-26, 457-480)."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    B, K = x.shape
+    N = codes.shape[0]
+    groups = (K + group_size - 1) // group_size
+    tiles = B * ((N + n_tile - 1) // n_tile)
+    z, has_zero = _zeros_or_dummy(zeros, scales)
+    y = np.empty((B, N), dtype=np.float16)
+    if bits == 4:
+        meta = _i32(B, N, K, codes.shape[1], group_size, groups, has_zero, n_tile)
+        _call_tg(_get().ref_q4_matvec_tiled_f16, x, codes, _f32(scales), z, meta, y, tiles, threads)
+    else:
+        meta = _i32(B, N, K, group_size, groups, has_zero, n_tile)
+        _call_tg(_get().ref_q8_matvec_tiled_f16, x, codes, _f32(scales), z, meta, y, tiles, threads)
+    return y
+
+
+def gate_up_tiled(bits, x, gate_codes, up_codes, gate_scales, up_scales, gate_zeros, up_zeros, group_size, n_tile=4,
+                  threads=128):
+    """kernels/q{4,8}_gate_up_matvec_tiled.metal: (gate, up) rows (ops/quant_ops.py:634-738)."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    gc = np.ascontiguousarray(gate_codes, dtype=np.uint8)
+    uc = np.ascontiguousarray(up_codes, dtype=np.uint8)
+    rows, K = x.shape
+    N = gc.shape[0]
+    groups = (K + group_size - 1) // group_size
+    tiles = rows * ((N + n_tile - 1) // n_tile)
+    gz, has_gz = _zeros_or_dummy(gate_zeros, gate_scales)
+    uz, has_uz = _zeros_or_dummy(up_zeros, up_scales)
+    gate = np.empty((rows, N), dtype=np.float16)
+    up = np.empty((rows, N), dtype=np.float16)
+    if bits == 4:
+        meta = _i32(rows, K, N, gc.shape[1], group_size, groups, has_gz, has_uz, n_tile)
+        fn = _get().ref_q4_gate_up_tiled_f16
+    else:
+        meta = _i32(rows, K, N, group_size, groups, has_gz, has_uz, n_tile)
+        fn = _get().ref_q8_gate_up_tiled_f16
+    _call_tg(fn, x, gc, uc, _f32(gate_scales), _f32(up_scales), gz, uz, meta, gate, up, tiles, threads)
+    return gate, up

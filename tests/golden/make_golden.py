@@ -11,7 +11,8 @@ Two sources, both the reference's own code, neither needing MLX:
   ``(q - zero) * scale`` dequantisation.
 * the Metal kernel bodies under ``kernels/`` compiled as C++ (oracle/metal_shim.cpp): dequant,
   serial matvec, paged q4/q8 GQA decode attention (ragged lengths, permuted block table with -1
-  entries), fused SwiGLU, block-table lookup.
+  entries), fused SwiGLU, block-table lookup, residual add, SwiGLU, and - on the shim's threadgroup emulator -
+  RMSNorm, fused residual + RMSNorm, the ``parallel`` and ``tiled`` matvec bodies and the tiled gate/up body.
 
 Inputs come from numpy's seeded generator and are stored next to the outputs, so the fixtures
 are self-contained.
@@ -145,6 +146,34 @@ def main():
             for name, val in dict(q=q, kq=kq, vq=vq, ks=ks, vs=vs, lengths=np.asarray(lengths, np.int32),
                                   shape=np.asarray((B, max_s, Hkv, D), np.int32), out=o).items():
                 out[f"{key}_{name}"] = val
+
+    # bodies that cooperate inside a threadgroup (run on the shim's threadgroup emulator), and the two element-wise
+    # bodies added with them; a generator of their own keeps every array above unchanged
+    rng3 = np.random.default_rng(20240608)
+    x = rng3.standard_normal((2, 3, 200)).astype(np.float16)
+    res = rng3.standard_normal((2, 3, 200)).astype(np.float16)
+    w = (rng3.random(200) + 0.5).astype(np.float16)
+    out["tg_norm_x"], out["tg_norm_res"], out["tg_norm_w"] = x, res, w
+    out["tg_residual_add"] = metal_ref.residual_add(x, res)
+    out["tg_swiglu"] = metal_ref.swiglu(x * np.float16(3), res)
+    out["tg_rms_norm"] = metal_ref.rms_norm(x, w, 1e-5)
+    out["tg_rmsnorm_residual_y"], out["tg_rmsnorm_residual_z"] = metal_ref.rmsnorm_residual(x, res, w, 1e-5)
+    for bits in (4, 8):
+        N, K, G = 10, 320, 32                       # N not a multiple of the 4-row tile
+        cols = K // 2 if bits == 4 else K
+        key = f"tg_q{bits}"
+        codes = rng3.integers(0, 256, size=(N, cols), dtype=np.uint8)
+        codes2 = rng3.integers(0, 256, size=(N, cols), dtype=np.uint8)
+        scales = (rng3.standard_normal((N, K // G)) * 0.01).astype(np.float16)
+        scales2 = (rng3.standard_normal((N, K // G)) * 0.01).astype(np.float16)
+        zeros = (rng3.standard_normal((N, K // G)) * 3 + (8 if bits == 4 else 128)).astype(np.float16)
+        xm = rng3.standard_normal((3, K)).astype(np.float16)
+        for name, val in dict(codes=codes, codes2=codes2, scales=scales, scales2=scales2, zeros=zeros, x=xm).items():
+            out[f"{key}_{name}"] = val
+        out[f"{key}_parallel"] = metal_ref.matvec_parallel(bits, xm, codes, scales, zeros, G)
+        out[f"{key}_tiled"] = metal_ref.matvec_tiled(bits, xm, codes, scales, zeros, G)
+        out[f"{key}_tiled_nozero"] = metal_ref.matvec_tiled(bits, xm, codes, scales, None, G)
+        out[f"{key}_gate"], out[f"{key}_up"] = metal_ref.gate_up_tiled(bits, xm, codes, codes2, scales, scales2, zeros, None, G)
 
     dest = Path(__file__).resolve().parent / "hotpath_golden.npz"
     np.savez_compressed(dest, **out)

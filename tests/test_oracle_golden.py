@@ -159,3 +159,62 @@ def test_sparse_mask_rule_known_answers():
     assert decode_row(4, "block_sparse", block_size=2, block_mask=block_mask).tolist() == m.tolist()[3]
     assert decode_row(6, "sliding_window_sink", window_size=3, sink_tokens=2).tolist() == \
         build_sparse_attention_mask(6, 6, "sliding_window_sink", window_size=3, sink_tokens=2).tolist()[5]
+
+
+def _ulp16(a):
+    """Spacing of fp16 at |a| (normal range)."""
+    a = a.float().abs().clamp_min(2.0 ** -14)
+    return torch.exp2(torch.floor(torch.log2(a)) - 10)
+
+
+def test_residual_add_and_swiglu_match_metal_kernel_bodies(golden):
+    x, res = t(golden["tg_norm_x"]), t(golden["tg_norm_res"])
+    assert torch.equal(elementwise_ops.reference_residual_add(x, res), t(golden["tg_residual_add"]))     # one rounding
+    got = elementwise_ops.reference_swiglu(x * 3, res)
+    want = t(golden["tg_swiglu"])
+    assert bool(((got.float() - want.float()).abs() <= _ulp16(want)).all())      # expf differs in its last bit
+
+
+def test_rms_norm_matches_metal_kernel_bodies(golden):
+    """rms_norm.metal and rmsnorm_residual.metal on the threadgroup emulator.  The sum of squares is taken in another
+    order (strided partials, simd_sum, whose order Metal leaves open) and rmsnorm_residual.metal normalises the unrounded
+    x + residual where the MLX reference rounds z first, so outputs may differ by one fp16 step; z is exact."""
+    x, res, w = t(golden["tg_norm_x"]), t(golden["tg_norm_res"]), t(golden["tg_norm_w"])
+    got = elementwise_ops.reference_rms_norm(x, w, eps=1e-5)
+    want = t(golden["tg_rms_norm"])
+    diff = (got.float() - want.float()).abs()
+    assert bool((diff <= _ulp16(want)).all()) and float((diff > 0).float().mean()) < 0.02
+    y, z = elementwise_ops.reference_rmsnorm_residual(x, res, w, eps=1e-5, return_residual=True)
+    assert torch.equal(z, t(golden["tg_rmsnorm_residual_z"]))
+    want_y = t(golden["tg_rmsnorm_residual_y"])
+    diff = (y.float() - want_y.float()).abs()
+    assert bool((diff <= _ulp16(want_y)).all()) and float((diff > 0).float().mean()) < 0.25
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_tiled_and_parallel_matvec_match_metal_kernel_bodies(golden, bits):
+    """The ``metal_parallel`` and ``metal_tiled`` bodies (threadgroup tree reductions, fp32 weights) against the
+    oracle's matvec (fp16-rounded W, fp32 matmul): same function up to the fp16 weight rounding, as for the serial
+    body; N = 10 leaves a ragged last tile."""
+    key = f"tg_q{bits}"
+    codes, scales, zeros, x = (t(golden[f"{key}_{n}"]) for n in ("codes", "scales", "zeros", "x"))
+    fn = oq.reference_q4_matvec_decode if bits == 4 else oq.reference_q8_matvec_decode
+    for z, names in ((zeros, ("parallel", "tiled")), (None, ("tiled_nozero",))):
+        got = fn(x, codes, scales, z, group_size=32).float()
+        for name in names:
+            want = t(golden[f"{key}_{name}"]).float()
+            assert float((got - want).norm() / want.norm()) < 1.5e-3, name
+    # the two Metal bodies themselves agree to summation order
+    a, b = t(golden[f"{key}_parallel"]).float(), t(golden[f"{key}_tiled"]).float()
+    assert float((a - b).norm() / b.norm()) < 1e-3
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_gate_up_matches_metal_kernel_body(golden, bits):
+    key = f"tg_q{bits}"
+    codes, codes2, scales, scales2, zeros, x = (t(golden[f"{key}_{n}"]) for n in
+                                                ("codes", "codes2", "scales", "scales2", "zeros", "x"))
+    gate, up = oq.reference_gate_up_matvec(x, codes, codes2, scales, scales2, zeros, None, bits=bits, group_size=32)
+    for got, name in ((gate, "gate"), (up, "up")):
+        want = t(golden[f"{key}_{name}"]).float()
+        assert float((got.float().reshape(want.shape) - want).norm() / want.norm()) < 1.5e-3, name
