@@ -38,9 +38,10 @@ METRIC = "decode tokens/s"
 WORKLOAD = "c5_llama3_8b_shaped_q4_stack_32_layers_q8_paged_kv_ctx4096"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of one matvec launch, per shape, from the ncu
-# captures summarised under profiles/ (one kernel, two launches each); the kernels read every weight byte once.
-DRAM_TRAFFIC_RATIO = {"qkv": 1.006, "o": 1.006, "gate": 1.004, "down": 1.005}
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of one batch-1 matvec launch, per shape of the
+# stack, from the ncu captures summarised in profiles/qgemv_kernel_c5_stack_shapes_b1.md (one kernel, two launches
+# each, `bench.py --profile-case <shape>_q4_b1`); the kernels read every weight byte once.
+DRAM_TRAFFIC_RATIO = {"qkv": 1.0040, "o": 1.0064, "gate": 1.0075, "down": 1.0018}
 
 
 def measured_peaks():
@@ -199,7 +200,8 @@ def kernel_microbenchmarks(device, peak, all_configs=False, cpu=False):
                 xc, rc = x.cpu(), res.cpu()
                 cpu_fn = lambda: om.reference_quantized_mlp_block(xc, rc, nw, gw, gs, uw, us, dw, ds, gate_zeros=gz,
                                                                   up_zeros=uz, down_zeros=dz, bits=4, group_size=64)
-            record(f"c3_q4_mlp_block_b{B}_4096_14336_g64", sec, nbytes, R, extra={"launches_per_block": 2}, cpu_fn=cpu_fn)
+            record(f"c3_q4_mlp_block_b{B}_4096_14336_g64", sec, nbytes, R, extra={"launches_per_block": 2 if B < 5 else 3},
+                   cpu_fn=cpu_fn)
         del devs
         torch.cuda.empty_cache()
     # C4
@@ -458,13 +460,14 @@ def run_own(args):
     stack.capture()
 
     # ---- headline: K graph-replayed decode steps, device-timed ----
-    sec_per_step, repeats, clocks = time_steps(stack, tokens, args.steps, warmup, barrier, local, world)
+    sec_per_step, repeats, clocks = time_steps(stack, tokens, args.steps, warmup, barrier, local, world, min_seconds=args.min_seconds)
     tokens_per_s = B / sec_per_step
 
     # ---- end to end: host token ids in, host hidden state out, every step ----
     host_tokens = tokens.cpu().pin_memory()
     host_out = torch.empty((B, cfg.hidden), dtype=torch.float16).pin_memory()
-    e2e_sec, e2e_repeats, _ = time_steps(stack, host_tokens, args.steps, 3, barrier, local, world, e2e=True, host_out=host_out)
+    e2e_sec, e2e_repeats, _ = time_steps(stack, host_tokens, args.steps, 3, barrier, local, world, e2e=True, host_out=host_out,
+                                         min_seconds=args.min_seconds)
 
     # ---- roofline of the dominant kernel: the matvec launches of one step, timed alone ----
     run_gemv, n_gemv = gemv_only_graph(stack)
@@ -510,7 +513,7 @@ def run_own(args):
                      "frac_of_peak": round(step_bytes / sec_per_step / 1e9 / peak, 4)},
         "roofline": {"bound": "hbm", "kernel": "qgemv_kernel (all q4 matvec launches of one step, timed alone)",
                      "achieved": round(gemv_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gemv_gbs / peak, 4),
-                     "traffic": round(gemv_traffic / n_gemv), "traffic_source": "per-shape ncu captures (profiles/): dram bytes read+written / algorithmic bytes 1.004-1.006, applied to this launch mix",
+                     "traffic": round(gemv_traffic / n_gemv), "traffic_source": "per-shape ncu captures (profiles/qgemv_kernel_c5_stack_shapes_b1.md): dram bytes read+written / algorithmic bytes 1.002-1.008 for the QKV, O, gate/up and down shapes, applied to this launch mix",
                      "peak_kind": peak_kind, "launches": n_gemv,
                      "algorithmic_bytes_per_launch": round(gemv_bytes / n_gemv), "us_per_launch": round(gemv_sec / n_gemv * 1e6, 3)},
         "e2e": {"value": round(B / e2e_sec, 2), "unit": "tokens/s", "ms_per_step": round(e2e_sec * 1e3, 4),
@@ -544,7 +547,7 @@ def run_own(args):
         torch.cuda.empty_cache()
     if world > 1:
         line["tp_parity"] = tp_parity_check(device, rank, world, group)
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.step_only:
         line["kernels"] = kernel_microbenchmarks(device, peak, all_configs=True)
         line["cpu_baseline"] = cpu_baseline(B, budget_s=20.0)
     if rank == 0:
@@ -570,6 +573,98 @@ def run_kernels_only(cpu=False):
     peak, peak_kind = measured_peaks()
     print(json.dumps({"kernels": kernel_microbenchmarks(torch.device("cuda", 0), peak, all_configs=True, cpu=cpu),
                       "peak": peak, "peak_kind": peak_kind}), flush=True)
+
+
+PROFILE_CASES = ("gate_up_q4_b1", "qkv_q4_b1", "o_q4_b1", "down_q4_b1", "gate_up_q4_b8", "gate_up_q4_b32", "down_q4_b8",
+                 "matvec_q8_b8", "mlp_block_q4_b8", "mlp_block_q4_b32", "attn_cluster_q8_b1_ctx4096", "attn_splitkv_q8_b16",
+                 "attn_fp16_b16")
+
+
+def run_profile_case(name):
+    """One kernel shape, a handful of eager launches over three rotating operand copies (more than L2 in all, a few
+    hundred MB on the device): the small case an ``ncu -k ... -c 2`` capture is meant to be pointed at."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    entry.load_package()
+    q = importlib.import_module(f"{entry.PKG_ALIAS}.ops.quant_ops")
+    pq = importlib.import_module(f"{entry.PKG_ALIAS}.ops.paged_quantized_kv_ops")
+    gqa = importlib.import_module(f"{entry.PKG_ALIAS}.ops.gqa_ops")
+    synth = importlib.import_module(f"{entry.PKG_ALIAS}.synth")
+    cabi = importlib.import_module(f"{entry.PKG_ALIAS}.ops._cabi")
+    R, info = 3, {"case": name}
+    if name.startswith("gate_up_q4"):
+        B = int(name.rsplit("_b", 1)[1])
+        sets = [[t.to(device) for t in synth.quantized_weight(14336, 4096, 4, 64, seed=11 + i) +
+                 synth.quantized_weight(14336, 4096, 4, 64, seed=21 + i)] for i in range(R)]
+        x = synth.activations((B, 4096), 5, device)
+        call = lambda d: q.q4_gate_up_matvec_tiled(x, d[0], d[3], d[1], d[4], d[2], d[5], group_size=64)
+        info["algorithmic_bytes"] = sum(t.numel() * t.element_size() for t in sets[0]) + B * (4096 + 2 * 14336) * 2
+    elif name.startswith("mlp_block_q4"):
+        mlp = importlib.import_module(f"{entry.PKG_ALIAS}.ops.mlp_block_ops")
+        B = int(name.rsplit("_b", 1)[1])
+        sets = [[t.to(device) for t in synth.quantized_weight(14336, 4096, 4, 64, seed=11 + i) +
+                 synth.quantized_weight(14336, 4096, 4, 64, seed=21 + i) +
+                 synth.quantized_weight(4096, 14336, 4, 64, seed=31 + i)] for i in range(R)]
+        x = synth.activations((B, 1, 4096), 5, device)
+        res = torch.zeros_like(x)
+        nw = torch.ones(4096, dtype=torch.float16, device=device)
+        call = lambda d: mlp.quantized_mlp_block(x, res, nw, d[0], d[1], d[3], d[4], d[6], d[7], gate_zeros=d[2],
+                                                 up_zeros=d[5], down_zeros=d[8], bits=4, group_size=64,
+                                                 backend_preset="cuda")
+        info["algorithmic_bytes"] = sum(t.numel() * t.element_size() for t in sets[0]) + B * (4096 * 3 + 14336 * 2) * 2
+    elif name in ("down_q4_b8", "matvec_q8_b8", "qkv_q4_b1", "o_q4_b1", "down_q4_b1"):
+        bits, N, K = {"down": (4, 4096, 14336), "matvec": (8, 14336, 4096), "qkv": (4, 6144, 4096),
+                      "o": (4, 4096, 4096)}[name.split("_")[0]]
+        B = int(name.rsplit("_b", 1)[1])
+        R = max(R, -(-200_000_000 // (N * K // (2 if bits == 4 else 1))))      # the copies together pass L2
+        sets = [[t.to(device) for t in synth.quantized_weight(N, K, bits, 64, seed=31 + i)] for i in range(R)]
+        x = synth.activations((B, K), 6, device)
+        fn = q.q4_matvec_decode if bits == 4 else q.q8_matvec_decode
+        call = lambda d: fn(x, d[0], d[1], d[2], group_size=64, backend="cuda")
+        info["algorithmic_bytes"] = sum(t.numel() * t.element_size() for t in sets[0]) + B * (K + N) * 2
+    elif name in ("attn_cluster_q8_b1_ctx4096", "attn_splitkv_q8_b16"):
+        if name.startswith("attn_cluster"):
+            B, lo, hi = 1, 4097, 4097
+            R = 16                                                  # 9.5 MB per cache: 16 copies pass L2
+        else:
+            B, lo, hi = 16, 1024, 8192
+        cases = [synth.paged_kv_case(B, 8, 128, 16, num_pages=B * 520, min_len=lo, max_len=hi, bits=8, group_size=32,
+                                     seed=41 + i) for i in range(R)]
+        sets = [pq.PagedQuantizedKVCache(**{k: (v.to(device) if torch.is_tensor(v) else v) for k, v in c.items()})
+                for c in cases]
+        qq = synth.activations((B, 1, 32, 128), 7, device)
+        call = lambda c: pq.paged_quantized_kv_gqa_decode_attention(qq, c, backend="cuda")
+        info["algorithmic_bytes"] = int(cases[0]["lengths"].sum()) * 8 * (2 * 128 + 2 * 4 * 2) + 2 * B * 32 * 128 * 2
+    elif name == "attn_fp16_b16":
+        B, ctx, P = 16, 4096, 16
+        g = torch.Generator().manual_seed(3)
+        sets = []
+        for i in range(R):
+            K = torch.randn((B * ctx // P, P, 8, 128), generator=g).to(torch.float16).to(device)
+            V = torch.randn((B * ctx // P, P, 8, 128), generator=g).to(torch.float16).to(device)
+            sets.append((K, V))
+        bt = torch.arange(B * ctx // P, dtype=torch.int32, device=device).reshape(B, -1)
+        ln = torch.full((B,), ctx, dtype=torch.int32, device=device)
+        qq = synth.activations((B, 1, 32, 128), 7, device)
+        call = lambda d: gqa.paged_gqa_decode_attention(qq, d[0], d[1], bt, ln)
+        info["algorithmic_bytes"] = 2 * B * ctx * 8 * 128 * 2 + 2 * B * 32 * 128 * 2
+    else:
+        raise SystemExit(f"unknown --profile-case {name!r}; one of {PROFILE_CASES}")
+    for _ in range(2):
+        for d in sets:
+            call(d)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for d in sets:
+        call(d)
+    end.record()
+    torch.cuda.synchronize()
+    info["eager_us_per_call"] = round(start.elapsed_time(end) * 1e3 / len(sets), 2)
+    info["device_status"] = cabi.device_status()
+    print(json.dumps(info), flush=True)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -669,12 +764,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--no-batch32", action="store_true", help="skip the secondary measurement of the step at batch 32")
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="the timed region repeats the --steps block until it has lasted this long")
+    ap.add_argument("--step-only", action="store_true",
+                    help="only the decode step (no kernel table, no CPU baseline): the short run a launch list is taken from")
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--kernels-only", action="store_true",
                     help="run only the per-kernel micro-benchmarks of configs C1-C4 (the small cases used for profiler captures)")
+    ap.add_argument("--profile-case", default=None, choices=PROFILE_CASES,
+                    help="run one kernel shape a few times eagerly (the small case for an ncu capture) and exit")
     ap.add_argument("--cpu-baselines", action="store_true",
                     help="with --kernels-only: also time each config through the oracle on the host cores")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
     if args.kernels_only:
         run_kernels_only(cpu=args.cpu_baselines)
     elif args.impl == "reference":

@@ -56,6 +56,8 @@ int b200q_device_status(int reset, void* stream);
 /* Runtime tuning knob (benchmark sweeps and tests; defaults are chosen per shape when unset/0).  Keys:
  *   "gemv.ts"            1 = every matvec the tcgen05 kernel supports goes to it, -1 = none, 0 = by batch
  *   "gemv.ts_min_batch"  smallest batch the tcgen05 kernel takes when "gemv.ts" is 0
+ *   "gemv.fuse_norm"     1 = the tcgen05 kernel computes a requested rmsnorm in its own prologue even when the caller
+ *                        gave a buffer for the normalised rows (default: a launch of the row kernel in front of it)
  *   "gemv.force_generic" 1 = always the one-warp-per-row kernel that follows the reference arithmetic literally
  *   "gemv.stage_k", "gemv.stages", "gemv.interleave"   ring geometry / row dealing of the mma.sync kernel
  *   "ts.stages", "ts.smem_kb", "ts.split", "ts.big"     ring depth, shared-memory budget, K split, shape of the tcgen05 kernel

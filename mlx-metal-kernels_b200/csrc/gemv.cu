@@ -133,11 +133,11 @@ bool prefer_ts(const GemvParams& p) {
     return p.B >= min_b;
 }
 
-// Large batches: the rmsnorm prologue costs the tcgen05 kernel's activation warps more than a launch of the row kernel
-// (measured at batch 32, 4096 -> 2 x 14336: 56 us fused against 33 + 3 us), so when the caller provides the buffer
-// for the normalised rows they are materialised first.
+// The rmsnorm prologue costs the tcgen05 kernel's activation warps more than a launch of the row kernel (measured,
+// 4096 -> 2 x 14336: at batch 32 56 us fused against 33 + 3 us, at batch 8 40 us against 30 + 3 us), so when the caller
+// provides the buffer for the normalised rows they are materialised first.
 int split_norm_prologue(GemvParams& p, cudaStream_t stream) {
-    if (p.norm_w == nullptr || p.normed_out == nullptr || p.B < 16 || !prefer_ts(p)) return B200Q_OK;
+    if (p.norm_w == nullptr || p.normed_out == nullptr || !prefer_ts(p) || tuning_get("gemv.fuse_norm") > 0) return B200Q_OK;
     const int rc = rmsnorm_residual_launch(p.x, p.res_in, p.norm_w, p.normed_out, p.z_out, p.B, p.K, p.eps, p.act_dtype,
                                            p.norm_w_dtype, stream);
     if (rc != B200Q_OK) return rc;

@@ -242,18 +242,31 @@ __device__ __forceinline__ GroupConst group_const(uint32_t s_bits, uint32_t z_bi
     return c;
 }
 
-// The epilogue of one 16-column slice: clamp, round, residual add or SwiGLU, store.
+// The residual values of output row n for all batch columns, fetched before the accumulators are waited for and before
+// the first store: y may alias the residual rows as far as the compiler knows, so a load placed after a store would
+// wait for it - one global-memory latency per column.
 template <int MATS>
-__device__ __forceinline__ void ts_store_cols(const TsParams& p, const float (&acc)[MATS][16], int n, int c0) {
+__device__ __forceinline__ void ts_load_residual(const TsParams& p, int n, float (&res)[32]) {
+    if (MATS == 1 && p.residual != nullptr && n < p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) res[j] = j < p.B ? __half2float(p.residual[(size_t)j * p.N + n]) : 0.0f;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) res[j] = 0.0f;
+    }
+}
+// The epilogue of one 16-column slice: clamp, round, residual add or SwiGLU, store.
+template <int MATS, int C0>
+__device__ __forceinline__ void ts_store_cols(const TsParams& p, const float (&acc)[MATS][16], int n, const float (&res)[32]) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-        const int b = c0 + j;
+        const int b = C0 + j;
         if (b >= p.B) break;
         const size_t o = (size_t)b * p.N + n;
         const float v0 = __half2float(__float2half_rn(fminf(fmaxf(acc[0][j], -65504.0f), 65504.0f)));
         if (MATS == 1) {
             float v = v0;
-            if (p.residual != nullptr) v = __half2float(p.residual[o]) + v;
+            if (p.residual != nullptr) v = res[C0 + j] + v;
             p.y[o] = __float2half_rn(v);
         } else {
             const float v1 = __half2float(__float2half_rn(fminf(fmaxf(acc[MATS - 1][j], -65504.0f), 65504.0f)));
@@ -672,14 +685,22 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
             // ---- epilogue of the tile (split == 1; with a split K range it follows the cluster exchange below) ----
             if (warp < 4 && p.split == 1) {
                 if (!waited_pdl) { pdl_wait(); waited_pdl = true; }
+                const int n = n0 + r;
+                float res[32];
+                ts_load_residual<MATS>(p, n, res);
                 wait_bar(d_full, (uint32_t)ti & 1u, EV_GEMV_FULL_WAIT, ok);
                 tc_fence_after();
-                const int n = n0 + r;
-                for (int c0 = 0; c0 < ncols && c0 < B; c0 += 16) {
+                {
                     float acc[MATS][16];
 #pragma unroll
-                    for (int m = 0; m < MATS; ++m) tc_ld16(lane_addr + (uint32_t)(m * ncols + c0), acc[m]);
-                    if (n < p.N) ts_store_cols<MATS>(p, acc, n, c0);
+                    for (int m = 0; m < MATS; ++m) tc_ld16(lane_addr + (uint32_t)(m * ncols), acc[m]);
+                    if (n < p.N) ts_store_cols<MATS, 0>(p, acc, n, res);
+                }
+                if (ncols > 16 && B > 16) {
+                    float acc[MATS][16];
+#pragma unroll
+                    for (int m = 0; m < MATS; ++m) tc_ld16(lane_addr + (uint32_t)(m * ncols + 16), acc[m]);
+                    if (n < p.N) ts_store_cols<MATS, 16>(p, acc, n, res);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -720,11 +741,15 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
         }
         if (!fast) cluster_sync_all();      // the partial sums are in the first CTA's shared memory
         if (epi && rank == 0) {
-            if (fast) wait_bar_cluster(red_bar, 0u, ok ? kTsWaitLimit : 64u);
             pdl_wait();
             const int n = cluster_id * kRows + r;
+            float res[32];
+            ts_load_residual<MATS>(p, n, res);
+            if (fast) wait_bar_cluster(red_bar, 0u, ok ? kTsWaitLimit : 64u);
             const float* red = reinterpret_cast<const float*>(sbase + (red_base - base));
-            for (int c0 = 0; c0 < rcols; c0 += 16) {
+#pragma unroll
+            for (int c0 = 0; c0 < 32; c0 += 16) {
+                if (c0 >= rcols) break;
                 float acc[MATS][16];
 #pragma unroll
                 for (int m = 0; m < MATS; ++m) {
@@ -734,7 +759,10 @@ __global__ void __launch_bounds__(ts_threads(WHOLE), WHOLE ? 1 : 2) qgemm_ts_ker
                         for (int j = 0; j < 16; ++j)
                             if (c0 + j < rcols) acc[m][j] += red[((((q - 1) * MATS + m) * rcols + c0 + j) * kRows + r)];
                 }
-                if (n < p.N) ts_store_cols<MATS>(p, acc, n, c0);
+                if (n < p.N) {
+                    if (c0 == 0) ts_store_cols<MATS, 0>(p, acc, n, res);
+                    else ts_store_cols<MATS, 16>(p, acc, n, res);
+                }
             }
         }
     }
@@ -823,19 +851,23 @@ int launch_ts(TsParams& p, cudaStream_t stream) {
     int split = 1;
     if (tiles_full < sms) split = std::min(8, sms / tiles_full);
     split = std::max(1, std::min(split, p.n_stage_total / 2));
-    // without the dedicated buffer the partial sums travel through the first CTA's weight ring: two stages always exist
-    const int ring_cap = 1 + (int)(2u * p.stage_bytes / ((uint32_t)MATS * p.ncols * kRows * 4));
-    if ((uint32_t)(split - 1) * MATS * p.B * kRows * 4 > 8192u) split = std::max(1, std::min(split, ring_cap));
+    // the partial sums of the other CTAs of a cluster (real batch columns only) must fit 48 KB of the first CTA's
+    // shared memory; like the split itself the bound depends on the batch alone, not on the shape of this launch
+    constexpr uint32_t kRedCap = 48u * 1024u;
+    const uint32_t part_bytes = (uint32_t)MATS * p.B * kRows * 4;
+    if ((uint32_t)(split - 1) * part_bytes > kRedCap) split = std::max(1, std::min(split, 1 + (int)(kRedCap / part_bytes)));
     const int fs = tuning_get("ts.split");
     if (fs > 0) split = std::max(1, std::min({fs, 8, p.n_stage_total}));
-    // partial sums of a split K range: a dedicated buffer of at most 8 KB (real batch columns only), else the weight ring
-    uint32_t red_bytes = (uint32_t)(split - 1) * MATS * p.B * kRows * 4;
-    bool fast_red = split > 1 && red_bytes <= 8192u && !tuning_get("ts.slow_reduce");
+    // they arrive in a dedicated buffer signalled by a barrier (whole-SM shape: up to the 48 KB, compact shape: 8 KB),
+    // else in the first CTA's weight ring between two cluster-wide barriers; both add them in rank order
+    const uint32_t red_bytes = (uint32_t)(split - 1) * part_bytes;
+    const bool fast_red = split > 1 && red_bytes <= (WHOLE ? kRedCap : 8192u) && !tuning_get("ts.slow_reduce");
+    const uint32_t red_alloc = fast_red ? (red_bytes + 1023u) / 1024u * 1024u : 0u;
     // rings: operand tiles (at least as many as activation warps: a warp must never meet a tile slot two uses ahead of
     // the MMAs; one more lets it keep the copies of its next stage in flight), then as many weight stages as fit
     constexpr int XW = ts_xwarps(WHOLE);
     const uint32_t per_tile = p.xt_bytes + p.res_bytes;
-    const uint32_t base_fixed = 2048u + (fast_red ? 8192u : 0u);
+    const uint32_t base_fixed = 2048u + red_alloc;
     int xt = XW + 2;
     while (xt > XW && base_fixed + (uint32_t)xt * per_tile + 3 * p.stage_bytes > budget) --xt;
     p.x_tiles = std::min(xt, kMaxXTiles);
@@ -854,7 +886,7 @@ int launch_ts(TsParams& p, cudaStream_t stream) {
     p.off_res = p.off_xt + (uint32_t)p.x_tiles * p.xt_bytes;
     p.off_red = (fast_red && split > 1) ? p.off_res + (uint32_t)p.x_tiles * p.res_bytes : 0u;
     const int clusters = split > 1 ? p.tiles : std::min(p.tiles, sms);
-    const uint32_t smem = 1024u + p.off_res + (uint32_t)p.x_tiles * p.res_bytes + (p.off_red ? 8192u : 0u);
+    const uint32_t smem = 1024u + p.off_res + (uint32_t)p.x_tiles * p.res_bytes + red_alloc;
 
     auto kernel = qgemm_ts_kernel<BITS, LOGG, MATS, WHOLE>;
     static bool configured[64] = {};
@@ -896,7 +928,10 @@ int launch_ts(TsParams& p, cudaStream_t stream) {
 template <int BITS, int LOGG, int MATS>
 int launch_ts_shape(TsParams& p, int64_t weight_bytes, cudaStream_t stream) {
     const int mode = tuning_get("ts.big");
-    const bool big = mode > 0 || (mode == 0 && weight_bytes >= (int64_t)16 << 20);
+    // (the size of the UNSHARDED matrix decides, so that a tensor-parallel shard runs the shape, and with it the K
+    // split, of the unsharded launch)
+    const int64_t full_bytes = weight_bytes * std::max(1, tuning_get("ts.tp_world"));
+    const bool big = mode > 0 || (mode == 0 && full_bytes >= (int64_t)16 << 20);
     if (!big) {
         const int rc = launch_ts<BITS, LOGG, MATS, false>(p, stream);
         if (rc != B200Q_ERR_UNSUPPORTED) return rc;

@@ -191,8 +191,9 @@ class DecodeStack:
         self.attn = torch.zeros((batch, self.hq * D), **f16)
         self.act = torch.zeros((batch, cfg.intermediate // tp_size), **f16)
         self.out = torch.zeros((batch, cfg.hidden), **f16)
-        # buffer for the normalised rows: large batches run the rmsnorm as a launch of its own in front of the matvec
-        self.normed = torch.zeros((batch, cfg.hidden), **f16) if batch >= 16 else None
+        # buffer for the normalised rows: the batches that run the tcgen05 matvec (5 rows and more) run the rmsnorm as a
+        # launch of its own in front of it
+        self.normed = torch.zeros((batch, cfg.hidden), **f16) if batch >= 5 else None
         self.peer_gather = False
         self.peer_fused = False
         # The exchange fused into the kernels exists in the mma.sync matvec kernel, which takes batches of up to 4

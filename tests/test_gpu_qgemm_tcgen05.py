@@ -17,7 +17,7 @@ def tcgen05(cuda):
     """Routes every supported launch to the tcgen05 kernel; restores the default routing afterwards."""
     cabi.set_tuning("gemv.ts", 1)
     yield cuda
-    for key in ("gemv.ts", "ts.big", "ts.split", "ts.slow_reduce", "ts.stages"):
+    for key in ("gemv.ts", "ts.big", "ts.split", "ts.slow_reduce", "ts.stages", "gemv.fuse_norm"):
         cabi.set_tuning(key, 0)
     assert cabi.device_status() == 0
 
@@ -110,9 +110,12 @@ def test_gate_up_swiglu(tcgen05, bits, B, N, K, big):
 
 @pytest.mark.parametrize("B,with_res", [(1, False), (6, True), (32, True)])
 @pytest.mark.parametrize("big", [-1, 1])
-def test_fused_norm_prologue_and_residual_epilogue(tcgen05, B, with_res, big):
-    """quantized_mlp_block through the tcgen05 kernel: [add + rmsnorm + gate/up + SwiGLU] and [down + residual]."""
+@pytest.mark.parametrize("fuse_norm", [1, 0])
+def test_fused_norm_prologue_and_residual_epilogue(tcgen05, B, with_res, big, fuse_norm):
+    """quantized_mlp_block through the tcgen05 kernel: [add + rmsnorm + gate/up + SwiGLU] and [down + residual], the
+    norm in the kernel's prologue (fuse_norm) or as the row kernel's launch in front of it (the default)."""
     cabi.set_tuning("ts.big", big)
+    cabi.set_tuning("gemv.fuse_norm", fuse_norm)
     hidden, inter = 1024, 2048
     gw, gs, gz = synth.quantized_weight(inter, hidden, 4, 64, seed=51)
     uw, us, uz = synth.quantized_weight(inter, hidden, 4, 64, seed=52)
