@@ -306,6 +306,15 @@ int b200q_tp_register(int slot, void* const* peer_full, uint32_t* const* peer_fl
                       int rank, int world);
 int b200q_tp_next(int in_slot, int out_slot);
 
+/* Packet form of a registered exchange slot (packets != 0): the slot's full buffers then hold one 32-bit word per
+ * 16-bit element - the element in the low half, the low bits of the exchange's sequence number in the high half -
+ * so they are TWICE the size of the plain rows, must start zeroed, and are read only by kernels called with this
+ * slot as in_slot (the pointer passed as `x` is the packet buffer).  A writer kernel stores each element and its
+ * "arrived" mark in one 4-byte peer store; a reader polls the packets it loads (bounded, event 5).  No system-scope
+ * fence, flag word or counter crosses NVLink: an exchange costs one one-way store latency.  The flag pointers given
+ * to b200q_tp_register are unused in this form.  Results are the same bits as in the plain form. */
+int b200q_tp_set_packets(int slot, int packets);
+
 /* Diagnostics (no counterpart in the reference): one CTA waits on a shared-memory barrier that nothing arrives on, with
  * the bounded wait the matvec and attention kernels use, for `limit` probes (1..65536).  The wait runs out, the kernel
  * returns, b200q_device_status() then reports event 1 and *probes_out (device uint32, may be NULL) holds `limit`.

@@ -325,6 +325,13 @@ int b200q_tp_register(int slot, void* const* peer_full, uint32_t* const* peer_fl
     return B200Q_OK;
 }
 
+int b200q_tp_set_packets(int slot, int packets) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (slot < 0 || slot >= 16 || !g_tp_valid[slot]) return B200Q_ERR_BAD_ARG;
+    g_tp_slots[slot].out.packets = packets ? 1 : 0;
+    return B200Q_OK;
+}
+
 int b200q_tp_next(int in_slot, int out_slot) {
     if ((in_slot >= 0 && tp_slot(in_slot) == nullptr) || (out_slot >= 0 && tp_slot(out_slot) == nullptr))
         return B200Q_ERR_BAD_ARG;

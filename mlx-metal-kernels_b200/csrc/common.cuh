@@ -56,12 +56,15 @@ struct TpOut {
     uint32_t* epoch;                // this rank's publication counter for the buffer (device memory)
     uint32_t* counter;              // CTAs of the writer kernel that have finished (device memory, zero between uses)
     int rank, world;                // world == 0: no exchange
+    int packets;                    // 1: the full buffers hold 4-byte packets (16 data bits + 16 sequence bits) instead of
+                                    // plain 16-bit rows, and no flag words are used (see tp_packet below)
 };
 struct TpIn {
     const uint32_t* flags;          // this rank's flag words [world]
     const uint32_t* epoch;          // this rank's publication counter (already advanced by the local writer)
     int world;                      // world == 0: nothing to wait for
     uint32_t spin_limit;            // acquire loads before the wait gives up (0: kTpSpinLimit); tuning key "tp.spin_limit"
+    int packets;                    // 1: the activations are a packet buffer; every load checks its own packets
 };
 struct TpSlot { TpOut out; };       // host table entry
 const TpSlot* tp_slot(int slot);    // nullptr if the slot was never registered
@@ -171,6 +174,62 @@ __device__ __forceinline__ bool tp_wait_source(const TpIn& in, int src) {
     for (uint32_t it = 0; it < limit; ++it)
         if ((int32_t)(ld_acquire_sys(in.flags + src) - seq) >= 0) return true;
     return false;
+}
+
+// ---- packet form of the exchange: payload and "it has arrived" in ONE 4-byte store ----------------------------
+// A full buffer in packet form holds one 32-bit word per 16-bit element: the element in the low half, the low bits of
+// the exchange's sequence number (never 0; the buffers start zeroed) in the high half.  A 4-byte store is single-copy
+// atomic, so a reader that finds the expected sequence number has the element - no fence, no flag word, no counter
+// round trip across NVLink: an exchange costs one one-way store latency instead of a fence round trip plus a flag.
+// Every exchange rewrites all packets of its buffer, so a stale packet carries the previous sequence number.
+__device__ __forceinline__ uint32_t tp_seq16(uint32_t seq) { return seq % 65535u + 1u; }
+__device__ __forceinline__ uint32_t tp_packet(unsigned short bits16, uint32_t seq16) { return (uint32_t)bits16 | (seq16 << 16); }
+__device__ __forceinline__ void st_volatile_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_u128(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Sequence number the writer kernel stamps its packets with; read after griddepcontrol.wait (everything earlier in the
+// stream, the previous use of the buffer included, is complete then).
+__device__ __forceinline__ uint32_t tp_writer_seq(const TpOut& out) {
+    return *reinterpret_cast<const volatile uint32_t*>(out.epoch) + 1u;
+}
+// Called by one whole warp of every CTA of the writer kernel after its packet stores: the last CTA advances this
+// rank's sequence counter (local memory only: the packets need no publication).
+__device__ __forceinline__ void tp_finish_writer_packets(const TpOut& out, int lane, unsigned total_ctas = 0) {
+    if (total_ctas == 0) total_ctas = gridDim.x * gridDim.y;
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence();
+        if (atomicAdd(out.counter, 1u) == total_ctas - 1u) {
+            const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(out.epoch) + 1u;
+            *out.epoch = seq;
+            *out.counter = 0u;
+        }
+    }
+}
+// 8 consecutive elements (32 bytes of packets, 32-byte aligned) of a packet buffer; polls until all eight carry
+// `seq16`, at most `limit` times.  Returns false when the wait ran out (the data are then whatever was there).
+__device__ __forceinline__ bool tp_load8_packets(const void* base, int64_t idx, uint32_t seq16, uint32_t limit, uint32_t (&w)[4]) {
+    const char* src = reinterpret_cast<const char*>(base) + idx * 4;
+    const uint32_t want = seq16 << 16;
+    uint4 a, b;
+    bool ok = false;
+    for (uint32_t it = 0; it < limit; ++it) {
+        a = ld_volatile_u128(src);
+        b = ld_volatile_u128(src + 16);
+        const uint32_t diff = ((a.x ^ want) | (a.y ^ want) | (a.z ^ want) | (a.w ^ want) |
+                               (b.x ^ want) | (b.y ^ want) | (b.z ^ want) | (b.w ^ want)) & 0xFFFF0000u;
+        if (diff == 0u) { ok = true; break; }
+    }
+    w[0] = (a.x & 0xFFFFu) | (a.y << 16);
+    w[1] = (a.z & 0xFFFFu) | (a.w << 16);
+    w[2] = (b.x & 0xFFFFu) | (b.y << 16);
+    w[3] = (b.z & 0xFFFFu) | (b.w << 16);
+    return ok;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {

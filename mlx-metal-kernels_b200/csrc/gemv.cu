@@ -203,6 +203,7 @@ int qmatvec_impl(int bits, const void* x, const uint8_t* codes, const void* scal
             p.tp_in.epoch = src.epoch;
             p.tp_in.world = src.world;
             p.tp_in.spin_limit = (uint32_t)std::max(0, tuning_get("tp.spin_limit"));
+            p.tp_in.packets = src.packets;
         }
         const bool tp_used = tp_in_slot >= 0 || tp_out_slot >= 0;
         if (!tp_used && fast_path_ok(p)) {
@@ -282,6 +283,7 @@ int gate_up_impl(int bits, const void* x, const uint8_t* gate_codes, const uint8
             p.tp_in.epoch = src.epoch;
             p.tp_in.world = src.world;
             p.tp_in.spin_limit = (uint32_t)std::max(0, tuning_get("tp.spin_limit"));
+            p.tp_in.packets = src.packets;
         }
         const bool tp_used = tp_in_slot >= 0 || tp_out_slot >= 0;
         if (!tp_used && fast_path_ok(p)) {

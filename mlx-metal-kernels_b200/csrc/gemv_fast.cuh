@@ -55,6 +55,34 @@ __device__ __forceinline__ void load8_raw(const void* base, int dtype, int64_t i
         }
     }
 }
+__device__ __forceinline__ void words_to_f32(const uint32_t (&w)[4], int dtype, float (&v)[8]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (dtype == B200Q_F16) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+            v[2 * i] = __low2float(h);
+            v[2 * i + 1] = __high2float(h);
+        } else {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+}
+// The kernel's input rows: plain, or (tensor-parallel exchange in packet form) packets that are polled until they carry
+// the sequence number `xs.seq16`.  After a wait ran out the following loads give up quickly.
+struct XSource { uint32_t seq16, limit; };
+__device__ __forceinline__ void load8_x(const void* base, int dtype, int64_t idx, XSource& xs, float (&v)[8]) {
+    if (xs.seq16 == 0u) {
+        load8_raw(base, dtype, idx, v);
+        return;
+    }
+    uint32_t w[4];
+    if (!tp_load8_packets(base, idx, xs.seq16, xs.limit, w)) {
+        atomicMax(&g_device_status, (int)EV_PEER_WAIT);
+        xs.limit = 64u;
+    }
+    words_to_f32(w, dtype, v);
+}
 __device__ __forceinline__ float round_act(float v, int dtype) {
     return dtype == B200Q_F16 ? __half2float(__float2half_rn(v)) : __bfloat162float(__float2bfloat16_rn(v));
 }
@@ -73,8 +101,8 @@ __device__ __forceinline__ void store8_act(void* base, int dtype, int64_t idx, c
     *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + idx) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 // z = cast(x + res) (res optional)
-__device__ __forceinline__ void load8_z(const GemvParams& p, int b, int k, float (&zv)[8]) {
-    load8_raw(p.x, p.act_dtype, (int64_t)b * p.K + k, zv);
+__device__ __forceinline__ void load8_z(const GemvParams& p, int b, int k, XSource& xs, float (&zv)[8]) {
+    load8_x(p.x, p.act_dtype, (int64_t)b * p.K + k, xs, zv);
     if (p.res_in != nullptr) {
         float r[8];
         load8_raw(p.res_in, p.act_dtype, (int64_t)b * p.K + k, r);
@@ -83,13 +111,14 @@ __device__ __forceinline__ void load8_z(const GemvParams& p, int b, int k, float
     }
 }
 // the activation row the matvec sees: x itself, or cast(z * inv_rms * w)
-__device__ __forceinline__ void load8_act(const GemvParams& p, int b, int k, float inv_rms, bool write_side, float (&v)[8]) {
+__device__ __forceinline__ void load8_act(const GemvParams& p, int b, int k, float inv_rms, bool write_side, XSource& xs,
+                                          float (&v)[8]) {
     if (p.norm_w == nullptr) {
-        load8_raw(p.x, p.act_dtype, (int64_t)b * p.K + k, v);
+        load8_x(p.x, p.act_dtype, (int64_t)b * p.K + k, xs, v);
         return;
     }
     float zv[8];
-    load8_z(p, b, k, zv);
+    load8_z(p, b, k, xs, zv);
     if (write_side && p.z_out != nullptr) store8_act(p.z_out, p.act_dtype, (int64_t)b * p.K + k, zv);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -277,6 +306,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
     if (warp == kEpilogueWarp) {
         // ------------------------------ epilogue warp ------------------------------------------
         pdl_wait();   // the output buffers may still be read by the previous kernel
+        const uint32_t out_seq16 = (p.tp_out.world > 0 && p.tp_out.packets) ? tp_seq16(tp_writer_seq(p.tp_out)) : 0u;
         bool ok = true;
         for (int tl = 0; tl < n_tiles; ++tl) {
             const int ps = tl % nslot;
@@ -315,6 +345,13 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                         const int64_t of = (int64_t)b * p.N * p.tp_out.world + (int64_t)p.tp_out.rank * p.N + row0 + r;
                         const unsigned short bits16 = p.act_dtype == B200Q_F16 ? __half_as_ushort(__float2half_rn(v))
                                                                                : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+                        if (p.tp_out.packets) {
+                            const uint32_t pk = tp_packet(bits16, out_seq16);
+#pragma unroll 1
+                            for (int peer = 0; peer < p.tp_out.world; ++peer)
+                                st_volatile_u32(reinterpret_cast<uint32_t*>(p.tp_out.full[peer]) + of, pk);
+                            return;
+                        }
 #pragma unroll 1
                         for (int peer = 0; peer < p.tp_out.world; ++peer)
                             reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
@@ -339,7 +376,10 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
             __syncwarp();
             if (lane == 0) mbar_arrive(&slot_free[ps]);
         }
-        if (p.tp_out.world > 0) tp_finish_writer(p.tp_out, lane);
+        if (p.tp_out.world > 0) {
+            if (p.tp_out.packets) tp_finish_writer_packets(p.tp_out, lane);
+            else tp_finish_writer(p.tp_out, lane);
+        }
         return;
     }
 
@@ -378,7 +418,11 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
 
 
     pdl_wait();   // activations belong to the previous kernel until here
-    if (p.tp_in.world > 0) {
+    XSource xsrc = {0u, p.tp_in.spin_limit ? p.tp_in.spin_limit : kTpSpinLimit};
+    if (p.tp_in.world > 0 && p.tp_in.packets) {
+        // packet form: nothing to wait for here, every load of the rows checks its own packets
+        xsrc.seq16 = tp_seq16(*reinterpret_cast<const volatile uint32_t*>(p.tp_in.epoch));
+    } else if (p.tp_in.world > 0) {
         // the activations are an exchange buffer filled by all ranks: wait for every source rank's flag
         if (ctid < p.tp_in.world && !tp_wait_source(p.tp_in, ctid)) atomicMax(&g_device_status, (int)EV_PEER_WAIT);
         named_bar_sync(1, kConsumerThreads);
@@ -395,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float ss = 0.0f;
                     for (int k = ctid * 8; k < p.K; k += kConsumerThreads * 8) {
                         float zv[8];
-                        load8_z(p, b, k, zv);
+                        load8_z(p, b, k, xsrc, zv);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
                     }
@@ -412,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float mx = 0.0f;
                     for (int k = ctid * 8; k < p.K; k += kConsumerThreads * 8) {
                         float v[8];
-                        load8_act(p, b, k, inv, false, v);
+                        load8_act(p, b, k, inv, false, xsrc, v);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
                     }
@@ -439,7 +483,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float ss = 0.0f;
                     for (int k = lane * 8; k < p.K; k += 256) {
                         float zv[8];
-                        load8_z(p, b, k, zv);
+                        load8_z(p, b, k, xsrc, zv);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
                     }
@@ -451,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float mx = 0.0f;
                     for (int k = lane * 8; k < p.K; k += 256) {
                         float v[8];
-                        load8_act(p, b, k, inv, false, v);
+                        load8_act(p, b, k, inv, false, xsrc, v);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
                     }
@@ -493,7 +537,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                 float v[8];
                 const float inv = need_row_pass ? xscale[B + b] : 1.0f;
                 const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
-                load8_act(p, b, xk0 + kk, inv, write_side, v);
+                load8_act(p, b, xk0 + kk, inv, write_side, xsrc, v);
                 __half h[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j] * down);

@@ -801,15 +801,25 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attn_cluster_kernel(con
             if (p.out != nullptr) reinterpret_cast<unsigned short*>(p.out)[((size_t)b * p.Hq + hq) * D + d] = bits16;
             if (p.tp_out.world > 0) {
                 const size_t of = ((size_t)b * p.tp_out.world + p.tp_out.rank) * p.Hq * D + (size_t)hq * D + d;
+                if (p.tp_out.packets) {
+                    const uint32_t pk = tp_packet(bits16, tp_seq16(tp_writer_seq(p.tp_out)));
 #pragma unroll 1
-                for (int peer = 0; peer < p.tp_out.world; ++peer)
-                    reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
+                    for (int peer = 0; peer < p.tp_out.world; ++peer)
+                        st_volatile_u32(reinterpret_cast<uint32_t*>(p.tp_out.full[peer]) + of, pk);
+                } else {
+#pragma unroll 1
+                    for (int peer = 0; peer < p.tp_out.world; ++peer)
+                        reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
+                }
             }
         }
     }
     if (p.tp_out.world > 0) {
         __syncthreads();                         // all of this CTA's peer stores are issued
-        if (warp == 0) tp_finish_writer(p.tp_out, lane, gridDim.x * gridDim.y * gridDim.z);
+        if (warp == 0) {
+            if (p.tp_out.packets) tp_finish_writer_packets(p.tp_out, lane, gridDim.x * gridDim.y * gridDim.z);
+            else tp_finish_writer(p.tp_out, lane, gridDim.x * gridDim.y * gridDim.z);
+        }
     }
 }
 
@@ -913,14 +923,24 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_attn_merge_kernel(cons
         if (p.tp_out.world > 0) {
             // tensor-parallel exchange: this head's row goes to column block `rank` of every rank's full rows
             const size_t of = ((size_t)b * p.tp_out.world + p.tp_out.rank) * p.Hq * D + (size_t)hq * D + threadIdx.x;
+            if (p.tp_out.packets) {
+                const uint32_t pk = tp_packet(bits16, tp_seq16(tp_writer_seq(p.tp_out)));
 #pragma unroll 1
-            for (int peer = 0; peer < p.tp_out.world; ++peer)
-                reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
+                for (int peer = 0; peer < p.tp_out.world; ++peer)
+                    st_volatile_u32(reinterpret_cast<uint32_t*>(p.tp_out.full[peer]) + of, pk);
+            } else {
+#pragma unroll 1
+                for (int peer = 0; peer < p.tp_out.world; ++peer)
+                    reinterpret_cast<unsigned short*>(p.tp_out.full[peer])[of] = bits16;
+            }
         }
     }
     if (p.tp_out.world > 0) {
         __syncthreads();                         // all of this CTA's peer stores are issued
-        if (warp == 0) tp_finish_writer(p.tp_out, lane);
+        if (warp == 0) {
+            if (p.tp_out.packets) tp_finish_writer_packets(p.tp_out, lane);
+            else tp_finish_writer(p.tp_out, lane);
+        }
     }
 }
 

@@ -42,6 +42,7 @@ SIGNATURES = {
     "b200q_peer_allgather": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp]),
     "b200q_tp_register": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i]),
     "b200q_tp_next": (_i, [_i, _i]),
+    "b200q_tp_set_packets": (_i, [_i, _i]),
     "b200q_wait_expiry_selftest": (_i, [_c.c_uint, _vp, _vp]),
     "b200q_swiglu": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _vp]),
     "b200q_residual_add": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),

@@ -164,7 +164,7 @@ class DecodeStack:
 
     def __init__(self, cfg: StackConfig, layers, final_norm, embedding, batch: int, max_context: int, device,
                  tp_rank: int = 0, tp_size: int = 1, process_group=None, use_peer_gather: bool = True,
-                 fuse_exchange: bool = True):
+                 fuse_exchange: bool = True, exchange_packets: bool = True):
         self.cfg, self.B, self.device = cfg, batch, device
         self.tp_rank, self.tp_size, self.pg = tp_rank, tp_size, process_group
         self.lib = _cabi.load()
@@ -199,6 +199,8 @@ class DecodeStack:
         # The exchange fused into the kernels exists in the mma.sync matvec kernel, which takes batches of up to 4
         # rows; larger batches run the tcgen05 kernel and exchange through the stand-alone peer kernel (or NCCL).
         self.fuse_exchange = fuse_exchange and batch <= 4
+        # fused exchange in packet form: element and arrival mark in one 4-byte peer store (no fence, no flag round trip)
+        self.exchange_packets = exchange_packets
         self.transport = "none"
         self.peer_gather_error = ""
         if tp_size > 1:
@@ -251,6 +253,11 @@ class DecodeStack:
                 off += (n + 255) // 256 * 256
             flag_off = off
             off += 3 * 256                                    # one 256-byte line of flag words per buffer
+            packet_offsets = []
+            if self.fuse_exchange and self.exchange_packets:  # the same rows as 4-byte packets (fused exchange only)
+                for n in sizes:
+                    packet_offsets.append(off)
+                    off += (2 * n + 255) // 256 * 256
             buf = symm.empty(off, dtype=torch.uint8, device=self.device)
             buf.zero_()
             handle = symm.rendezvous(buf, group)
@@ -278,19 +285,31 @@ class DecodeStack:
         if self.fuse_exchange and base + 3 <= 16:
             DecodeStack._next_slot += 3
             self.slots = (base, base + 1, base + 2)
+            self.fused_full = list(self.peer_full)            # what the consumer kernels are given as their input rows
+            self.fused_epochs = self.peer_epochs
+            fused_ptrs = self.peer_ptrs
+            if packet_offsets:
+                self.fused_full = [buf[o:o + B * w * 4].view(torch.int32).view(B, w) for w, o in zip(widths, packet_offsets)]
+                fused_ptrs = [(ctypes.c_void_p * W)(*[p + o for p in ptrs]) for o in packet_offsets]
+                self.fused_epochs = torch.zeros(3, dtype=torch.int32, device=self.device)
+                self._fused_ptrs = fused_ptrs
             for i, slot in enumerate(self.slots):
-                _cabi.check(self.lib.b200q_tp_register(slot, self.peer_ptrs[i], self.peer_flag_ptrs[i],
-                                                       self.peer_epochs[i:].data_ptr(), self.peer_counters[i:].data_ptr(),
+                _cabi.check(self.lib.b200q_tp_register(slot, fused_ptrs[i], self.peer_flag_ptrs[i],
+                                                       self.fused_epochs[i:].data_ptr(), self.peer_counters[i:].data_ptr(),
                                                        self.tp_rank, W), "tp_register")
+                _cabi.check(self.lib.b200q_tp_set_packets(slot, 1 if packet_offsets else 0), "tp_set_packets")
             self.peer_fused = True
-            self.transport = "fused_peer"
+            self.transport = "fused_packets" if packet_offsets else "fused_peer"
 
     def verify_exchanges(self):
         """Compares this rank's exchange sequence numbers with its peers' (call between steps; synchronises)."""
         if not self.peer_gather:
             return None
         torch.cuda.synchronize(self.device)
-        return verify_exchange_counts(self.peer_epochs.cpu().tolist(), self.pg)
+        counts = self.peer_epochs.cpu().tolist()
+        if self.peer_fused and self.fused_epochs is not self.peer_epochs:
+            counts += self.fused_epochs.cpu().tolist()
+        return verify_exchange_counts(counts, self.pg)
 
     def close(self):
         """Returns this stack's exchange slots to the process-wide pool (the last stack created is released first)."""
@@ -402,17 +421,17 @@ class DecodeStack:
                 sa, sh, sm = self.slots
                 last = w is self.layers[-1]
                 ck(lib.b200q_tp_next(sa, sh), "tp_next")
-                ck(lib.b200q_qmatvec(bits, self.peer_full[0].data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
+                ck(lib.b200q_qmatvec(bits, self.fused_full[0].data_ptr(), ow.data_ptr(), os_.data_ptr(), oz.data_ptr(), None,
                                      None, B, ow.shape[0], cfg.n_heads * D, G, F16, F16, st), "o_proj")
                 ck(lib.b200q_tp_next(sh, sm), "tp_next")
-                ck(lib.b200q_gate_up_swiglu(bits, self.peer_full[1].data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
+                ck(lib.b200q_gate_up_swiglu(bits, self.fused_full[1].data_ptr(), gw.data_ptr(), uw.data_ptr(), gs.data_ptr(),
                                             us.data_ptr(), gz.data_ptr(), uz.data_ptr(), None, None, None,
                                             self.h.data_ptr(), w["post_norm"].data_ptr(), F16, cfg.eps, self.h2.data_ptr(),
                                             None, B, gw.shape[0], cfg.hidden, G, F16, F16, st), "gate_up")
                 if last:
                     # the final norm is not a kernel that can wait: close the step with the stand-alone exchange
                     ck(lib.b200q_tp_next(sm, -1), "tp_next")
-                    ck(lib.b200q_qmatvec(bits, self.peer_full[2].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
+                    ck(lib.b200q_qmatvec(bits, self.fused_full[2].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
                                          None, self.o_loc.data_ptr(), B, dw.shape[0], cfg.intermediate, G, F16, F16, st),
                        "down_proj")
                     pending = self._gather(1, self.o_loc)
@@ -420,9 +439,9 @@ class DecodeStack:
                     n += 5 + attn_launches
                 else:
                     ck(lib.b200q_tp_next(sm, sh), "tp_next")
-                    ck(lib.b200q_qmatvec(bits, self.peer_full[2].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
+                    ck(lib.b200q_qmatvec(bits, self.fused_full[2].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(),
                                          None, None, B, dw.shape[0], cfg.intermediate, G, F16, F16, st), "down_proj")
-                    pending = self.peer_full[1]
+                    pending = self.fused_full[1]
                     pending_slot = sh
                     n += 4 + attn_launches + 2 * norm_launch
         if pending is None:

@@ -64,6 +64,13 @@ def _rank_main(rank, world, port, result_path, batch):
         nccl = make(rank, world, False)
         peer = make(rank, world, True)
         fused = make(rank, world, True, fused=True)
+        plain = stack_mod.DecodeStack(cfg, layers, fnorm, emb, B, 96, device, tp_rank=rank, tp_size=world, process_group=None,
+                                      use_peer_gather=True, fuse_exchange=True, exchange_packets=False)
+        for src, dst in zip(fused.caches, plain.caches):
+            for name in ("k_codes", "v_codes", "k_scales", "v_scales"):
+                getattr(dst, name).copy_(getattr(src, name))
+        plain.positions.fill_(40)
+        plain.lengths.fill_(41)
         ok["peer_enabled"] = bool(peer.peer_gather)
         ok["fused_enabled"] = bool(fused.peer_fused)
         ok["fused_expected"] = bool(fused.fuse_exchange)       # the stack fuses the exchange at small batches only
@@ -80,13 +87,15 @@ def _rank_main(rank, world, port, result_path, batch):
         toks = torch.randint(0, cfg.vocab, (4, B), device=device)
         dist.broadcast(toks, 0)
         outs = {}
-        for name, st in (("single", single), ("nccl", nccl), ("peer", peer), ("fused", fused)):
+        for name, st in (("single", single), ("nccl", nccl), ("peer", peer), ("fused", fused), ("plain", plain)):
             st.capture()
             outs[name] = [st.step(toks[i]).clone() for i in range(4)]
         torch.cuda.synchronize()
         ok["nccl_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["nccl"], outs["single"]))
         ok["peer_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["peer"], outs["single"]))
         ok["fused_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["fused"], outs["single"]))
+        ok["plain_fused_equals_single"] = all(torch.equal(a, b) for a, b in zip(outs["plain"], outs["single"]))
+        ok["exchange_counts"] = [fused.verify_exchanges(), plain.verify_exchanges()]
         ok["status"] = int(cabi.device_status())
         gathered = [None] * world
         dist.all_gather_object(gathered, ok)
@@ -159,4 +168,5 @@ def test_peer_gather_and_sharded_stack(tmp_path, world, batch):
         assert all(v for k, v in ok.items() if k.startswith("gather_")), ok
         assert ok["fused_enabled"] == ok["fused_expected"], ok
         assert ok["fused_equals_single"], ok          # at large batches this stack runs the stand-alone exchange
-        assert ok["transports"] == ("nccl", "peer_kernel", "fused_peer" if ok["fused_expected"] else "peer_kernel"), ok
+        assert ok["transports"] == ("nccl", "peer_kernel", "fused_packets" if ok["fused_expected"] else "peer_kernel"), ok
+        assert ok["plain_fused_equals_single"], ok      # the fused exchange with flag words instead of packets
