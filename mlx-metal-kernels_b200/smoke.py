@@ -38,6 +38,14 @@ def run() -> None:
     y = quant_ops.q4_matvec_decode(d(x), d(w), d(s), d(z), group_size=64, backend="cuda")
     err = _rel(y, oq.reference_q4_matvec_decode(x, w, s, z, group_size=64))
     assert err <= 1e-3, f"q4 matvec rel-L2 {err}"
+    # q4 / q8 matvec at batch 8: the tcgen05 kernel (TMA-tiled codes, weights dequantised into tensor memory)
+    for bits in (4, 8):
+        w8, s8, z8 = synth.quantized_weight(384, 1024, bits, 64, seed=11 + bits)
+        x8 = synth.activations((8, 1024), 12)
+        fn = quant_ops.q4_matvec_decode if bits == 4 else quant_ops.q8_matvec_decode
+        ref = oq.reference_q4_matvec_decode if bits == 4 else oq.reference_q8_matvec_decode
+        err = _rel(fn(d(x8), d(w8), d(s8), d(z8), group_size=64, backend="cuda"), ref(x8, w8, s8, z8, group_size=64))
+        assert err <= 1e-3, f"q{bits} batch-8 matvec rel-L2 {err}"
     # bit-exact dequant
     deq = quant_ops.dequant_q4(d(w), d(s), d(z), group_size=64)
     assert torch.equal(deq.cpu(), oq.reference_dequant_q4(w, s, z, group_size=64)), "dequant not bit-exact"
@@ -56,15 +64,17 @@ def run() -> None:
     err = _rel(out, want)
     assert err <= 1e-3, f"mlp block rel-L2 {err}"
 
-    # paged q4 GQA decode attention, ragged lengths
-    case = synth.paged_kv_case(3, 8, 128, 16, num_pages=64, min_len=5, max_len=300, bits=4, group_size=32, seed=7)
-    q = synth.activations((3, 1, 32, 128), 8)
-    cache = pq.PagedQuantizedKVCache(**{k: (d(v) if torch.is_tensor(v) else v) for k, v in case.items()})
-    o = pq.paged_quantized_kv_gqa_decode_attention(d(q), cache, backend="cuda")
-    ocache = opq.OraclePagedKV(**case)
-    want = opq.reference_paged_quantized_kv_gqa_decode_attention(q, ocache)
-    err = float((o.cpu().float() - want.float()).abs().max())
-    assert err <= 2e-3, f"paged attention max abs err {err}"
+    # paged q4 / q8 GQA decode attention, ragged lengths: batch 3 runs the one-launch cluster kernel, batch 6 the
+    # split-KV kernel with its merge
+    for bits, B in ((4, 3), (8, 6)):
+        case = synth.paged_kv_case(B, 8, 128, 16, num_pages=40 * B, min_len=5, max_len=300, bits=bits, group_size=32, seed=7)
+        q = synth.activations((B, 1, 32, 128), 8)
+        cache = pq.PagedQuantizedKVCache(**{k: (d(v) if torch.is_tensor(v) else v) for k, v in case.items()})
+        o = pq.paged_quantized_kv_gqa_decode_attention(d(q), cache, backend="cuda")
+        ocache = opq.OraclePagedKV(**case)
+        want = opq.reference_paged_quantized_kv_gqa_decode_attention(q, ocache)
+        err = float((o.cpu().float() - want.float()).abs().max())
+        assert err <= 2e-3, f"q{bits} paged attention max abs err {err}"
     torch.cuda.synchronize()
     status = _cabi.device_status()
     assert status == 0, f"device status word {status}"

@@ -103,3 +103,46 @@ def test_fused_exchange_wait_gives_up_and_recovers(cuda, short_waits):
     call()
     assert cabi.device_status() == 0
     assert rel_l2(y, want) <= 1e-3
+
+
+def test_packet_exchange_wait_gives_up_and_recovers(cuda, short_waits):
+    """The packet form of the fused exchange: the matvec's loads of its input rows poll the packets they need.  With
+    the second rank's half of the row still carrying the previous sequence number the wait runs out (event 5, the
+    kernel still finishes); once those packets are stamped the same call equals the oracle."""
+    lib = cabi.load()
+    B, K, N = 1, 512, 256
+    w, s, z = synth.quantized_weight(N, K, 4, 64, seed=5)
+    x = synth.activations((B, K), 6)
+    want = oq.reference_q4_matvec_decode(x, w, s, z, group_size=64)
+    dw, ds, dz = w.to(cuda), s.to(cuda), z.to(cuda)
+    seq = 7                                                       # this rank's counter: exchange number 7 was issued
+    stamp = (seq % 65535 + 1) << 16
+    bits = x.view(torch.int16).to(torch.int32) & 0xFFFF          # the elements as the low halves of the packets
+    packets = (bits | stamp).to(cuda)
+    stale = packets.clone()
+    stale[:, K // 2:] = bits[:, K // 2:].to(cuda) | (((seq - 1) % 65535 + 1) << 16)    # rank 1's half: previous exchange
+    buffers = [stale.clone().contiguous(), torch.zeros_like(stale)]
+    flags = [torch.zeros(2, dtype=torch.int32, device=cuda) for _ in range(2)]
+    epoch = torch.full((1,), seq, dtype=torch.int32, device=cuda)
+    counter = torch.zeros(1, dtype=torch.int32, device=cuda)
+    full_ptrs = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in buffers])
+    flag_ptrs = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in flags])
+    slot = 14
+    cabi.check(lib.b200q_tp_register(slot, full_ptrs, flag_ptrs, epoch.data_ptr(), counter.data_ptr(), 0, 2), "tp_register")
+    cabi.check(lib.b200q_tp_set_packets(slot, 1), "tp_set_packets")
+    assert lib.b200q_tp_set_packets(13, 1) != 0                   # a slot that was never registered
+    y = torch.zeros((B, N), dtype=torch.float16, device=cuda)
+
+    def call():
+        cabi.check(lib.b200q_tp_next(slot, -1), "tp_next")
+        cabi.check(lib.b200q_qmatvec(4, buffers[0].data_ptr(), dw.data_ptr(), ds.data_ptr(), dz.data_ptr(), None,
+                                     y.data_ptr(), B, N, K, 64, cabi.F16, cabi.dtype_code(ds.dtype), cabi.stream()), "qmatvec")
+
+    assert cabi.device_status() == 0
+    call()
+    assert cabi.device_status() == EV_PEER_WAIT
+    buffers[0].copy_(packets)                                     # the peer's packets "arrive"
+    call()
+    assert cabi.device_status() == 0
+    assert rel_l2(y, want) <= 1e-3
+    cabi.check(lib.b200q_tp_set_packets(slot, 0), "tp_set_packets")
