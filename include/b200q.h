@@ -59,13 +59,16 @@ int b200q_device_status(int reset, void* stream);
  *   "gemv.fuse_norm"     1 = the tcgen05 kernel computes a requested rmsnorm in its own prologue even when the caller
  *                        gave a buffer for the normalised rows (default: a launch of the row kernel in front of it)
  *   "gemv.force_generic" 1 = always the one-warp-per-row kernel that follows the reference arithmetic literally
- *   "gemv.stage_k", "gemv.stages", "gemv.interleave"   ring geometry / row dealing of the mma.sync kernel
+ *   "gemv.stage_k", "gemv.stages", "gemv.smem_kb", "gemv.interleave"   ring geometry, shared-memory budget and row
+ *                        dealing of the mma.sync kernel
  *   "ts.stages", "ts.smem_kb", "ts.split", "ts.big"     ring depth, shared-memory budget, K split, shape of the tcgen05 kernel
+ *   "ts.slow_reduce"     1 = the partial sums of a K split always travel through the first CTA's weight ring
  *   "ts.tp_world"        number of equal row shards the matrices of this process are split into (tensor parallelism):
  *                        the tcgen05 kernel then splits K, and the attention picks its kernel, as the unsharded call
  *                        would, which keeps a shard's rows bit-identical to the unsharded result
  *   "attn.ctas_per_sm", "attn.min_pages"                grid sizing of the split-KV attention kernel
  *   "attn.cluster"       1 = the one-kernel cluster form of the attention whenever it applies, -1 = never, 0 = small batches
+ *   "attn.cluster_size"  CTAs per cluster of that form: 4, 8 (default) or 16
  *   "attn.force_simple"  1 = always the one-warp-per-head attention kernel
  *   "peer.spin_limit", "tp.spin_limit"   flag probes after which b200q_peer_allgather / the wait of an exchange fused
  *                        into a kernel gives up and records event 5 (default 2^22; tests shorten it)
