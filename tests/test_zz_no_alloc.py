@@ -41,8 +41,13 @@ def test_static_scratch_variant_matches_workspace_variant(cuda, bits):
         want = torch.full_like(q, float("nan"))
         got = torch.full_like(q, float("nan"))
         assert _call(lib, False, case, q, want, ws) == 0
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(cuda)[0]
         assert _call(lib, True, case, q, got) == 0
         torch.cuda.synchronize()
+        if seed != 11:                        # (the very first call on a device may load the kernel's module)
+            # the call left device memory as it found it (a scratch allocation would show as 8 MiB or more)
+            assert free_before - torch.cuda.mem_get_info(cuda)[0] < (4 << 20)
         assert not torch.isnan(got).any()
         assert torch.equal(got, want)          # same kernels, same partials: bit for bit
         outs.append(got)
