@@ -57,10 +57,16 @@ __device__ __forceinline__ void load16(float (&dst)[16], const T* row, int d0, i
     }
 }
 
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// (max, sum, weighted rows) of two disjoint token sets -> of their union; the maxima are in log2 units
 __device__ __forceinline__ void merge_state(float& m, float& l, float (&acc)[16], float m_o, float l_o, const float (&acc_o)[16]) {
     const float M = fmaxf(m, m_o);
-    const float a = m == -INFINITY ? 0.0f : expf(m - M);
-    const float b = m_o == -INFINITY ? 0.0f : expf(m_o - M);
+    const float a = m == -INFINITY ? 0.0f : exp2_fast(m - M);
+    const float b = m_o == -INFINITY ? 0.0f : exp2_fast(m_o - M);
     l = l * a + l_o * b;
 #pragma unroll
     for (int e = 0; e < 16; ++e) acc[e] = acc[e] * a + acc_o[e] * b;
@@ -85,6 +91,8 @@ __global__ void __launch_bounds__(kWarps * 32) paged_fp16_attn_kernel(const __gr
                                          reinterpret_cast<uintptr_t>(p.q)) % 16 == 0);
     const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
     const uint32_t tmask = 0xFFu << (8 * tg);
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+    const int pshift = (p.P & (p.P - 1)) == 0 ? 31 - __clz(p.P) : -1;     // page size a power of two: shifts, no division
 
     for (int c0 = 0; c0 < group; c0 += kHeadChunk) {
         const int nh = min(kHeadChunk, group - c0);
@@ -105,9 +113,10 @@ __global__ void __launch_bounds__(kWarps * 32) paged_fp16_attn_kernel(const __gr
         }
 #pragma unroll 2
         for (int j = lo + warp * 4 + tg; j < hi; j += kWarps * 4) {
-            const int page = bt[j / p.P];
+            const int blk = pshift >= 0 ? j >> pshift : j / p.P;
+            const int page = bt[blk];
             if (page < 0 || page >= p.num_pages) continue;            // unassigned page: its tokens take no part
-            const size_t row = (((size_t)page * p.P + (j % p.P)) * p.Hkv + h) * p.D;
+            const size_t row = (((size_t)page * p.P + (j - blk * p.P)) * p.Hkv + h) * p.D;
             float kf[16], vf[16];
             load16<T>(kf, kp + row, d0, p.D, vec);
             load16<T>(vf, vp + row, d0, p.D, vec);
@@ -120,10 +129,10 @@ __global__ void __launch_bounds__(kWarps * 32) paged_fp16_attn_kernel(const __gr
                 dot += __shfl_xor_sync(tmask, dot, 1);        // the eight lanes of this token only: the other token
                 dot += __shfl_xor_sync(tmask, dot, 2);        // groups of the warp may have left the loop
                 dot += __shfl_xor_sync(tmask, dot, 4);
-                const float sc = dot * p.scale;
+                const float sc = dot * scale_log2;            // scores in log2 units: one ex2 per exponential
                 const float m_new = fmaxf(m[i], sc);
-                const float alpha = m[i] == -INFINITY ? 0.0f : expf(m[i] - m_new);
-                const float beta = expf(sc - m_new);
+                const float alpha = exp2_fast(m[i] - m_new);  // ex2(-inf) = 0 for the first token
+                const float beta = exp2_fast(sc - m_new);
                 l[i] = l[i] * alpha + beta;
                 m[i] = m_new;
 #pragma unroll
@@ -159,7 +168,7 @@ __global__ void __launch_bounds__(kWarps * 32) paged_fp16_attn_kernel(const __gr
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
                 const float mw = part[w][i][0];
-                const float f = mw == -INFINITY ? 0.0f : expf(mw - M);
+                const float f = mw == -INFINITY ? 0.0f : exp2_fast(mw - M);
                 lsum += part[w][i][1] * f;
                 o += part[w][i][2 + d] * f;
             }
@@ -186,7 +195,7 @@ __global__ void __launch_bounds__(128) paged_fp16_merge_kernel(const __grid_cons
     float lsum = 0.0f, o = 0.0f;
     for (int s = 0; s < p.splits; ++s) {
         const float* src = p.workspace + ((size_t)s * p.B * p.Hq + item) * kPartStride;
-        const float f = src[0] == -INFINITY ? 0.0f : expf(src[0] - M);
+        const float f = src[0] == -INFINITY ? 0.0f : exp2f(src[0] - M);      // the maxima are in log2 units
         lsum += src[1] * f;
         if (d < p.D) o += src[2 + d] * f;
     }
