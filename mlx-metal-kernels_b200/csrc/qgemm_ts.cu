@@ -62,7 +62,7 @@ constexpr uint32_t kTsWaitLimit = 1u << 20;
 // producer (also owns the tensor-memory allocation), 9 the MMA issuer, then the activation warps.  Two shapes:
 // the compact one (2 activation warps) stays below half of an SM's shared memory, registers and tensor memory, so
 // that two kernels of a dependent chain can be resident together; the whole-SM one (4 activation warps, deeper
-// rings, all of tensor memory) is for batches above 16 rows and large matrices.
+// rings, all of tensor memory) is for large matrices (16 MB of codes and up) and for whatever the compact one cannot hold.
 constexpr int kDeqWarps = 8;
 constexpr int ts_xwarps(bool whole) { return whole ? 4 : 2; }
 constexpr int ts_threads(bool whole) { return (kDeqWarps + 2 + ts_xwarps(whole)) * 32; }
