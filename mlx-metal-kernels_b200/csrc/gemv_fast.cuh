@@ -70,9 +70,12 @@ __device__ __forceinline__ void words_to_f32(const uint32_t (&w)[4], int dtype, 
 }
 // The kernel's input rows: plain, or (tensor-parallel exchange in packet form) packets that are polled until they carry
 // the sequence number `xs.seq16`.  After a wait ran out the following loads give up quickly.
+// PACKETS is a template parameter of the kernel: the polling loop next to the plain loads cost the single-GPU decode
+// step 6 % (registers, code layout), so kernels that read plain rows are compiled without it.
 struct XSource { uint32_t seq16, limit; };
+template <bool PACKETS>
 __device__ __forceinline__ void load8_x(const void* base, int dtype, int64_t idx, XSource& xs, float (&v)[8]) {
-    if (xs.seq16 == 0u) {
+    if constexpr (!PACKETS) {
         load8_raw(base, dtype, idx, v);
         return;
     }
@@ -101,8 +104,9 @@ __device__ __forceinline__ void store8_act(void* base, int dtype, int64_t idx, c
     *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + idx) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 // z = cast(x + res) (res optional)
+template <bool PACKETS>
 __device__ __forceinline__ void load8_z(const GemvParams& p, int b, int k, XSource& xs, float (&zv)[8]) {
-    load8_x(p.x, p.act_dtype, (int64_t)b * p.K + k, xs, zv);
+    load8_x<PACKETS>(p.x, p.act_dtype, (int64_t)b * p.K + k, xs, zv);
     if (p.res_in != nullptr) {
         float r[8];
         load8_raw(p.res_in, p.act_dtype, (int64_t)b * p.K + k, r);
@@ -111,14 +115,15 @@ __device__ __forceinline__ void load8_z(const GemvParams& p, int b, int k, XSour
     }
 }
 // the activation row the matvec sees: x itself, or cast(z * inv_rms * w)
+template <bool PACKETS>
 __device__ __forceinline__ void load8_act(const GemvParams& p, int b, int k, float inv_rms, bool write_side, XSource& xs,
                                           float (&v)[8]) {
     if (p.norm_w == nullptr) {
-        load8_x(p.x, p.act_dtype, (int64_t)b * p.K + k, xs, v);
+        load8_x<PACKETS>(p.x, p.act_dtype, (int64_t)b * p.K + k, xs, v);
         return;
     }
     float zv[8];
-    load8_z(p, b, k, xs, zv);
+    load8_z<PACKETS>(p, b, k, xs, zv);
     if (write_side && p.z_out != nullptr) store8_act(p.z_out, p.act_dtype, (int64_t)b * p.K + k, zv);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -178,7 +183,7 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t h) { return __half2
 
 // BITS: code width.  LOGG: log2(group size) in {5, 6, 7}.  NB: tensor-core columns per quantisation group
 // (batch rows rounded up to 1, 2, 4, 8).  NT: column tiles (2 only with NB == 8: 9..16 batch rows).
-template <int BITS, int LOGG, int NB, int NT, bool GATE_UP>
+template <int BITS, int LOGG, int NB, int NT, bool GATE_UP, bool PACKETS>
 __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MATS = GATE_UP ? 2 : 1;
@@ -419,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
 
     pdl_wait();   // activations belong to the previous kernel until here
     XSource xsrc = {0u, p.tp_in.spin_limit ? p.tp_in.spin_limit : kTpSpinLimit};
-    if (p.tp_in.world > 0 && p.tp_in.packets) {
+    if (PACKETS) {
         // packet form: nothing to wait for here, every load of the rows checks its own packets
         xsrc.seq16 = tp_seq16(*reinterpret_cast<const volatile uint32_t*>(p.tp_in.epoch));
     } else if (p.tp_in.world > 0) {
@@ -439,7 +444,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float ss = 0.0f;
                     for (int k = ctid * 8; k < p.K; k += kConsumerThreads * 8) {
                         float zv[8];
-                        load8_z(p, b, k, xsrc, zv);
+                        load8_z<PACKETS>(p, b, k, xsrc, zv);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
                     }
@@ -456,7 +461,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float mx = 0.0f;
                     for (int k = ctid * 8; k < p.K; k += kConsumerThreads * 8) {
                         float v[8];
-                        load8_act(p, b, k, inv, false, xsrc, v);
+                        load8_act<PACKETS>(p, b, k, inv, false, xsrc, v);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
                     }
@@ -483,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float ss = 0.0f;
                     for (int k = lane * 8; k < p.K; k += 256) {
                         float zv[8];
-                        load8_z(p, b, k, xsrc, zv);
+                        load8_z<PACKETS>(p, b, k, xsrc, zv);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) ss += zv[i] * zv[i];
                     }
@@ -495,7 +500,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                     float mx = 0.0f;
                     for (int k = lane * 8; k < p.K; k += 256) {
                         float v[8];
-                        load8_act(p, b, k, inv, false, xsrc, v);
+                        load8_act<PACKETS>(p, b, k, inv, false, xsrc, v);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
                     }
@@ -537,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, kMinCtasPerSm) qgemv_kernel(const __
                 float v[8];
                 const float inv = need_row_pass ? xscale[B + b] : 1.0f;
                 const float down = need_row_pass ? 1.0f / xscale[b] : 1.0f;
-                load8_act(p, b, xk0 + kk, inv, write_side, xsrc, v);
+                load8_act<PACKETS>(p, b, xk0 + kk, inv, write_side, xsrc, v);
                 __half h[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j] * down);
@@ -944,14 +949,20 @@ int launch_fast(GemvParams& p, cudaStream_t stream) {
     if (!fits) return B200Q_ERR_UNSUPPORTED;
     const uint64_t total = p.off_ring + (uint64_t)p.stages * p.stage_bytes;
 
-    auto kernel = qgemv_kernel<BITS, LOGG, NB, NT, GATE_UP>;
-    static bool configured[64] = {};   // per instantiation and device; a race only repeats the call
+    // input rows in packet form (fused tensor-parallel exchange): its own instantiation, batches of up to 4 rows
+    const bool packets = p.tp_in.world > 0 && p.tp_in.packets;
+    auto kernel = qgemv_kernel<BITS, LOGG, NB, NT, GATE_UP, false>;
+    if (packets) {
+        if constexpr (NB <= 4 && NT == 1) kernel = qgemv_kernel<BITS, LOGG, NB, NT, GATE_UP, true>;
+        else return B200Q_ERR_UNSUPPORTED;
+    }
+    static bool configured[2][64] = {};   // per instantiation and device; a race only repeats the call
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    if (!configured[packets][dev & 63]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap) != cudaSuccess)
             return B200Q_ERR_LAUNCH;
-        configured[dev & 63] = true;
+        configured[packets][dev & 63] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
