@@ -444,3 +444,17 @@ def test_window_page_walk_covers_exactly_the_attended_positions():
                 want = osparse.decode_row(L, "sliding_window_sink" if sink else "sliding_window", window_size=window,
                                           sink_tokens=sink)
                 assert torch.equal(seen, want), (L, sink, window)
+
+
+def test_header_lists_every_tuning_key_the_library_reads():
+    """b200q_set_tuning takes free-form keys; the list in include/b200q.h must name each key the sources read."""
+    import re
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    header = (root / "include" / "b200q.h").read_text()
+    keys = set()
+    for src in (root / "mlx-metal-kernels_b200" / "csrc").glob("*.cu*"):
+        keys |= set(re.findall(r'tuning_get\("([a-z0-9_.]+)"\)', src.read_text()))
+    assert len(keys) >= 20
+    missing = sorted(k for k in keys if f'"{k}"' not in header)
+    assert not missing, missing
