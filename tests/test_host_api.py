@@ -458,3 +458,25 @@ def test_header_lists_every_tuning_key_the_library_reads():
     assert len(keys) >= 20
     missing = sorted(k for k in keys if f'"{k}"' not in header)
     assert not missing, missing
+
+
+def test_new_entry_points_validate_their_arguments_without_a_device():
+    """Argument checks of the entry points added for block-sparse decode, fp16 pages, the KV quantiser, the packet
+    exchange and the wait self-test return before anything is launched, so they can be exercised without a GPU."""
+    lib = cabi.load()
+    BAD_ARG, UNSUPPORTED = -1, -2
+    # fp16 paged decode: null pointers, heads that do not divide, head dim above 128
+    assert lib.b200q_paged_fp16_gqa_decode(None, None, None, None, None, None, None, 0, 1, 4, 2, 64, 16, 8, 4, 0.125, 0, None) == BAD_ARG
+    assert lib.b200q_paged_fp16_gqa_workspace_bytes(0, 4, 2, 4) == 0
+    assert lib.b200q_paged_fp16_gqa_workspace_bytes(1, 4, 2, 1) == 0           # one CTA per head suffices: no scratch
+    # block-sparse decode: a null mask or a non-positive block size
+    args = [8] + [None] * 9 + [0]
+    assert lib.b200q_paged_gqa_decode_block_sparse(*args, None, 1, 1, 16, None, 1, 4, 2, 128, 16, 8, 4, 32, 0.1, 0, 0, None) == BAD_ARG
+    # packet form of a slot that was never registered; wait self-test outside its range
+    assert lib.b200q_tp_set_packets(9, 1) == BAD_ARG
+    assert lib.b200q_tp_set_packets(99, 1) == BAD_ARG
+    assert lib.b200q_wait_expiry_selftest(0, None, None) == BAD_ARG
+    assert lib.b200q_wait_expiry_selftest(1 << 17, None, None) == BAD_ARG
+    # KV quantiser: null pointers
+    assert lib.b200q_quantize_kv(8, None, None, None, 4, 128, 32, 0, None) == BAD_ARG
+    assert UNSUPPORTED != BAD_ARG
