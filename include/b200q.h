@@ -315,7 +315,8 @@ int b200q_tp_next(int in_slot, int out_slot);
  * slot as in_slot (the pointer passed as `x` is the packet buffer).  A writer kernel stores each element and its
  * "arrived" mark in one 4-byte peer store; a reader polls the packets it loads (bounded, event 5).  No system-scope
  * fence, flag word or counter crosses NVLink: an exchange costs one one-way store latency.  The flag pointers given
- * to b200q_tp_register are unused in this form.  Results are the same bits as in the plain form. */
+ * to b200q_tp_register are unused in this form.  Results are the same bits as in the plain form.  Readers of a packet
+ * buffer take batches of up to 4 rows (B200Q_ERR_UNSUPPORTED above that). */
 int b200q_tp_set_packets(int slot, int packets);
 
 /* Diagnostics (no counterpart in the reference): one CTA waits on a shared-memory barrier that nothing arrives on, with
